@@ -1,0 +1,266 @@
+"""The multi-tensor step: from pytrees to fo_step() calls.
+
+The reference loops over leaves in Python and issues one device call per leaf
+(flashoptim_jax/adamw.py:522-540, lion.py:168-188, sgd.py:193-217).  Here the loop only
+fills descriptor tables; leaves that share the kernel's compile-time switches (param
+dtype, grad dtype, ECC width, state kind, group size) form a bucket and each bucket is one
+fo_step() call that covers all its leaves in a single launch.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Any, Dict, List, NamedTuple, Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+from . import tree as pytree
+from ._dev import DTYPE_CODE, ECC_BITS_OF, as_tensor, require_cuda, stream_ptr
+from .quantization import QuantizedArray
+from .utils import (
+    _group_config_for_path,
+    _has_state_leaf,
+    _is_quantized_leaf,
+    _resolve_learning_rate,
+    _tree_leaves_with_paths,
+    _use_ecc_leaf,
+    _validate_fused_group_size,
+    _validate_master_weight_bits,
+    _validate_meaningful_master_weight_bits,
+    _validate_param_dtypes,
+    no_ecc_leaf,
+    no_state_leaf,
+)
+
+LEAF_DTYPE = np.dtype(
+    [("grad", "<u8"), ("param", "<u8"), ("ecc", "<u8"), ("mu", "<u8"), ("mu_scales", "<u8"), ("nu", "<u8"),
+     ("nu_scales", "<u8"), ("n", "<u8"), ("hyper", "<u4"), ("reserved", "<u4")]
+)
+HYPER_DTYPE = np.dtype(
+    [("lr", "<f4"), ("wd", "<f4"), ("b1", "<f4"), ("b2", "<f4"), ("one_minus_b1", "<f4"), ("one_minus_b2", "<f4"),
+     ("eps", "<f4"), ("bc1", "<f4"), ("bc2", "<f4"), ("flags", "<u4"), ("dev_scalars", "<u8")]
+)
+assert LEAF_DTYPE.itemsize == ctypes.sizeof(_lib.FoLeaf) and HYPER_DTYPE.itemsize == ctypes.sizeof(_lib.FoHyper)
+
+F32 = np.float32
+
+
+def one_minus(beta: float, fused: bool) -> np.float32:
+    """(1 - beta): in fp32 as the fused kernel text does (adamw.py:99-100), or in Python
+    floats rounded once as the jnp text does (adamw.py:394-395)."""
+    if fused:
+        return F32(F32(1.0) - F32(beta))
+    return F32(1.0 - float(beta))
+
+
+def bias_correction(beta: float, count: int) -> np.float32:
+    """1 - f32(beta) ** f32(count) (adamw.py:527-528); the power is taken in float64 and
+    rounded once to fp32."""
+    return F32(F32(1.0) - F32(float(F32(beta)) ** float(count)))
+
+
+class LeafWork(NamedTuple):
+    """Device buffers of one leaf for one step (updated in place) plus its hyper-parameters."""
+
+    bucket: Tuple[Any, ...]  # (device index, param dtype code, grad dtype code, ecc bits, state kind, group size)
+    grad: torch.Tensor
+    param: torch.Tensor
+    ecc: Optional[torch.Tensor]
+    mu: Optional[torch.Tensor]
+    mu_scales: Optional[torch.Tensor]
+    nu: Optional[torch.Tensor]
+    nu_scales: Optional[torch.Tensor]
+    hyper: Tuple[Any, ...]  # (lr, wd, b1, b2, omb1, omb2, eps, bc1, bc2, flags)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def launch(opt: int, work: List[LeafWork]) -> int:
+    """Issue one fo_step per bucket (per <=16 hyper sets); returns the number of calls."""
+    buckets: Dict[Tuple[Any, ...], List[LeafWork]] = {}
+    for w in work:
+        buckets.setdefault(w.bucket, []).append(w)
+    calls = 0
+    lib = _lib.lib()
+    for key, items in buckets.items():
+        dev_index, pdt, gdt, ecc_bits, state, group_size = key
+        hyper_index: Dict[Tuple[Any, ...], int] = {}
+        pending: List[Tuple[LeafWork, int]] = []
+
+        def flush():
+            nonlocal calls, hyper_index, pending
+            if not pending:
+                return
+            leaves = np.zeros(len(pending), dtype=LEAF_DTYPE)
+            ws = [w for w, _ in pending]
+            leaves["grad"] = [w.grad.data_ptr() for w in ws]
+            leaves["param"] = [w.param.data_ptr() for w in ws]
+            leaves["ecc"] = [_ptr(w.ecc) for w in ws]
+            leaves["mu"] = [_ptr(w.mu) for w in ws]
+            leaves["mu_scales"] = [_ptr(w.mu_scales) for w in ws]
+            leaves["nu"] = [_ptr(w.nu) for w in ws]
+            leaves["nu_scales"] = [_ptr(w.nu_scales) for w in ws]
+            leaves["n"] = [w.param.numel() for w in ws]
+            leaves["hyper"] = [h for _, h in pending]
+            hypers = np.zeros(len(hyper_index), dtype=HYPER_DTYPE)
+            for hp, idx in hyper_index.items():
+                hypers[idx] = hp + (0,)
+            desc = _lib.FoStepDesc(
+                struct_size=ctypes.sizeof(_lib.FoStepDesc), opt=opt, param_dtype=pdt, grad_dtype=gdt, ecc_bits=ecc_bits,
+                state=state, group_size=group_size, n_leaves=len(pending), n_hypers=len(hyper_index),
+                leaves=leaves.ctypes.data, hypers=hypers.ctypes.data,
+            )
+            device = torch.device("cuda", dev_index)
+            with torch.cuda.device(device):
+                _lib.check(lib.fo_step(ctypes.byref(desc), stream_ptr(device)))
+            calls += 1
+            hyper_index = {}
+            pending = []
+
+        for w in items:
+            if w.hyper not in hyper_index and len(hyper_index) == _lib.FO_MAX_HYPERS:
+                flush()
+            idx = hyper_index.setdefault(w.hyper, len(hyper_index))
+            pending.append((w, idx))
+        flush()
+    return calls
+
+
+# ---- state initialisation (flashoptim_jax/utils.py:287-306, 337-358) -------------------------
+
+
+def init_moment(param: torch.Tensor, group_size: int, quantize: bool, code_dtype: torch.dtype):
+    """Zero moment: quantized zeros are code 0 / scale 0, which is what quantizing zeros gives."""
+    if quantize:
+        n = param.numel()
+        return QuantizedArray(
+            values=torch.zeros(param.shape, dtype=code_dtype, device=param.device),
+            scales=torch.zeros(((n + group_size - 1) // group_size,), dtype=torch.float16, device=param.device),
+        )
+    return torch.zeros(param.shape, dtype=torch.float32, device=param.device)
+
+
+def init_ecc(param: torch.Tensor, master_weight_bits: Optional[int]) -> torch.Tensor:
+    if _use_ecc_leaf(param, master_weight_bits):
+        return torch.zeros(param.shape, dtype=torch.int8 if master_weight_bits == 24 else torch.int16, device=param.device)
+    return no_ecc_leaf(param.device)
+
+
+def init_common(params: Any, defaults, param_groups, name: str, per_leaf_check=None):
+    """Validation shared by the three init functions; yields (path, leaf tensor, config)."""
+    _validate_param_dtypes(params, defaults, param_groups, name)
+    _validate_meaningful_master_weight_bits(params, defaults, param_groups, name)
+    path_leaves, treedef = _tree_leaves_with_paths(params)
+    out = []
+    for path, leaf in path_leaves:
+        config = _group_config_for_path(path, leaf, defaults, param_groups)
+        _validate_master_weight_bits(config["master_weight_bits"])
+        _validate_fused_group_size(config["group_size"], quantize=config["quantize"], fused=config["fused"])
+        if per_leaf_check is not None:
+            per_leaf_check(config)
+        out.append((path, as_tensor(leaf), config))
+    return out, treedef
+
+
+# ---- one step ----------------------------------------------------------------------------------
+
+
+def _prep_grad(grad: Any, param: torch.Tensor) -> torch.Tensor:
+    g = as_tensor(grad)
+    if g.device != param.device:
+        g = g.to(param.device)
+    if g.dtype not in DTYPE_CODE:
+        g = g.to(torch.float32)  # the reference upcasts every grad to fp32 first (adamw.py:531)
+    if g.shape != param.shape:
+        raise ValueError(f"gradient shape {tuple(g.shape)} does not match parameter shape {tuple(param.shape)}")
+    return g.contiguous()
+
+
+def _own(t: torch.Tensor, donate: bool) -> torch.Tensor:
+    """The buffer the kernel may overwrite: the caller's own when donated, else a copy."""
+    if donate and t.is_contiguous():
+        return t
+    return t.clone(memory_format=torch.contiguous_format)
+
+
+def flatten_step_inputs(name: str, params, grads, state_trees: List[Any]):
+    """Flatten params / grads / state trees and check that they line up (adamw.py:511-519)."""
+    grad_pl, grad_def = _tree_leaves_with_paths(grads)
+    param_pl, treedef = _tree_leaves_with_paths(params)
+    flat_states = []
+    for i, st in enumerate(state_trees):
+        leaves, st_def = pytree.tree_flatten(st, is_leaf=_is_quantized_leaf)
+        if st_def != treedef:
+            raise ValueError(f"{name} state trees must match parameter structure")
+        flat_states.append(leaves)
+    if grad_def != treedef:
+        raise ValueError(f"{name} state trees must match parameter structure")
+    if [p for p, _ in param_pl] != [p for p, _ in grad_pl]:
+        raise ValueError(f"{name} gradients must match parameter paths")
+    return param_pl, [g for _, g in grad_pl], flat_states, treedef
+
+
+def make_work(
+    param: torch.Tensor,
+    grad: torch.Tensor,
+    ecc_leaf: Any,
+    mu_leaf: Any,
+    nu_leaf: Any,
+    config: Dict[str, Any],
+    hyper: Tuple[Any, ...],
+    donate: bool,
+    has_nu: bool,
+    use_momentum: bool = True,
+):
+    """Resolve one leaf into kernel buffers.  Returns (LeafWork, new param, new ecc, new mu, new nu)."""
+    require_cuda(param, "parameter")
+    g = _prep_grad(grad, param)
+    p = _own(param, donate)
+    use_ecc = _use_ecc_leaf(param, config["master_weight_bits"])
+    ecc_out: Any
+    ecc_buf = None
+    ecc_bits = 0
+    if use_ecc:
+        want = torch.int8 if config["master_weight_bits"] == 24 else torch.int16
+        e = as_tensor(ecc_leaf)
+        if e.dim() == 0 and e.dtype == torch.int32:  # sentinel where a buffer is expected: start from zeros (utils.py:459-461)
+            ecc_buf = torch.zeros(param.shape, dtype=want, device=param.device)
+        else:
+            ecc_buf = _own(e.to(want) if e.dtype != want else e, donate and e.dtype == want)
+        ecc_bits = ECC_BITS_OF[want]
+        ecc_out = ecc_buf
+    else:
+        ecc_out = ecc_leaf if isinstance(ecc_leaf, torch.Tensor) and ecc_leaf.dim() == 0 else no_ecc_leaf(param.device)
+
+    group_size = int(config["group_size"])
+    mu_buf = mu_sc = nu_buf = nu_sc = None
+    mu_out: Any = mu_leaf
+    nu_out: Any = nu_leaf
+    if not use_momentum:
+        state = _lib.FO_STATE_NONE
+        mu_out = mu_leaf if isinstance(mu_leaf, torch.Tensor) else no_state_leaf(param.device)
+    elif config["quantize"]:
+        state = _lib.FO_STATE_QUANT
+        if not isinstance(mu_leaf, QuantizedArray):
+            raise ValueError("quantize=True expects QuantizedArray moments in the optimizer state")
+        mu_buf, mu_sc = _own(mu_leaf.values, donate), _own(mu_leaf.scales, donate)
+        mu_out = QuantizedArray(values=mu_buf, scales=mu_sc)
+        if has_nu:
+            nu_buf, nu_sc = _own(nu_leaf.values, donate), _own(nu_leaf.scales, donate)
+            nu_out = QuantizedArray(values=nu_buf, scales=nu_sc)
+    else:
+        state = _lib.FO_STATE_FULL
+        mu_buf = _own(as_tensor(mu_leaf, dtype=torch.float32), donate)
+        mu_out = mu_buf
+        if has_nu:
+            nu_buf = _own(as_tensor(nu_leaf, dtype=torch.float32), donate)
+            nu_out = nu_buf
+    bucket = (param.device.index if param.device.index is not None else torch.cuda.current_device(),
+              DTYPE_CODE[param.dtype], DTYPE_CODE[g.dtype], ecc_bits, state,
+              group_size if state == _lib.FO_STATE_QUANT else 32)
+    work = LeafWork(bucket, g, p, ecc_buf, mu_buf, mu_sc, nu_buf, nu_sc, hyper)
+    return work, p, ecc_out, mu_out, nu_out

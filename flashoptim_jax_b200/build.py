@@ -1,0 +1,107 @@
+"""Builds libflashoptim_b200.so in-tree with nvcc for sm_100a.
+
+The step-kernel family is split into ten instantiation slices (optimizer x state kind)
+compiled from one source with different -D switches, so the build runs in parallel.
+Objects go to csrc/build/, the library to lib/.  Nothing is compiled at import time:
+call build_native() (or `python -m flashoptim_jax_b200.build`).
+"""
+
+from __future__ import annotations
+
+import concurrent.futures
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from typing import List, Tuple
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+OBJ_DIR = os.path.join(CSRC, "build")
+LIB_DIR = os.path.join(HERE, "lib")
+LIB_PATH = os.path.join(LIB_DIR, "libflashoptim_b200.so")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-fmad=false",  # a*b+c never contracts; the explicit __fmaf_rn calls stay FMAs
+    "--ftz=false", "--prec-div=true", "--prec-sqrt=true",
+    "-Xcompiler", "-fPIC,-ffp-contract=off,-O2",
+]
+
+# (object name, source, extra defines)
+_OPTS = (("adam", "FO_OPT_ADAM"), ("lion", "FO_OPT_LION"), ("sgd", "FO_OPT_SGD"))
+_KINDS = (("quant", 0), ("full", 1), ("generic", 3))
+
+
+def _units() -> List[Tuple[str, str, List[str]]]:
+    units = [(name, name + ".cu", []) for name in ("fo_api", "fo_codec", "fo_selftest")]
+    for oname, omacro in _OPTS:
+        for kname, kind in _KINDS:
+            units.append((f"fo_step_{oname}_{kname}", "fo_step_inst.cu",
+                          [f"-DFO_INST_OPT={omacro}", f"-DFO_INST_KIND={kind}", f"-DFO_INST_NAME=lookup_{oname}_{kname}"]))
+    units.append(("fo_step_sgd_none", "fo_step_inst.cu",
+                  ["-DFO_INST_OPT=FO_OPT_SGD", "-DFO_INST_KIND=2", "-DFO_INST_NAME=lookup_sgd_none"]))
+    return units
+
+
+def _nvcc() -> str:
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        raise RuntimeError("nvcc not found; the CUDA toolkit is required to build libflashoptim_b200.so")
+    return nvcc
+
+
+def _sources_digest(extra: List[str]) -> str:
+    h = hashlib.sha256()
+    for root in (CSRC, os.path.join(os.path.dirname(HERE), "include")):
+        for name in sorted(os.listdir(root)):
+            if name.endswith((".cu", ".cuh", ".h")):
+                with open(os.path.join(root, name), "rb") as f:
+                    h.update(name.encode())
+                    h.update(f.read())
+    h.update(" ".join(NVCC_FLAGS + extra).encode())
+    return h.hexdigest()
+
+
+def build_native(force: bool = False, jobs: int | None = None, extra_flags: List[str] | None = None,
+                 lib_path: str = LIB_PATH, verbose: bool = False) -> str:
+    """Compile every CUDA source for sm_100a and link the shared object; returns its path."""
+    extra = list(extra_flags or [])
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    os.makedirs(os.path.dirname(lib_path), exist_ok=True)
+    stamp = lib_path + ".digest"
+    digest = _sources_digest(extra)
+    if not force and os.path.exists(lib_path) and os.path.exists(stamp) and open(stamp).read() == digest:
+        return lib_path
+    nvcc = _nvcc()
+    tag = hashlib.sha256(" ".join(extra).encode()).hexdigest()[:8] if extra else "std"
+    units = _units()
+
+    def compile_one(unit):
+        name, src, defs = unit
+        obj = os.path.join(OBJ_DIR, f"{name}.{tag}.o")
+        cmd = [nvcc, *NVCC_FLAGS, *extra, *defs, "-c", os.path.join(CSRC, src), "-o", obj]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {name}:\n{' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+        if verbose and (r.stdout or r.stderr):
+            print(f"[{name}]\n{r.stdout}{r.stderr}")
+        return obj
+
+    jobs = jobs or max(1, min(len(units), os.cpu_count() or 1))
+    with concurrent.futures.ThreadPoolExecutor(max_workers=jobs) as pool:
+        objs = list(pool.map(compile_one, units))
+    cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", lib_path, *objs, "-lcudart"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"link failed:\n{' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+    with open(stamp, "w") as f:
+        f.write(digest)
+    return lib_path
+
+
+if __name__ == "__main__":
+    path = build_native(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    print(path)

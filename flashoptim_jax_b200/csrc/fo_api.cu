@@ -1,0 +1,160 @@
+// extern "C" surface of libflashoptim_b200.so: argument checking, building the kernel
+// parameter tables, launching.  No allocation, no synchronisation, caller's stream only.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "fo_step.cuh"
+
+namespace fo {
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+static LaunchFn find_launcher(int opt, int pdt, int ecc_bits, int state, bool generic) {
+  if (opt == FO_OPT_ADAM) {
+    if (generic) return lookup_adam_generic(pdt, ecc_bits);
+    if (state == FO_STATE_QUANT) return lookup_adam_quant(pdt, ecc_bits);
+    if (state == FO_STATE_FULL) return lookup_adam_full(pdt, ecc_bits);
+  } else if (opt == FO_OPT_LION) {
+    if (generic) return lookup_lion_generic(pdt, ecc_bits);
+    if (state == FO_STATE_QUANT) return lookup_lion_quant(pdt, ecc_bits);
+    if (state == FO_STATE_FULL) return lookup_lion_full(pdt, ecc_bits);
+  } else if (opt == FO_OPT_SGD) {
+    if (generic) return lookup_sgd_generic(pdt, ecc_bits);
+    if (state == FO_STATE_QUANT) return lookup_sgd_quant(pdt, ecc_bits);
+    if (state == FO_STATE_FULL) return lookup_sgd_full(pdt, ecc_bits);
+    if (state == FO_STATE_NONE) return lookup_sgd_none(pdt, ecc_bits);
+  }
+  return nullptr;
+}
+
+static DevHyper make_dev_hyper(const FoHyper& h, int opt) {
+  DevHyper d;
+  memset(&d, 0, sizeof(d));
+  d.lr = h.lr; d.wd = h.wd; d.b1 = h.b1; d.b2 = h.b2;
+  d.omb1 = h.one_minus_b1; d.omb2 = h.one_minus_b2;
+  d.eps = h.eps; d.bc1 = h.bc1; d.bc2 = h.bc2;
+  // single IEEE fp32 operations, as the reference forms them (adamw.py:103-105)
+  volatile float prod = h.lr * h.wd;
+  d.decay = 1.0f - prod;
+  d.flags = h.flags & (FO_FLAG_DECOUPLED_WD | FO_FLAG_NESTEROV | FO_FLAG_LION_LERP | FO_FLAG_LP_DELTA | FO_FLAG_SCALE_FLOOR);
+  if (opt == FO_OPT_ADAM) {
+    d.lr_bc1 = h.lr / h.bc1;
+    d.sqrt_bc2 = sqrtf(h.bc2);
+    d.rcp_sqrt_bc2 = 1.0f / d.sqrt_bc2;
+    if (adam_is_tame(h.eps, d.sqrt_bc2)) d.flags |= kFlagTameAdam;
+  }
+  d.dyn = h.dev_scalars;
+  return d;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace fo
+
+using namespace fo;
+
+extern "C" int fo_step(const FoStepDesc* d, void* cuda_stream) {
+  if (d == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_step: null descriptor");
+  if (d->struct_size != sizeof(FoStepDesc))
+    return fail(FO_ERR_INVALID_ARG, "fo_step: struct_size %u != %zu (ABI mismatch)", d->struct_size, sizeof(FoStepDesc));
+  if (d->opt < FO_OPT_ADAM || d->opt > FO_OPT_SGD) return fail(FO_ERR_INVALID_ARG, "fo_step: bad opt %d", d->opt);
+  if (d->param_dtype < FO_F32 || d->param_dtype > FO_F16) return fail(FO_ERR_INVALID_ARG, "fo_step: bad param_dtype %d", d->param_dtype);
+  if (d->grad_dtype < FO_F32 || d->grad_dtype > FO_F16) return fail(FO_ERR_INVALID_ARG, "fo_step: bad grad_dtype %d", d->grad_dtype);
+  if (d->ecc_bits != 0 && d->ecc_bits != 8 && d->ecc_bits != 16) return fail(FO_ERR_INVALID_ARG, "fo_step: ecc_bits must be 0, 8 or 16, got %d", d->ecc_bits);
+  if (d->param_dtype == FO_F32 && d->ecc_bits != 0) return fail(FO_ERR_INVALID_ARG, "fo_step: fp32 params carry no ECC");
+  if (d->state < FO_STATE_QUANT || d->state > FO_STATE_NONE) return fail(FO_ERR_INVALID_ARG, "fo_step: bad state %d", d->state);
+  if (d->state == FO_STATE_NONE && d->opt != FO_OPT_SGD) return fail(FO_ERR_INVALID_ARG, "fo_step: only SGD can run without a momentum buffer");
+  if (d->n_leaves == 0) return FO_OK;
+  if (d->leaves == nullptr || d->hypers == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_step: null table");
+  if (d->n_hypers == 0) return fail(FO_ERR_INVALID_ARG, "fo_step: no hyper-parameter set");
+  if (d->n_hypers > FO_MAX_HYPERS) return fail(FO_ERR_TOO_LARGE, "fo_step: %u hyper sets, at most %d per call", d->n_hypers, FO_MAX_HYPERS);
+  bool generic = false;
+  if (d->state == FO_STATE_QUANT) {
+    if (d->group_size < 1) return fail(FO_ERR_INVALID_ARG, "fo_step: group_size %d", d->group_size);
+    if (d->group_size > kGenericTile) return fail(FO_ERR_UNSUPPORTED, "fo_step: group_size %d > %d", d->group_size, kGenericTile);
+    generic = d->group_size != 32;
+  }
+  LaunchFn launch = find_launcher(d->opt, d->param_dtype, d->ecc_bits, d->state, generic);
+  if (launch == nullptr) return fail(FO_ERR_UNSUPPORTED, "fo_step: no kernel for this combination");
+
+  const bool need_mu = d->state != FO_STATE_NONE;
+  const bool need_nu = need_mu && d->opt == FO_OPT_ADAM;
+  const bool need_scales = d->state == FO_STATE_QUANT;
+  for (uint32_t i = 0; i < d->n_leaves; ++i) {
+    const FoLeaf& L = d->leaves[i];
+    if (L.n == 0) continue;
+    if (L.grad == nullptr || L.param == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_step: leaf %u: null grad/param", i);
+    if (d->ecc_bits != 0 && L.ecc == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_step: leaf %u: null ecc", i);
+    if (need_mu && L.mu == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_step: leaf %u: null mu", i);
+    if (need_nu && L.nu == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_step: leaf %u: null nu", i);
+    if (need_scales && L.mu_scales == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_step: leaf %u: null mu_scales", i);
+    if (need_scales && need_nu && L.nu_scales == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_step: leaf %u: null nu_scales", i);
+    if (L.hyper >= d->n_hypers) return fail(FO_ERR_INVALID_ARG, "fo_step: leaf %u: hyper index %u out of range", i, L.hyper);
+  }
+
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  const unsigned long long chunk = chunk_elems(d->state, d->group_size, generic);
+  const unsigned long long kMaxBlocks = 0x7FFFFFFFull;
+
+  StepParams p;
+  memset(&p, 0, sizeof(p));
+  for (uint32_t h = 0; h < d->n_hypers; ++h) p.hyper[h] = make_dev_hyper(d->hypers[h], d->opt);
+  p.grad_dtype = d->grad_dtype;
+  p.group_size = d->state == FO_STATE_QUANT ? d->group_size : 32;
+
+  int count = 0;
+  unsigned long long blocks = 0;
+  auto flush = [&]() -> int {
+    if (count == 0) return FO_OK;
+    p.n_leaves = count;
+    p.first_block[count] = (uint32_t)blocks;
+    cudaError_t e = launch(p, (unsigned int)blocks, stream);
+    count = 0;
+    blocks = 0;
+    if (e != cudaSuccess) return fail(FO_ERR_CUDA, "fo_step: launch failed: %s", cudaGetErrorString(e));
+    return FO_OK;
+  };
+  for (uint32_t i = 0; i < d->n_leaves; ++i) {
+    const FoLeaf& L = d->leaves[i];
+    if (L.n == 0) continue;
+    const unsigned long long nb = (L.n + chunk - 1) / chunk;
+    if (nb > kMaxBlocks) return fail(FO_ERR_TOO_LARGE, "fo_step: leaf %u with %llu elements exceeds one launch", i, (unsigned long long)L.n);
+    if (count == kMaxLeaves || blocks + nb > kMaxBlocks) {
+      int rc = flush();
+      if (rc != FO_OK) return rc;
+    }
+    DevLeaf& D = p.leaf[count];
+    D.grad = L.grad; D.param = L.param; D.ecc = L.ecc; D.mu = L.mu; D.mu_scales = L.mu_scales;
+    D.nu = L.nu; D.nu_scales = L.nu_scales; D.n = L.n;
+    p.first_block[count] = (uint32_t)blocks;
+    p.hyper_of[count] = (uint8_t)L.hyper;
+    p.aligned[count] = aligned16(L.grad) && aligned16(L.param) && aligned16(L.ecc) && aligned16(L.mu) && aligned16(L.nu);
+    blocks += nb;
+    ++count;
+  }
+  return flush();
+}
+
+extern "C" int fo_version(void) { return FO_ABI_VERSION; }
+
+extern "C" const char* fo_status_string(int status) {
+  switch (status) {
+    case FO_OK: return "ok";
+    case FO_ERR_INVALID_ARG: return "invalid argument";
+    case FO_ERR_UNSUPPORTED: return "unsupported configuration";
+    case FO_ERR_CUDA: return "CUDA error";
+    case FO_ERR_TOO_LARGE: return "size beyond a stated maximum";
+    default: return "unknown status";
+  }
+}
+
+extern "C" const char* fo_last_error(void) { return fo::g_err; }

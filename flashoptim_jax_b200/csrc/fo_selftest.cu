@@ -1,0 +1,169 @@
+// Device self-checks: every arithmetic shortcut in fo_math.cuh (namespace fast) against the
+// plain IEEE formulation (namespace ieee), exhaustively where the input space allows.
+#include "fo_step.cuh"
+
+namespace fo {
+int fail(int code, const char* fmt, ...);
+
+FO_DEVI bool same_float(float a, float b) {
+  return __float_as_uint(a) == __float_as_uint(b) || (a != a && b != b);
+}
+
+FO_DEVI void tally(unsigned long long bad, unsigned long long* out) {
+  for (int o = 16; o > 0; o >>= 1) bad += __shfl_xor_sync(0xFFFFFFFFu, bad, o);
+  if ((threadIdx.x & 31) == 0 && bad) atomicAdd(out, bad);
+}
+
+// every non-negative finite fp32, zero and subnormals included
+__global__ void selftest_sqrt(unsigned long long* out) {
+  unsigned long long bad = 0;
+  const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+  for (unsigned long long b = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; b < 0x7F800000ull; b += stride) {
+    float v = __uint_as_float((uint32_t)b);
+    bad += !same_float(fast::sqrt_rn(v), fsqrt(v));
+  }
+  tally(bad, out);
+}
+
+// every fp32 with |n| <= 1: the int8 code through the shortcut division vs the IEEE one
+__global__ void selftest_softsign(unsigned long long* out) {
+  unsigned long long bad = 0;
+  const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+  for (unsigned long long b = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; b <= 0x3F800000ull; b += stride) {
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      float n = __uint_as_float((uint32_t)b | (s ? 0x80000000u : 0u));
+      bad += fast::softsign_code(n) != ieee::quant_m(n, 1.0f);
+    }
+  }
+  tally(bad, out);
+}
+
+template <int PDT, int ECC_BITS>
+__global__ void selftest_reconstruct(unsigned long long* out) {
+  unsigned long long bad = 0;
+  constexpr unsigned long long kEcc = 1ull << ECC_BITS;
+  const unsigned long long total = 65536ull * kEcc;
+  const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+  for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    uint32_t bits = (uint32_t)(i / kEcc);
+    int e = (int)(i % kEcc) - (int)(kEcc / 2);
+    bad += !same_float(fast::reconstruct<PDT, ECC_BITS>(bits, e), ieee::reconstruct<PDT, ECC_BITS>(bits, e));
+  }
+  tally(bad, out);
+}
+
+template <int PDT, int ECC_BITS>
+__global__ void selftest_split(unsigned long long* out) {
+  unsigned long long bad = 0;
+  const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+  for (unsigned long long b = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; b < (1ull << 32); b += stride) {
+    float theta = __uint_as_float((uint32_t)b);
+    if (theta != theta) continue;
+    uint32_t b0, b1;
+    int e0, e1;
+    fast::split<PDT, ECC_BITS>(theta, b0, e0);
+    ieee::split<PDT, ECC_BITS>(theta, b1, e1);
+    bad += (b0 != b1) || (e0 != e1);
+  }
+  tally(bad, out);
+}
+
+FO_DEVI uint32_t mix(uint64_t x) {
+  x ^= x >> 33; x *= 0xff51afd7ed558ccdull; x ^= x >> 33; x *= 0xc4ceb9fe1a85ec53ull; x ^= x >> 33;
+  return (uint32_t)x;
+}
+
+// random (value, group scale) pairs with |value| <= scale: codes through the reciprocal
+// shortcut vs the IEEE divisions; and the Adam denominator sqrt(nu)/sqrt(bc2) + eps.
+__global__ void selftest_group_div(unsigned long long pairs, unsigned long long* out) {
+  unsigned long long bad = 0;
+  const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+  for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < pairs; i += stride) {
+    uint32_t r0 = mix(i * 4 + 0), r1 = mix(i * 4 + 1), r2 = mix(i * 4 + 2), r3 = mix(i * 4 + 3);
+    // scale: random mantissa, exponent field in [28, 226] (about 1e-30 .. 1e30)
+    float safe = __uint_as_float(((28u + r0 % 199u) << 23) | (r1 & 0x7FFFFFu));
+    // value: scale shrunk by a random factor in (0, 1], heavy weight near 1 and across 40 binades
+    float frac = __uint_as_float(((127u - (r2 >> 8) % ((r2 & 1u) ? 2u : 40u)) << 23) | (r3 & 0x7FFFFFu));
+    float x = fminf(fmul(safe, fmul(frac, 0.5f)), safe);
+    if (r2 & 2u) x = safe;  // the group maximum itself
+    fast::GroupScale gs = fast::group_scale(safe, false);
+    bad += fast::quant_m(x, gs) != ieee::quant_m(x, safe);
+    bad += fast::quant_m(-x, gs) != ieee::quant_m(-x, safe);
+    bad += fast::quant_v(x, gs) != ieee::quant_v(x, safe);
+    // Adam denominator: sqrt_bc2 in [2^-16, 2), eps in [1e-12, 1], root anywhere in [0, 1e30]
+    float sq = __uint_as_float(((111u + r1 % 17u) << 23) | (r0 & 0x7FFFFFu));
+    float eps = __uint_as_float(((87u + r3 % 41u) << 23) | (r2 & 0x7FFFFFu));
+    float root = (r0 & 4u) ? x : __uint_as_float(((r2 >> 3) % 227u << 23) | (r1 & 0x7FFFFFu));
+    if (adam_is_tame(eps, sq)) {
+      float a = fadd(fast::div_by_rcp(root, sq, __frcp_rn(sq)), eps);
+      float b = fadd(fdiv(root, sq), eps);
+      bad += !same_float(a, b);
+    }
+  }
+  tally(bad, out);
+}
+
+__global__ void selftest_code_tables(unsigned long long* out) {
+  unsigned long long bad = 0;
+  const int stride = gridDim.x * blockDim.x;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < 65536; i += stride) {
+    int e16 = i - 32768;
+    bad += !same_float(fast::ecc_fraction<16>(e16), fdiv((float)e16, 32767.0f));
+    if (i < 256) {
+      int e8 = i - 128;
+      bad += !same_float(fast::ecc_fraction<8>(e8), fdiv((float)e8, 127.0f));
+    }
+  }
+  tally(bad, out);
+}
+
+}  // namespace fo
+
+using namespace fo;
+
+extern "C" int fo_selftest(int32_t which, int64_t arg, uint64_t* mismatches, void* cuda_stream) {
+  if (mismatches == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_selftest: null result pointer");
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  unsigned long long* d = nullptr;
+  // the only allocation in the library: a test-only counter, freed before returning
+  cudaError_t e = cudaMalloc(&d, sizeof(unsigned long long));
+  if (e != cudaSuccess) return fail(FO_ERR_CUDA, "fo_selftest: %s", cudaGetErrorString(e));
+  cudaMemsetAsync(d, 0, sizeof(unsigned long long), s);
+  const int grid = 148 * 8, block = 256;
+  int rc = FO_OK;
+  switch (which) {
+    case FO_SELFTEST_SQRT: selftest_sqrt<<<grid, block, 0, s>>>(d); break;
+    case FO_SELFTEST_SOFTSIGN: selftest_softsign<<<grid, block, 0, s>>>(d); break;
+    case FO_SELFTEST_GROUP_DIV:
+      selftest_group_div<<<grid, block, 0, s>>>((unsigned long long)(arg > 0 ? arg : 1) * 1000000ull, d);
+      break;
+    case FO_SELFTEST_CODE_TABLES: selftest_code_tables<<<64, block, 0, s>>>(d); break;
+    case FO_SELFTEST_RECONSTRUCT:
+    case FO_SELFTEST_SPLIT: {
+      const int pdt = (int)(arg / 100), eb = (int)(arg % 100);
+      bool ok = false;
+#define X(P, E)                                                                              \
+  if (pdt == P && eb == E) {                                                                 \
+    ok = true;                                                                               \
+    if (which == FO_SELFTEST_RECONSTRUCT) selftest_reconstruct<P, E><<<grid, block, 0, s>>>(d); \
+    else selftest_split<P, E><<<grid, block, 0, s>>>(d);                                     \
+  }
+      X(FO_BF16, 8) X(FO_BF16, 16) X(FO_F16, 8) X(FO_F16, 16)
+#undef X
+      if (!ok) rc = fail(FO_ERR_INVALID_ARG, "fo_selftest: arg %lld names no (dtype, ecc) pair", (long long)arg);
+      break;
+    }
+    default: rc = fail(FO_ERR_INVALID_ARG, "fo_selftest: unknown test %d", which);
+  }
+  if (rc == FO_OK) {
+    e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    unsigned long long h = 0;
+    if (e == cudaSuccess) e = cudaMemcpy(&h, d, sizeof(h), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) rc = fail(FO_ERR_CUDA, "fo_selftest: %s", cudaGetErrorString(e));
+    *mismatches = h;
+  }
+  cudaFree(d);
+  return rc;
+}

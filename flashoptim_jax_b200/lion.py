@@ -1,0 +1,79 @@
+"""flash_lion: the reference's API (flashoptim_jax/lion.py:192-249) over the CUDA step.
+
+`fused=True` follows the kernel text b*mu + (1-b)*g with (1-b) formed in fp32
+(momentum_kernel.py:77-79); `fused=False` follows the jnp text mu + (1-b)*(g - mu) with
+(1-b) formed in Python floats (lion.py:50-52).  Both run the same CUDA kernel.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Dict, List, NamedTuple, Optional
+
+import torch
+
+from . import _engine as eng
+from . import _lib
+from . import utils
+from ._dev import as_tensor
+
+
+class FlashLionState(NamedTuple):
+    count: torch.Tensor
+    mu: Any
+    ecc: Any
+
+
+def flash_lion(learning_rate=1e-4, b1: float = 0.9, b2: float = 0.99, weight_decay: float = 0.0, quantize: bool = True,
+               master_weight_bits: Optional[int] = 24, group_size: int = 32, fused: bool = True,
+               param_groups: Optional[List[Dict[str, Any]]] = None, donate: bool = False) -> utils.FlashOptimizer:
+    name = "flash_lion"
+    utils._validate_master_weight_bits(master_weight_bits)
+    utils._validate_fused_group_size(group_size, quantize=quantize, fused=fused)
+    defaults = {
+        "learning_rate": learning_rate, "b1": b1, "b2": b2, "weight_decay": weight_decay, "quantize": quantize,
+        "master_weight_bits": master_weight_bits, "group_size": group_size, "fused": fused,
+    }
+
+    def init_fn(params: Any) -> FlashLionState:
+        entries, treedef = eng.init_common(params, defaults, param_groups, name)
+        mus = [eng.init_moment(leaf, c["group_size"], c["quantize"], torch.int8) for _, leaf, c in entries]
+        eccs = [eng.init_ecc(leaf, c["master_weight_bits"]) for _, leaf, c in entries]
+        return FlashLionState(count=torch.zeros((), dtype=torch.int32), mu=treedef.unflatten(mus), ecc=treedef.unflatten(eccs))
+
+    def step_fn(params: Any, state: FlashLionState, grads: Any):
+        old_count = as_tensor(state.count, dtype=torch.int32).cpu()
+        param_pl, grad_leaves, (ecc_leaves, mu_leaves), treedef = eng.flatten_step_inputs(
+            name, params, grads, [state.ecc, state.mu])
+        work, new_p, new_e, new_m = [], [], [], []
+        for (path, leaf), g, e, m in zip(param_pl, grad_leaves, ecc_leaves, mu_leaves):
+            leaf = as_tensor(leaf)
+            config = utils._group_config_for_path(path, leaf, defaults, param_groups)
+            lr = utils._resolve_learning_rate(config["learning_rate"], old_count)
+            is_fused = bool(config["fused"])
+            flags = _lib.FO_FLAG_DECOUPLED_WD | (_lib.FO_FLAG_SCALE_FLOOR if is_fused else _lib.FO_FLAG_LION_LERP)
+            hyper = (
+                eng.F32(lr), eng.F32(config["weight_decay"]), eng.F32(config["b1"]), eng.F32(config["b2"]),
+                eng.one_minus(config["b1"], is_fused), eng.one_minus(config["b2"], is_fused),
+                eng.F32(0.0), eng.F32(1.0), eng.F32(1.0), flags,
+            )
+            w, p_out, e_out, m_out, _ = eng.make_work(leaf, g, e, m, None, config, hyper, donate, has_nu=False)
+            work.append(w)
+            new_p.append(p_out); new_e.append(e_out); new_m.append(m_out)
+        eng.launch(_lib.FO_OPT_LION, work)
+        new_state = FlashLionState(count=torch.tensor(int(old_count) + 1, dtype=torch.int32),
+                                   mu=treedef.unflatten(new_m), ecc=treedef.unflatten(new_e))
+        return treedef.unflatten(new_p), new_state
+
+    return utils.FlashOptimizer(init=init_fn, step=step_fn)
+
+
+def flash_lion_state_dict(state: FlashLionState) -> Dict[str, Any]:
+    """flashoptim_jax/lion.py:234-240."""
+    return {"count": as_tensor(state.count), "mu": utils._tree_state_dict(state.mu), "ecc": utils._tree_state_dict(state.ecc)}
+
+
+def load_flash_lion_state_dict(state_dict: Dict[str, Any]) -> FlashLionState:
+    """flashoptim_jax/lion.py:243-249."""
+    return FlashLionState(count=as_tensor(state_dict["count"], dtype=torch.int32),
+                          mu=utils._tree_from_state_dict(state_dict["mu"]),
+                          ecc=utils._tree_from_state_dict(state_dict["ecc"]))

@@ -1,0 +1,173 @@
+/*
+ * flashoptim_b200 — C ABI of the B200-native optimizer-step library.
+ *
+ * One shared object (libflashoptim_b200.so), plain C types only.  Every array argument
+ * is a DEVICE pointer unless it is called a table; tables (leaf / hyper-parameter
+ * descriptors) are HOST memory and are copied into kernel parameters at launch.  The
+ * library never allocates, frees or keeps caller memory, never synchronises the device
+ * and launches only on the stream it is given, so a call can sit inside any framework's
+ * stream order (XLA custom call, PyTorch, CUDA graph).  All updates are in place: the
+ * reference's fused kernels alias every output onto its input
+ * (flashoptim_jax/adamw.py:268,293; flashoptim_jax/momentum_kernel.py:222,246).
+ *
+ * All functions return FO_OK or an FO_ERR_* code; fo_status_string() names a code and
+ * fo_last_error() returns a thread-local detail message.
+ *
+ * Citations "file:line" refer to the reference project (samacqua/flashoptim-jax).
+ */
+#ifndef FLASHOPTIM_B200_H_
+#define FLASHOPTIM_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FO_ABI_VERSION 1
+
+/* status codes */
+#define FO_OK 0
+#define FO_ERR_INVALID_ARG 1  /* null pointer, bad enum, inconsistent descriptor */
+#define FO_ERR_UNSUPPORTED 2  /* legal in the reference but not built here (e.g. group_size > 1024) */
+#define FO_ERR_CUDA 3         /* a CUDA runtime call failed; see fo_last_error() */
+#define FO_ERR_TOO_LARGE 4    /* more hyper-parameter sets than one call can carry, or a size beyond a stated maximum */
+
+/* element types of params / grads (the dtypes the fused path accepts, flashoptim_jax/utils.py:26-31) */
+#define FO_F32 0
+#define FO_BF16 1
+#define FO_F16 2
+
+/* optimizer family: Adam/AdamW share a kernel (flashoptim_jax/adamw.py:28-222), Lion and
+ * SGD/SGDW share the other (flashoptim_jax/momentum_kernel.py:21-180, switch do_lion) */
+#define FO_OPT_ADAM 0
+#define FO_OPT_LION 1
+#define FO_OPT_SGD 2
+
+/* how the moments are stored */
+#define FO_STATE_QUANT 0 /* int8 mu / uint8 nu codes + fp16 group scales (quantize=True) */
+#define FO_STATE_FULL 1  /* fp32 mu / nu (quantize=False; adamw.py:148-222, momentum_kernel.py:115-180) */
+#define FO_STATE_NONE 2  /* SGD with momentum == 0: no buffer (flashoptim_jax/sgd.py:50-57, utils.py:351-352) */
+
+/* FoHyper.flags */
+#define FO_FLAG_DECOUPLED_WD 1u /* AdamW / SGDW: theta *= 1 - lr*wd (adamw.py:102-103); clear = wd added to the grad (adamw.py:95-96) */
+#define FO_FLAG_NESTEROV 2u     /* SGD: step = grad + momentum*mu (momentum_kernel.py:82) */
+#define FO_FLAG_LION_LERP 4u    /* Lion written as mu + (1-b)(g-mu) (lion.py:50-52) instead of b*mu + (1-b)*g (momentum_kernel.py:78-79) */
+#define FO_FLAG_LP_DELTA 8u     /* Adam hands back param + lp(new - param) like the CPU path (adamw.py:411,415,463) instead of new (adamw.py:134) */
+#define FO_FLAG_SCALE_FLOOR 16u /* group scale guard max(absmax,1e-12) (adamw.py:121,128) instead of where(absmax>0,absmax,1) (quantization.py:41,64) */
+
+/*
+ * One set of hyper-parameters (one param group, flashoptim_jax/utils.py:138-154).
+ * These are the 0-d fp32 operands of the reference kernels (adamw.py:272-278,
+ * momentum_kernel.py:230-233) plus the two derived constants the two reference texts form
+ * differently (see FO_FLAG_*).  Field use by family:
+ *   ADAM: lr wd b1 b2 one_minus_b1 one_minus_b2 eps bc1 bc2
+ *   LION: lr wd b1 b2 one_minus_b1 one_minus_b2          (b1 = update coef, b2 = momentum coef)
+ *   SGD : lr wd b1(=momentum) one_minus_b1(= 1 - dampening)
+ * dev_scalars, when not NULL, is a device float[3] = {lr, bc1, bc2} read by the kernel in
+ * place of the host values, so a traced schedule / step count needs no host round trip.
+ */
+typedef struct FoHyper {
+  float lr, wd;
+  float b1, b2;
+  float one_minus_b1, one_minus_b2;
+  float eps;
+  float bc1, bc2; /* 1 - b^count, count = step number after increment (adamw.py:510,527-528) */
+  uint32_t flags;
+  const float* dev_scalars;
+} FoHyper;
+
+/*
+ * One pytree leaf, flattened row-major (flashoptim_jax/utils.py:450-496).
+ *   grad       n elements of grad dtype
+ *   param      n elements of param dtype, updated in place
+ *   ecc        n int8 (ecc_bits 8) / int16 (ecc_bits 16), or NULL when ecc_bits == 0
+ *   mu         n int8 codes (QUANT) or n fp32 (FULL), NULL for NONE
+ *   mu_scales  ceil(n / group_size) fp16 (QUANT), else NULL
+ *   nu, nu_scales  same for the second moment (uint8 codes), ADAM only, else NULL
+ *   hyper      index into the hyper table
+ */
+typedef struct FoLeaf {
+  const void* grad;
+  void* param;
+  void* ecc;
+  void* mu;
+  void* mu_scales;
+  void* nu;
+  void* nu_scales;
+  uint64_t n;
+  uint32_t hyper;
+  uint32_t reserved;
+} FoLeaf;
+
+/*
+ * One multi-tensor step: every leaf of the table shares the compile-time switches of the
+ * reference's pallas_call (adamw.py:309-320, momentum_kernel.py:262-275); leaves that
+ * differ in them go into separate calls.  Any number of leaves; at most FO_MAX_HYPERS
+ * hyper sets.
+ */
+#define FO_MAX_HYPERS 16
+typedef struct FoStepDesc {
+  uint32_t struct_size; /* sizeof(FoStepDesc), guards against ABI skew */
+  int32_t opt;          /* FO_OPT_* */
+  int32_t param_dtype;  /* FO_F32 / FO_BF16 / FO_F16 */
+  int32_t grad_dtype;   /* FO_F32 / FO_BF16 / FO_F16 (the reference upcasts grads to fp32 first, adamw.py:531) */
+  int32_t ecc_bits;     /* 0, 8 (master_weight_bits 24 on a 16-bit param) or 16 (32) */
+  int32_t state;        /* FO_STATE_* */
+  int32_t group_size;   /* elements per quantization group, 1..1024 (QUANT only; default 32) */
+  uint32_t n_leaves;
+  uint32_t n_hypers;
+  const FoLeaf* leaves;   /* host table */
+  const FoHyper* hypers;  /* host table */
+} FoStepDesc;
+
+/* Replaces pl.pallas_call(...) of _fused_flash_adamw_leaf_impl (adamw.py:225-353) and of
+ * fused_momentum_leaf_impl (momentum_kernel.py:183-302), for a whole pytree at once. */
+int fo_step(const FoStepDesc* desc, void* cuda_stream);
+
+/* Codecs on fp32 arrays; n elements, scales has ceil(n/group_size) fp16 entries.
+ * scale_floor selects the guard of FO_FLAG_SCALE_FLOOR.
+ *   fo_quantize_momentum   flashoptim_jax/quantization.py:37-46
+ *   fo_dequantize_momentum flashoptim_jax/quantization.py:49-56
+ *   fo_quantize_variance   flashoptim_jax/quantization.py:59-68
+ *   fo_dequantize_variance flashoptim_jax/quantization.py:71-77 */
+int fo_quantize_momentum(const float* x, int8_t* values, void* scales_f16, uint64_t n, int32_t group_size,
+                         int32_t scale_floor, void* cuda_stream);
+int fo_dequantize_momentum(const int8_t* values, const void* scales_f16, float* out, uint64_t n, int32_t group_size,
+                           void* cuda_stream);
+int fo_quantize_variance(const float* x, uint8_t* values, void* scales_f16, uint64_t n, int32_t group_size,
+                         int32_t scale_floor, void* cuda_stream);
+int fo_dequantize_variance(const uint8_t* values, const void* scales_f16, float* out, uint64_t n, int32_t group_size,
+                           void* cuda_stream);
+
+/* fp32 master weight <-> (16-bit param, ECC).  ecc_bits 0 means a plain cast (ecc unused).
+ *   fo_split        flashoptim_jax/compression.py:84-104, utils.py:539-557
+ *   fo_reconstruct  flashoptim_jax/compression.py:107-121, utils.py:521-536 */
+int fo_split(const float* theta, void* param_lp, void* ecc, int32_t param_dtype, int32_t ecc_bits, uint64_t n,
+             void* cuda_stream);
+int fo_reconstruct(const void* param_lp, const void* ecc, float* theta, int32_t param_dtype, int32_t ecc_bits,
+                   uint64_t n, void* cuda_stream);
+
+/*
+ * Device self-checks of the exact-arithmetic shortcuts the kernels use (no counterpart in
+ * the reference).  Each runs a sweep on the current device and writes the number of inputs
+ * on which the shortcut and the plain IEEE formulation disagree into *mismatches (host).
+ * These calls synchronise the stream.  `which` is one of FO_SELFTEST_*; `arg` selects a
+ * sub-case (see the test-suite).
+ */
+#define FO_SELFTEST_SQRT 0        /* every non-negative finite fp32 */
+#define FO_SELFTEST_SOFTSIGN 1    /* every fp32 in [-1, 1] */
+#define FO_SELFTEST_RECONSTRUCT 2 /* every (param bits, ecc) pair; arg = param_dtype*100 + ecc_bits */
+#define FO_SELFTEST_SPLIT 3       /* every fp32 bit pattern; arg = param_dtype*100 + ecc_bits */
+#define FO_SELFTEST_GROUP_DIV 4   /* arg = number of random (a, b) pairs in millions */
+#define FO_SELFTEST_CODE_TABLES 5 /* every int8 / uint8 code and every int16 ECC value */
+int fo_selftest(int32_t which, int64_t arg, uint64_t* mismatches, void* cuda_stream);
+
+int fo_version(void);
+const char* fo_status_string(int status);
+const char* fo_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHOPTIM_B200_H_ */
