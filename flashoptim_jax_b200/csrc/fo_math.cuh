@@ -155,7 +155,7 @@ FO_DEVI void split(float theta, uint32_t& bits, int& ecc) {
   bits = L::from_f32(theta);
   float err = fsub(theta, L::to_f32(bits));
   int eb = max((int)((bits & 0x7FFFu) >> L::MANT), 1);
-  int field = 127 - (eb - L::BIAS - L::MANT - 1) + 127;  // exponent field of 2^(-log_half_ulp)
+  int field = 127 - (eb - L::BIAS - L::MANT - 1);  // exponent field of 2^(-log_half_ulp)
   float en;
   if (field <= 254) {
     en = fmul(err, __uint_as_float((uint32_t)field << 23));
