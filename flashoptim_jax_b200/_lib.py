@@ -19,7 +19,7 @@ FO_STATE_QUANT, FO_STATE_FULL, FO_STATE_NONE = 0, 1, 2
 FO_FLAG_DECOUPLED_WD, FO_FLAG_NESTEROV, FO_FLAG_LION_LERP, FO_FLAG_LP_DELTA, FO_FLAG_SCALE_FLOOR = 1, 2, 4, 8, 16
 FO_MAX_HYPERS = 16
 FO_SELFTEST_SQRT, FO_SELFTEST_SOFTSIGN, FO_SELFTEST_RECONSTRUCT, FO_SELFTEST_SPLIT = 0, 1, 2, 3
-FO_SELFTEST_GROUP_DIV, FO_SELFTEST_CODE_TABLES = 4, 5
+FO_SELFTEST_GROUP_DIV, FO_SELFTEST_CODE_TABLES, FO_SELFTEST_RCP = 4, 5, 6
 
 EXPORTS = (
     "fo_step", "fo_quantize_momentum", "fo_dequantize_momentum", "fo_quantize_variance",

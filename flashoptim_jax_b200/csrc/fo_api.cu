@@ -58,6 +58,18 @@ static DevHyper make_dev_hyper(const FoHyper& h, int opt) {
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// SM count of the device that is current on the calling thread (cached per device ordinal)
+static int sm_count_of_current_device() {
+  static int cache[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  if (dev >= 0 && dev < 64 && cache[dev] > 0) return cache[dev];
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+  if (dev >= 0 && dev < 64) cache[dev] = sms;
+  return sms;
+}
+
 }  // namespace fo
 
 using namespace fo;
@@ -102,7 +114,10 @@ extern "C" int fo_step(const FoStepDesc* d, void* cuda_stream) {
   }
 
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  const unsigned long long chunk = chunk_elems(d->state, d->group_size, generic);
+  const unsigned long long chunk = chunk_elems(d->group_size, generic);
+  LaunchInfo info;
+  info.sm_count = sm_count_of_current_device();
+  if (info.sm_count <= 0) return fail(FO_ERR_CUDA, "fo_step: cannot query the current device");
   const unsigned long long kMaxBlocks = 0x7FFFFFFFull;
 
   StepParams p;
@@ -117,7 +132,8 @@ extern "C" int fo_step(const FoStepDesc* d, void* cuda_stream) {
     if (count == 0) return FO_OK;
     p.n_leaves = count;
     p.first_block[count] = (uint32_t)blocks;
-    cudaError_t e = launch(p, (unsigned int)blocks, stream);
+    info.total_chunks = (unsigned int)blocks;
+    cudaError_t e = launch(p, info, stream);
     count = 0;
     blocks = 0;
     if (e != cudaSuccess) return fail(FO_ERR_CUDA, "fo_step: launch failed: %s", cudaGetErrorString(e));

@@ -7,55 +7,56 @@
 
 namespace fo {
 int fail(int code, const char* fmt, ...);
+constexpr int kCodecThreads = 256;
 
 // One block per tile of whole groups (any group size 1..1024), group maxima through
 // shared-memory atomics on non-negative float bit patterns.
 template <bool VARIANCE>
-__global__ void __launch_bounds__(kThreads) quantize_kernel(const float* __restrict__ x, void* __restrict__ values,
+__global__ void __launch_bounds__(256) quantize_kernel(const float* __restrict__ x, void* __restrict__ values,
                                                             __half* __restrict__ scales, unsigned long long n, int G,
                                                             int floor_mode) {
   __shared__ unsigned int smax[kGenericTile];
   const int groups_per_tile = max(1, kGenericTile / G);
   const int tile = groups_per_tile * G;
   const unsigned long long base = (unsigned long long)blockIdx.x * tile;
-  for (int i = threadIdx.x; i < groups_per_tile; i += kThreads) smax[i] = 0u;
+  for (int i = threadIdx.x; i < groups_per_tile; i += kCodecThreads) smax[i] = 0u;
   __syncthreads();
-  constexpr int kPer = kGenericTile / kThreads;
+  constexpr int kPer = kGenericTile / kCodecThreads;
   float val[kPer];
 #pragma unroll
   for (int k = 0; k < kPer; ++k) {
-    const int li = threadIdx.x + k * kThreads;
+    const int li = threadIdx.x + k * kCodecThreads;
     const unsigned long long i = base + li;
     val[k] = 0.0f;
     if (li < tile && i < n) {
       float v = x[i];
-      val[k] = VARIANCE ? step_sqrt(v) : v;
+      val[k] = VARIANCE ? fast::sqrt_rn(v) : v;
       atomicMax(&smax[li / G], __float_as_uint(fabsf(val[k])));
     }
   }
   __syncthreads();
 #pragma unroll
   for (int k = 0; k < kPer; ++k) {
-    const int li = threadIdx.x + k * kThreads;
+    const int li = threadIdx.x + k * kCodecThreads;
     const unsigned long long i = base + li;
     if (li < tile && i < n) {
       const float a = __uint_as_float(smax[li / G]);
-      const GroupScale gs = step_group_scale(a, floor_mode != 0);
-      if (VARIANCE) ((unsigned char*)values)[i] = (unsigned char)step_quant_v(val[k], gs);
-      else ((signed char*)values)[i] = (signed char)step_quant_m(val[k], gs);
+      const fast::GroupScale gs = fast::group_scale(a, floor_mode != 0);
+      if (VARIANCE) ((unsigned char*)values)[i] = (unsigned char)fast::quant_v(val[k], gs);
+      else ((signed char*)values)[i] = (signed char)fast::quant_m(val[k], gs);
       if (li % G == 0) scales[i / G] = __float2half_rn(a);
     }
   }
 }
 
 template <bool VARIANCE>
-__global__ void __launch_bounds__(kThreads) dequantize_kernel(const void* __restrict__ values,
+__global__ void __launch_bounds__(kCodecThreads) dequantize_kernel(const void* __restrict__ values,
                                                               const __half* __restrict__ scales, float* __restrict__ out,
                                                               unsigned long long n, int G) {
   __shared__ float lut_m[256], lut_v[256];
   build_luts(lut_m, lut_v);
-  const unsigned long long stride = (unsigned long long)gridDim.x * kThreads;
-  for (unsigned long long i = (unsigned long long)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+  const unsigned long long stride = (unsigned long long)gridDim.x * kCodecThreads;
+  for (unsigned long long i = (unsigned long long)blockIdx.x * kCodecThreads + threadIdx.x; i < n; i += stride) {
     const float sc = __half2float(scales[i / G]);
     const unsigned int b = ((const unsigned char*)values)[i];
     if (VARIANCE) {
@@ -68,15 +69,14 @@ __global__ void __launch_bounds__(kThreads) dequantize_kernel(const void* __rest
 }
 
 template <int PDT, int ECC_BITS>
-__global__ void __launch_bounds__(kThreads) split_kernel(const float* __restrict__ theta, unsigned short* __restrict__ lp,
+__global__ void __launch_bounds__(kCodecThreads) split_kernel(const float* __restrict__ theta, unsigned short* __restrict__ lp,
                                                          void* __restrict__ ecc, unsigned long long n) {
-  const unsigned long long stride = (unsigned long long)gridDim.x * kThreads;
-  for (unsigned long long i = (unsigned long long)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
-    Hyp h;
-    h.flags = 0;
+  const unsigned long long stride = (unsigned long long)gridDim.x * kCodecThreads;
+  for (unsigned long long i = (unsigned long long)blockIdx.x * kCodecThreads + threadIdx.x; i < n; i += stride) {
     uint32_t nb;
-    int e;
-    store_form<PDT, ECC_BITS>(h, theta[i], 0u, nb, e);
+    int e = 0;
+    if constexpr (ECC_BITS != 0) fast::split<PDT, ECC_BITS>(theta[i], nb, e);
+    else nb = Lp<PDT>::from_f32(theta[i]);
     lp[i] = (unsigned short)nb;
     if constexpr (ECC_BITS == 16) ((short*)ecc)[i] = (short)e;
     if constexpr (ECC_BITS == 8) ((signed char*)ecc)[i] = (signed char)e;
@@ -84,20 +84,21 @@ __global__ void __launch_bounds__(kThreads) split_kernel(const float* __restrict
 }
 
 template <int PDT, int ECC_BITS>
-__global__ void __launch_bounds__(kThreads) reconstruct_kernel(const unsigned short* __restrict__ lp,
+__global__ void __launch_bounds__(kCodecThreads) reconstruct_kernel(const unsigned short* __restrict__ lp,
                                                                const void* __restrict__ ecc, float* __restrict__ theta,
                                                                unsigned long long n) {
-  const unsigned long long stride = (unsigned long long)gridDim.x * kThreads;
-  for (unsigned long long i = (unsigned long long)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+  const unsigned long long stride = (unsigned long long)gridDim.x * kCodecThreads;
+  for (unsigned long long i = (unsigned long long)blockIdx.x * kCodecThreads + threadIdx.x; i < n; i += stride) {
     int e = 0;
     if constexpr (ECC_BITS == 16) e = ((const short*)ecc)[i];
     if constexpr (ECC_BITS == 8) e = ((const signed char*)ecc)[i];
-    theta[i] = master_of<PDT, ECC_BITS>(lp[i], e);
+    if constexpr (ECC_BITS != 0) theta[i] = fast::reconstruct<PDT, ECC_BITS>(lp[i], e);
+    else theta[i] = Lp<PDT>::to_f32(lp[i]);
   }
 }
 
 static unsigned int stride_grid(unsigned long long n) {
-  unsigned long long b = (n + kThreads - 1) / kThreads;
+  unsigned long long b = (n + kCodecThreads - 1) / kCodecThreads;
   const unsigned long long cap = 148ull * 8ull * 4ull;
   return (unsigned int)(b < cap ? (b ? b : 1) : cap);
 }
@@ -118,7 +119,7 @@ static int quantize_entry(const float* x, void* values, void* scales, uint64_t n
   const unsigned long long tile = (unsigned long long)(kGenericTile / G) * G;
   const unsigned long long blocks = (n + tile - 1) / tile;
   if (blocks > 0x7FFFFFFFull) return fail(FO_ERR_TOO_LARGE, "%s: %llu elements exceed one launch", what, (unsigned long long)n);
-  quantize_kernel<VARIANCE><<<(unsigned int)blocks, kThreads, 0, (cudaStream_t)stream>>>(x, values, (__half*)scales, n, G, floor_mode);
+  quantize_kernel<VARIANCE><<<(unsigned int)blocks, kCodecThreads, 0, (cudaStream_t)stream>>>(x, values, (__half*)scales, n, G, floor_mode);
   return check_launch(what);
 }
 
@@ -128,7 +129,7 @@ static int dequantize_entry(const void* values, const void* scales, float* out, 
   if (n == 0) return FO_OK;
   if (values == nullptr || scales == nullptr || out == nullptr) return fail(FO_ERR_INVALID_ARG, "%s: null pointer", what);
   if (G < 1) return fail(FO_ERR_INVALID_ARG, "%s: group_size %d", what, G);
-  dequantize_kernel<VARIANCE><<<stride_grid(n), kThreads, 0, (cudaStream_t)stream>>>(values, (const __half*)scales, out, n, G);
+  dequantize_kernel<VARIANCE><<<stride_grid(n), kCodecThreads, 0, (cudaStream_t)stream>>>(values, (const __half*)scales, out, n, G);
   return check_launch(what);
 }
 
@@ -158,7 +159,7 @@ extern "C" int fo_split(const float* theta, void* lp, void* ecc, int32_t pdt, in
   if (theta == nullptr || lp == nullptr || (ecc_bits != 0 && ecc == nullptr)) return fail(FO_ERR_INVALID_ARG, "fo_split: null pointer");
 #define X(P, E)                                                                                                         \
   if (pdt == P && ecc_bits == E) {                                                                                      \
-    split_kernel<P, E><<<stride_grid(n), kThreads, 0, (cudaStream_t)stream>>>(theta, (unsigned short*)lp, ecc, n);       \
+    split_kernel<P, E><<<stride_grid(n), kCodecThreads, 0, (cudaStream_t)stream>>>(theta, (unsigned short*)lp, ecc, n);       \
     return check_launch("fo_split");                                                                                    \
   }
   FO_LP_COMBOS(X)
@@ -172,7 +173,7 @@ extern "C" int fo_reconstruct(const void* lp, const void* ecc, float* theta, int
   if (theta == nullptr || lp == nullptr || (ecc_bits != 0 && ecc == nullptr)) return fail(FO_ERR_INVALID_ARG, "fo_reconstruct: null pointer");
 #define X(P, E)                                                                                                         \
   if (pdt == P && ecc_bits == E) {                                                                                      \
-    reconstruct_kernel<P, E><<<stride_grid(n), kThreads, 0, (cudaStream_t)stream>>>((const unsigned short*)lp, ecc, theta, n); \
+    reconstruct_kernel<P, E><<<stride_grid(n), kCodecThreads, 0, (cudaStream_t)stream>>>((const unsigned short*)lp, ecc, theta, n); \
     return check_launch("fo_reconstruct");                                                                              \
   }
   FO_LP_COMBOS(X)

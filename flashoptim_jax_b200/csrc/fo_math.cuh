@@ -124,10 +124,38 @@ FO_DEVI float div_by_rcp(float a, float b, float y) {
   return __fmaf_rn(r, y, q0);
 }
 
+// RN(1/s) for s in [1e-30, 1e30]: MUFU.RCP and FO_RCP_STEPS correction steps, no range
+// checks.  Compared with the IEEE reciprocal over every float of that range by fo_selftest.
+#ifndef FO_RCP_STEPS
+#define FO_RCP_STEPS 1
+#endif
+template <int STEPS>
+FO_DEVI float rcp_steps(float s) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(s));
+#pragma unroll
+  for (int k = 0; k < STEPS; ++k) {
+    float e = __fmaf_rn(-s, y, 1.0f);
+    y = __fmaf_rn(e, y, y);
+  }
+  return y;
+}
+FO_DEVI float rcp_rn(float s) {
+#if FO_RCP_STEPS == 0
+  return __frcp_rn(s);
+#else
+  return rcp_steps<FO_RCP_STEPS>(s);
+#endif
+}
+
 // integer-valued x in [-MAX, MAX] divided by the ECC range
 template <int ECC_BITS>
+FO_DEVI float ecc_fraction_f(float x) {
+  return div_by_rcp(x, Ecc<ECC_BITS>::MAX, __uint_as_float(Ecc<ECC_BITS>::RCP_BITS));
+}
+template <int ECC_BITS>
 FO_DEVI float ecc_fraction(int ecc) {
-  return div_by_rcp((float)ecc, Ecc<ECC_BITS>::MAX, __uint_as_float(Ecc<ECC_BITS>::RCP_BITS));
+  return ecc_fraction_f<ECC_BITS>((float)ecc);
 }
 
 // 2^(log_half_ulp) as a float, from the exponent field of the 16-bit value.
@@ -149,6 +177,9 @@ FO_DEVI float reconstruct(uint32_t bits, int ecc) {
   return fadd(Lp<PDT>::to_f32(bits), err);
 }
 
+// sign(s)*floor(|s|+0.5) for |s| <= 32767, as an integer: trunc(s + copysign(0.5, s))
+FO_DEVI int round_half_away(float s) { return __float2int_rz(fadd(s, copysignf(0.5f, s))); }
+
 template <int PDT, int ECC_BITS>
 FO_DEVI void split(float theta, uint32_t& bits, int& ecc) {
   using L = Lp<PDT>;
@@ -164,15 +195,47 @@ FO_DEVI void split(float theta, uint32_t& bits, int& ecc) {
     en = fmul(fmul(err, __uint_as_float(254u << 23)), __uint_as_float((uint32_t)(field - 127) << 23));
   }
   float c = fminf(fmaxf(en, -1.0f), 1.0f);
-  float s = fmul(c, Ecc<ECC_BITS>::MAX);
-  // sign(s)*floor(|s|+0.5) == trunc(s + copysign(0.5, s))
-  ecc = __float2int_rz(fadd(s, copysignf(0.5f, s)));
+  ecc = round_half_away(fmul(c, Ecc<ECC_BITS>::MAX));
 }
 
-// sqrt through MUFU.RSQ and one FMA correction; values the approximation cannot take
-// (zero, tiny, huge, inf, nan) go to the IEEE instruction.
-FO_DEVI float sqrt_rn(float v) {
-  if (!(v >= 1.0e-30f && v <= 1.0e30f)) return v == 0.0f ? v : fsqrt(v);
+// ---- the same two conversions for values already known to be "ordinary" -------------------
+// Given the fp32 image lpf of a 16-bit value with |lpf| >= kOrdinaryMin<PDT>: 2^ls and 2^-ls
+// by exponent-field arithmetic.  fp16 has no small-value exception once the field is clamped
+// to the smallest normal half (zero and subnormal halves use the min normal exponent).
+template <int PDT>
+struct Ordinary;
+template <>
+struct Ordinary<FO_BF16> {
+  static constexpr float kMin = 3.0092655e-36f;  // 2^-118: below it 2^ls or 2^-ls is not a normal float
+  static FO_DEVI uint32_t ebits(float lpf) { return __float_as_uint(lpf) & 0x7F800000u; }
+  static FO_DEVI float ulp_half(uint32_t eb) { return __uint_as_float(eb - (8u << 23)); }
+  static FO_DEVI float ulp_half_inv(uint32_t eb) { return __uint_as_float((262u << 23) - eb); }
+};
+template <>
+struct Ordinary<FO_F16> {
+  static constexpr float kMin = 0.0f;
+  static FO_DEVI uint32_t ebits(float lpf) { return max(__float_as_uint(lpf) & 0x7F800000u, 113u << 23); }
+  static FO_DEVI float ulp_half(uint32_t eb) { return __uint_as_float(eb - (11u << 23)); }
+  static FO_DEVI float ulp_half_inv(uint32_t eb) { return __uint_as_float((265u << 23) - eb); }
+};
+
+template <int PDT, int ECC_BITS>
+FO_DEVI float reconstruct_ordinary(float lpf, float ecc_as_float) {
+  const uint32_t eb = Ordinary<PDT>::ebits(lpf);
+  return fadd(lpf, fmul(ecc_fraction_f<ECC_BITS>(ecc_as_float), Ordinary<PDT>::ulp_half(eb)));
+}
+// lpf is RN_lp(theta) already converted back to fp32
+template <int PDT, int ECC_BITS>
+FO_DEVI int ecc_ordinary(float theta, float lpf) {
+  const uint32_t eb = Ordinary<PDT>::ebits(lpf);
+  float en = fmul(fsub(theta, lpf), Ordinary<PDT>::ulp_half_inv(eb));
+  float a = fminf(fabsf(en), 1.0f);
+  float s = copysignf(fmul(a, Ecc<ECC_BITS>::MAX), en);
+  return round_half_away(s);
+}
+
+// sqrt through MUFU.RSQ and one FMA correction, for 1e-30 <= v < inf
+FO_DEVI float sqrt_core(float v) {
   float y;
   asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(v));
   float r = fmul(v, y);
@@ -180,20 +243,28 @@ FO_DEVI float sqrt_rn(float v) {
   float e = __fmaf_rn(-r, r, v);
   return __fmaf_rn(e, h, r);
 }
+FO_DEVI float sqrt_rn(float v) {
+  if (!(v >= 1.0e-30f)) return fsqrt(v);
+  return sqrt_core(v);
+}
 
-// code of the soft-sign transform: floor(127 * (2n / (1 + |n|)) + 0.5) for |n| <= 1
-FO_DEVI int softsign_code(float n) {
+// floor(y) for |y| < 2^22 as the low bits of a float: adding 1.5*2^23 rounding down leaves
+// 0x400000 + floor(y) in the mantissa, so the low byte is floor(y) in two's complement.
+FO_DEVI uint32_t floor_bits(float y) { return __float_as_uint(__fadd_rd(y, 12582912.0f)); }
+
+// soft-sign transform 2n / (1 + |n|) for |n| <= 1 through MUFU.RCP, one Newton step and a
+// residual correction; only the resulting int8 code has to match the IEEE division.
+FO_DEVI float softsign_t(float n) {
   float d = fadd(1.0f, fabsf(n));
   float a = fadd(n, n);
-  float y0;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y0) : "f"(d));
-  float e = __fmaf_rn(-d, y0, 1.0f);
-  float y = __fmaf_rn(e, y0, y0);
+  float y = rcp_steps<1>(d);
   float q0 = fmul(a, y);
   float r = __fmaf_rn(-d, q0, a);
-  float t = __fmaf_rn(r, y, q0);
-  return __float2int_rd(fadd(fmul(t, 127.0f), 0.5f));
+  return __fmaf_rn(r, y, q0);
 }
+// low byte = floor(127 t + 0.5) in two's complement
+FO_DEVI uint32_t softsign_code_bits(float n) { return floor_bits(fadd(fmul(softsign_t(n), 127.0f), 0.5f)); }
+FO_DEVI int softsign_code(float n) { return (int)(signed char)(softsign_code_bits(n) & 0xFFu); }
 
 // per-group quantizer state: the scale guard, its reciprocal and whether the shortcut is safe
 struct GroupScale {
@@ -202,27 +273,23 @@ struct GroupScale {
 };
 FO_DEVI GroupScale group_scale(float absmax, bool floor_mode) {
   GroupScale g;
-  g.safe = ieee::safe_scale(absmax, floor_mode);
-  g.tame = g.safe >= 1.0e-30f && g.safe <= 1.0e30f;
-  g.rcp = __frcp_rn(g.safe);
+  g.tame = absmax >= 1.0e-12f && absmax <= 1.0e30f;  // above both guards' thresholds: safe == absmax
+  g.safe = g.tame ? absmax : ieee::safe_scale(absmax, floor_mode);
+  g.rcp = g.tame ? rcp_rn(absmax) : 0.0f;
   return g;
 }
 FO_DEVI int quant_m(float x, const GroupScale& g) {
   if (!g.tame) return ieee::quant_m(x, g.safe);
   return softsign_code(div_by_rcp(x, g.safe, g.rcp));
 }
+FO_DEVI uint32_t quant_v_bits(float root, float safe, float rcp) {
+  return floor_bits(fadd(fmul(div_by_rcp(root, safe, rcp), 255.0f), 0.5f));
+}
 FO_DEVI int quant_v(float root, const GroupScale& g) {
   if (!g.tame) return ieee::quant_v(root, g.safe);
-  float t = div_by_rcp(root, g.safe, g.rcp);
-  return __float2int_rd(fadd(fmul(t, 255.0f), 0.5f));
+  return (int)(quant_v_bits(root, g.safe, g.rcp) & 0xFFu);
 }
 
 }  // namespace fast
-
-#ifdef FO_NAIVE_MATH
-namespace M = ieee;
-#else
-namespace M = fast;
-#endif
 
 }  // namespace fo

@@ -21,6 +21,7 @@ __global__ void selftest_sqrt(unsigned long long* out) {
   for (unsigned long long b = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; b < 0x7F800000ull; b += stride) {
     float v = __uint_as_float((uint32_t)b);
     bad += !same_float(fast::sqrt_rn(v), fsqrt(v));
+    if (v >= 1.0e-30f) bad += !same_float(fast::sqrt_core(v), fsqrt(v));
   }
   tally(bad, out);
 }
@@ -48,7 +49,11 @@ __global__ void selftest_reconstruct(unsigned long long* out) {
   for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     uint32_t bits = (uint32_t)(i / kEcc);
     int e = (int)(i % kEcc) - (int)(kEcc / 2);
-    bad += !same_float(fast::reconstruct<PDT, ECC_BITS>(bits, e), ieee::reconstruct<PDT, ECC_BITS>(bits, e));
+    const float want = ieee::reconstruct<PDT, ECC_BITS>(bits, e);
+    bad += !same_float(fast::reconstruct<PDT, ECC_BITS>(bits, e), want);
+    const float lpf = Lp<PDT>::to_f32(bits);
+    if (fabsf(lpf) >= fast::Ordinary<PDT>::kMin && fabsf(lpf) <= 3.0e38f)
+      bad += !same_float(fast::reconstruct_ordinary<PDT, ECC_BITS>(lpf, (float)e), want);
   }
   tally(bad, out);
 }
@@ -65,6 +70,13 @@ __global__ void selftest_split(unsigned long long* out) {
     fast::split<PDT, ECC_BITS>(theta, b0, e0);
     ieee::split<PDT, ECC_BITS>(theta, b1, e1);
     bad += (b0 != b1) || (e0 != e1);
+    const float lpf = Lp<PDT>::to_f32(b1);
+    if (fabsf(lpf) >= fast::Ordinary<PDT>::kMin && fabsf(lpf) <= 3.0e38f)
+      bad += fast::ecc_ordinary<PDT, ECC_BITS>(theta, lpf) != e1;
+    // the packed conversion the hot path uses must agree with the scalar one
+    float lo, hi;
+    unpack2<PDT>(pack2<PDT>(theta, -theta), lo, hi);
+    bad += !same_float(lo, lpf) || !same_float(hi, -lpf);
   }
   tally(bad, out);
 }
@@ -91,6 +103,10 @@ __global__ void selftest_group_div(unsigned long long pairs, unsigned long long*
     bad += fast::quant_m(x, gs) != ieee::quant_m(x, safe);
     bad += fast::quant_m(-x, gs) != ieee::quant_m(-x, safe);
     bad += fast::quant_v(x, gs) != ieee::quant_v(x, safe);
+    if (gs.tame) {
+      bad += (int)(signed char)(fast::softsign_code_bits(fast::div_by_rcp(x, safe, gs.rcp)) & 0xFFu) != ieee::quant_m(x, safe);
+      bad += !same_float(gs.rcp, __frcp_rn(safe));
+    }
     // Adam denominator: sqrt_bc2 in [2^-16, 2), eps in [1e-12, 1], root anywhere in [0, 1e30]
     float sq = __uint_as_float(((111u + r1 % 17u) << 23) | (r0 & 0x7FFFFFu));
     float eps = __uint_as_float(((87u + r3 % 41u) << 23) | (r2 & 0x7FFFFFu));
@@ -102,6 +118,24 @@ __global__ void selftest_group_div(unsigned long long pairs, unsigned long long*
     }
   }
   tally(bad, out);
+}
+
+// every float in [1e-30, 1e30]: reciprocal by MUFU.RCP + k correction steps vs the IEEE one.
+// out[0] counts mismatches of the variant the kernels use, out[1] of one step, out[2] of two.
+__global__ void selftest_rcp(unsigned long long* out) {
+  unsigned long long bad0 = 0, bad1 = 0, bad2 = 0;
+  const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+  const unsigned long long lo = __float_as_uint(1.0e-30f), hi = __float_as_uint(1.0e30f);
+  for (unsigned long long b = lo + (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; b <= hi; b += stride) {
+    const float s = __uint_as_float((uint32_t)b);
+    const float want = __frcp_rn(s);
+    bad0 += !same_float(fast::rcp_rn(s), want);
+    bad1 += !same_float(fast::rcp_steps<1>(s), want);
+    bad2 += !same_float(fast::rcp_steps<2>(s), want);
+  }
+  tally(bad0, out);
+  tally(bad1, out + 1);
+  tally(bad2, out + 2);
 }
 
 __global__ void selftest_code_tables(unsigned long long* out) {
@@ -127,9 +161,9 @@ extern "C" int fo_selftest(int32_t which, int64_t arg, uint64_t* mismatches, voi
   cudaStream_t s = (cudaStream_t)cuda_stream;
   unsigned long long* d = nullptr;
   // the only allocation in the library: a test-only counter, freed before returning
-  cudaError_t e = cudaMalloc(&d, sizeof(unsigned long long));
+  cudaError_t e = cudaMalloc(&d, 4 * sizeof(unsigned long long));
   if (e != cudaSuccess) return fail(FO_ERR_CUDA, "fo_selftest: %s", cudaGetErrorString(e));
-  cudaMemsetAsync(d, 0, sizeof(unsigned long long), s);
+  cudaMemsetAsync(d, 0, 4 * sizeof(unsigned long long), s);
   const int grid = 148 * 8, block = 256;
   int rc = FO_OK;
   switch (which) {
@@ -139,6 +173,7 @@ extern "C" int fo_selftest(int32_t which, int64_t arg, uint64_t* mismatches, voi
       selftest_group_div<<<grid, block, 0, s>>>((unsigned long long)(arg > 0 ? arg : 1) * 1000000ull, d);
       break;
     case FO_SELFTEST_CODE_TABLES: selftest_code_tables<<<64, block, 0, s>>>(d); break;
+    case FO_SELFTEST_RCP: selftest_rcp<<<grid, block, 0, s>>>(d); break;
     case FO_SELFTEST_RECONSTRUCT:
     case FO_SELFTEST_SPLIT: {
       const int pdt = (int)(arg / 100), eb = (int)(arg % 100);
@@ -159,10 +194,11 @@ extern "C" int fo_selftest(int32_t which, int64_t arg, uint64_t* mismatches, voi
   if (rc == FO_OK) {
     e = cudaGetLastError();
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
-    unsigned long long h = 0;
-    if (e == cudaSuccess) e = cudaMemcpy(&h, d, sizeof(h), cudaMemcpyDeviceToHost);
+    unsigned long long h[4] = {0, 0, 0, 0};
+    if (e == cudaSuccess) e = cudaMemcpy(h, d, sizeof(h), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) rc = fail(FO_ERR_CUDA, "fo_selftest: %s", cudaGetErrorString(e));
-    *mismatches = h;
+    // arg selects which counter of a multi-counter test is reported (FO_SELFTEST_RCP: 0 in use, 1 one step, 2 two steps)
+    *mismatches = (which == FO_SELFTEST_RCP && arg >= 0 && arg < 3) ? h[arg] : h[0];
   }
   cudaFree(d);
   return rc;

@@ -67,3 +67,9 @@ def test_selftest_rejects_unknown_ids():
     out = ctypes.c_uint64(0)
     assert _lib.lib().fo_selftest(99, 0, ctypes.byref(out), 0) != 0
     assert _lib.lib().fo_selftest(_lib.FO_SELFTEST_SPLIT, 7, ctypes.byref(out), 0) != 0
+
+
+def test_reciprocal_shortcut_matches_ieee_for_every_float_in_range():
+    from flashoptim_jax_b200 import _lib
+
+    assert _run(_lib.FO_SELFTEST_RCP, 0) == 0
