@@ -10,7 +10,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libflashoptim_b200.so")
+# FLASHOPTIM_B200_LIB names another build of the same library (e.g. one compiled with other tuning macros)
+LIB_PATH = os.environ.get("FLASHOPTIM_B200_LIB") or os.path.join(_HERE, "lib", "libflashoptim_b200.so")
 
 FO_OK = 0
 FO_F32, FO_BF16, FO_F16 = 0, 1, 2
@@ -19,7 +20,7 @@ FO_STATE_QUANT, FO_STATE_FULL, FO_STATE_NONE = 0, 1, 2
 FO_FLAG_DECOUPLED_WD, FO_FLAG_NESTEROV, FO_FLAG_LION_LERP, FO_FLAG_LP_DELTA, FO_FLAG_SCALE_FLOOR = 1, 2, 4, 8, 16
 FO_MAX_HYPERS = 16
 FO_SELFTEST_SQRT, FO_SELFTEST_SOFTSIGN, FO_SELFTEST_RECONSTRUCT, FO_SELFTEST_SPLIT = 0, 1, 2, 3
-FO_SELFTEST_GROUP_DIV, FO_SELFTEST_CODE_TABLES, FO_SELFTEST_RCP = 4, 5, 6
+FO_SELFTEST_GROUP_DIV, FO_SELFTEST_CODE_TABLES, FO_SELFTEST_RCP, FO_SELFTEST_PACKED = 4, 5, 6, 7
 
 EXPORTS = (
     "fo_step", "fo_quantize_momentum", "fo_dequantize_momentum", "fo_quantize_variance",

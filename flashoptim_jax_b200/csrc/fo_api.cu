@@ -125,6 +125,7 @@ extern "C" int fo_step(const FoStepDesc* d, void* cuda_stream) {
   for (uint32_t h = 0; h < d->n_hypers; ++h) p.hyper[h] = make_dev_hyper(d->hypers[h], d->opt);
   p.grad_dtype = d->grad_dtype;
   p.group_size = d->state == FO_STATE_QUANT ? d->group_size : 32;
+  p.one = 1.0f;
 
   int count = 0;
   unsigned long long blocks = 0;

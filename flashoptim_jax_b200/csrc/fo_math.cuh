@@ -206,7 +206,7 @@ template <int PDT>
 struct Ordinary;
 template <>
 struct Ordinary<FO_BF16> {
-  static constexpr float kMin = 3.0092655e-36f;  // 2^-118: below it 2^ls or 2^-ls is not a normal float
+  static constexpr float kMin = 7.8886091e-31f;  // 2^-100: below it 2^ls, 2^-ls or MAX*2^-ls stops being a normal float
   static FO_DEVI uint32_t ebits(float lpf) { return __float_as_uint(lpf) & 0x7F800000u; }
   static FO_DEVI float ulp_half(uint32_t eb) { return __uint_as_float(eb - (8u << 23)); }
   static FO_DEVI float ulp_half_inv(uint32_t eb) { return __uint_as_float((262u << 23) - eb); }
@@ -291,5 +291,165 @@ FO_DEVI int quant_v(float root, const GroupScale& g) {
 }
 
 }  // namespace fast
+
+// ===========================================================================================
+// fast2: the same shortcuts on pairs of elements with the sm_100 packed fp32x2 instructions
+// (add / mul / fma .f32x2: two independent IEEE operations per issue slot).  One pair is two
+// neighbouring elements of a leaf.  Every function here has a scalar twin above with the
+// same operation sequence per component, so results are bit-identical to fast:: and hence
+// to ieee::; fo_selftest sweeps these packed forms.
+namespace fast2 {
+
+using f2 = float2;
+FO_DEVI f2 mk(float a, float b) { return make_float2(a, b); }
+FO_DEVI f2 sp(float a) { return make_float2(a, a); }
+// Inline PTX with explicit rounding modifiers: an operation that names its rounding mode is
+// never merged into an fma.  (The __fmul2_rn / __fadd2_rn intrinsics were observed to be
+// contracted into fma.f32x2 even under -fmad=false, which changes last bits.)
+FO_DEVI unsigned long long as_b64(f2 a) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a.x), "f"(a.y));
+  return r;
+}
+FO_DEVI f2 as_f2(unsigned long long r) {
+  f2 a;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a.x), "=f"(a.y) : "l"(r));
+  return a;
+}
+FO_DEVI f2 mul2(f2 a, f2 b) {
+  unsigned long long d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(as_b64(a)), "l"(as_b64(b)));
+  return as_f2(d);
+}
+FO_DEVI f2 add2(f2 a, f2 b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(as_b64(a)), "l"(as_b64(b)));
+  return as_f2(d);
+}
+FO_DEVI f2 fma2(f2 a, f2 b, f2 c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(as_b64(a)), "l"(as_b64(b)), "l"(as_b64(c)));
+  return as_f2(d);
+}
+// x + y where x and/or y are themselves products.  The assembler was observed to contract
+// mul.rn.f32x2 followed by add.rn.f32x2 into one fma.f32x2 (and to simplify x*1 first), which
+// changes last bits.  Writing the sum as x*one + y with `one` a run-time 1.0f it cannot see
+// through keeps both roundings: a product of three factors is not an fma, and neither is an
+// fma whose addend is a product.  RN(x*1 + y) == RN(x + y).
+FO_DEVI f2 sum2(f2 x, f2 y, f2 one) { return fma2(x, one, y); }
+FO_DEVI f2 add2_rd(f2 a, f2 b) {
+  unsigned long long d;
+  asm("add.rm.f32x2 %0, %1, %2;" : "=l"(d) : "l"(as_b64(a)), "l"(as_b64(b)));
+  return as_f2(d);
+}
+
+FO_DEVI float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+FO_DEVI float rsqrt_approx(float x) {
+  float y;
+  asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// a / b given nb = -b and y = RN(1/b)
+FO_DEVI f2 div_by_rcp2(f2 a, f2 nb, f2 y) {
+  f2 q0 = mul2(a, y);
+  f2 r = fma2(nb, q0, a);
+  return fma2(r, y, q0);
+}
+
+// RN(1/d) per component for d in [1e-30, 1e30]; nd = -d
+FO_DEVI f2 rcp2(f2 d, f2 nd) {
+  f2 y0 = mk(rcp_approx(d.x), rcp_approx(d.y));
+  f2 e = fma2(nd, y0, sp(1.0f));
+  return fma2(e, y0, y0);
+}
+
+// RN(a/d) per component, proven: y = RN(1/d) (checked exhaustively), first correction
+// gives a faithful quotient, the second the correctly rounded one (Markstein).  Needs
+// d in [1e-30, 1e30], |a| in [2^-40, 2^60], |a/d| in [2^-110, 2^110].
+FO_DEVI f2 div2(f2 a, f2 d) {
+  f2 nd = mul2(d, sp(-1.0f));
+  f2 y = rcp2(d, nd);
+  f2 q = mul2(a, y);
+  f2 r = fma2(nd, q, a);
+  q = fma2(r, y, q);
+  r = fma2(nd, q, a);
+  return fma2(r, y, q);
+}
+
+// sqrt per component for 1e-30 <= v < inf
+FO_DEVI f2 sqrt_core2(f2 v) {
+  f2 y = mk(rsqrt_approx(v.x), rsqrt_approx(v.y));
+  f2 r = mul2(v, y);
+  f2 h = mul2(y, sp(0.5f));
+  f2 nr = mul2(r, sp(-1.0f));
+  f2 e = fma2(nr, r, v);
+  return fma2(e, h, r);
+}
+
+// power-of-two scales folded into the ECC constants: the fraction comes out pre-multiplied by
+// 2^-(MANT+1), so 2^log_half_ulp is just the exponent field of the stored value
+template <int PDT, int ECC_BITS>
+struct EccConst {
+  static constexpr float kFold = PDT == FO_BF16 ? 256.0f : 2048.0f;           // 2^(MANT+1)
+  static constexpr float kNegDiv = -(Ecc<ECC_BITS>::MAX * kFold);              // -(MAX * 2^(MANT+1)), exact
+  static FO_DEVI float rcp() { return __uint_as_float(Ecc<ECC_BITS>::RCP_BITS) * (1.0f / kFold); }  // RN(1/MAX) * 2^-(MANT+1), exact
+};
+template <int PDT>
+FO_DEVI uint32_t exp_field(float lpf) {
+  uint32_t eb = __float_as_uint(lpf) & 0x7F800000u;
+  if constexpr (PDT == FO_F16) eb = max(eb, 113u << 23);  // zero / subnormal halves use the min normal exponent
+  return eb;
+}
+// master weight from (stored value as fp32, ECC as fp32) for ordinary values (see fast::Ordinary)
+template <int PDT, int ECC_BITS>
+FO_DEVI f2 reconstruct_ordinary2(f2 lpf, f2 ef, f2 one) {
+  using K = EccConst<PDT, ECC_BITS>;
+  f2 fr = div_by_rcp2(ef, sp(K::kNegDiv), sp(K::rcp()));
+  f2 sc = mk(__uint_as_float(exp_field<PDT>(lpf.x)), __uint_as_float(exp_field<PDT>(lpf.y)));
+  return sum2(mul2(fr, sc), lpf, one);
+}
+// ECC of theta given lpf = RN_lp(theta) as fp32, ordinary values
+template <int PDT, int ECC_BITS>
+FO_DEVI void ecc_ordinary2(f2 theta, f2 lpf, int& e0, int& e1) {
+  // MAX * 2^-log_half_ulp as a float: exponent arithmetic on the bits of MAX
+  constexpr uint32_t kMaxBits = ECC_BITS == 8 ? 0x42FE0000u : 0x46FFFE00u;  // 127.0f, 32767.0f
+  constexpr uint32_t kBase = kMaxBits + ((PDT == FO_BF16 ? 262u - 127u : 265u - 127u) << 23);
+  f2 err = fma2(lpf, sp(-1.0f), theta);
+  f2 sc = mk(__uint_as_float(kBase - exp_field<PDT>(lpf.x)), __uint_as_float(kBase - exp_field<PDT>(lpf.y)));
+  f2 s = mul2(err, sc);  // clip(err * 2^-ls, -1, 1) * MAX == clip(err * 2^-ls * MAX, -MAX, MAX)
+  f2 a = mk(fminf(fabsf(s.x), Ecc<ECC_BITS>::MAX), fminf(fabsf(s.y), Ecc<ECC_BITS>::MAX));
+  f2 y = add2(a, sp(0.5f));
+  e0 = __float2int_rz(copysignf(y.x, s.x));
+  e1 = __float2int_rz(copysignf(y.y, s.y));
+}
+
+// bits whose low byte is floor(127 * 2n/(1+|n|) + 0.5), |n| <= 1
+FO_DEVI void softsign_code_bits2(f2 n, f2 one, uint32_t& c0, uint32_t& c1) {
+  f2 d = add2(mk(fabsf(n.x), fabsf(n.y)), sp(1.0f));
+  f2 nd = mul2(d, sp(-1.0f));
+  f2 y = rcp2(d, nd);
+  f2 q0 = mul2(n, y);
+  f2 r = fma2(nd, q0, n);
+  f2 q = fma2(r, y, q0);                       // n/(1+|n|); 2n/(1+|n|) * 127 == q * 254 exactly
+  f2 c = sum2(mul2(q, sp(254.0f)), sp(0.5f), one);
+  f2 fl = add2_rd(c, sp(12582912.0f));
+  c0 = __float_as_uint(fl.x);
+  c1 = __float_as_uint(fl.y);
+}
+// bits whose low byte is floor(255 * root/av + 0.5); nav = -av, rcp = RN(1/av)
+FO_DEVI void quant_v_bits2(f2 root, f2 nav, f2 rcp, f2 one, uint32_t& c0, uint32_t& c1) {
+  f2 t = div_by_rcp2(root, nav, rcp);
+  f2 c = sum2(mul2(t, sp(255.0f)), sp(0.5f), one);
+  f2 fl = add2_rd(c, sp(12582912.0f));
+  c0 = __float_as_uint(fl.x);
+  c1 = __float_as_uint(fl.y);
+}
+
+}  // namespace fast2
 
 }  // namespace fo

@@ -15,19 +15,24 @@ FO_DEVI void tally(unsigned long long bad, unsigned long long* out) {
 }
 
 // every non-negative finite fp32, zero and subnormals included
-__global__ void selftest_sqrt(unsigned long long* out) {
+__global__ void selftest_sqrt(const float one, unsigned long long* out) {
   unsigned long long bad = 0;
   const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
   for (unsigned long long b = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; b < 0x7F800000ull; b += stride) {
     float v = __uint_as_float((uint32_t)b);
     bad += !same_float(fast::sqrt_rn(v), fsqrt(v));
-    if (v >= 1.0e-30f) bad += !same_float(fast::sqrt_core(v), fsqrt(v));
+    if (v >= 1.0e-30f) {
+      bad += !same_float(fast::sqrt_core(v), fsqrt(v));
+      const float w = __uint_as_float(0x7F7FFFFFu - (uint32_t)b + __float_as_uint(1.0e-30f));  // a second, unrelated lane
+      const float2 r2 = fast2::sqrt_core2(make_float2(v, w));
+      bad += !same_float(r2.x, fsqrt(v)) || !same_float(r2.y, fsqrt(w));
+    }
   }
   tally(bad, out);
 }
 
 // every fp32 with |n| <= 1: the int8 code through the shortcut division vs the IEEE one
-__global__ void selftest_softsign(unsigned long long* out) {
+__global__ void selftest_softsign(const float one, unsigned long long* out) {
   unsigned long long bad = 0;
   const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
   for (unsigned long long b = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; b <= 0x3F800000ull; b += stride) {
@@ -35,13 +40,17 @@ __global__ void selftest_softsign(unsigned long long* out) {
     for (int s = 0; s < 2; ++s) {
       float n = __uint_as_float((uint32_t)b | (s ? 0x80000000u : 0u));
       bad += fast::softsign_code(n) != ieee::quant_m(n, 1.0f);
+      uint32_t c0, c1;
+      fast2::softsign_code_bits2(make_float2(n, -n), fast2::sp(one), c0, c1);
+      bad += (int)(signed char)(c0 & 0xFFu) != ieee::quant_m(n, 1.0f);
+      bad += (int)(signed char)(c1 & 0xFFu) != ieee::quant_m(-n, 1.0f);
     }
   }
   tally(bad, out);
 }
 
 template <int PDT, int ECC_BITS>
-__global__ void selftest_reconstruct(unsigned long long* out) {
+__global__ void selftest_reconstruct(const float one, unsigned long long* out) {
   unsigned long long bad = 0;
   constexpr unsigned long long kEcc = 1ull << ECC_BITS;
   const unsigned long long total = 65536ull * kEcc;
@@ -53,13 +62,19 @@ __global__ void selftest_reconstruct(unsigned long long* out) {
     bad += !same_float(fast::reconstruct<PDT, ECC_BITS>(bits, e), want);
     const float lpf = Lp<PDT>::to_f32(bits);
     if (fabsf(lpf) >= fast::Ordinary<PDT>::kMin && fabsf(lpf) <= 3.0e38f)
+    {
       bad += !same_float(fast::reconstruct_ordinary<PDT, ECC_BITS>(lpf, (float)e), want);
+      const int en = (e == -(1 << (ECC_BITS - 1))) ? e : -e;  // the most negative pattern has no negation
+      const float2 t2 = fast2::reconstruct_ordinary2<PDT, ECC_BITS>(make_float2(lpf, -lpf), make_float2((float)e, (float)en), fast2::sp(one));
+      const float want_neg = ieee::reconstruct<PDT, ECC_BITS>(bits ^ 0x8000u, en);
+      bad += !same_float(t2.x, want) || !same_float(t2.y, want_neg);
+    }
   }
   tally(bad, out);
 }
 
 template <int PDT, int ECC_BITS>
-__global__ void selftest_split(unsigned long long* out) {
+__global__ void selftest_split(const float one, unsigned long long* out) {
   unsigned long long bad = 0;
   const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
   for (unsigned long long b = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; b < (1ull << 32); b += stride) {
@@ -72,7 +87,12 @@ __global__ void selftest_split(unsigned long long* out) {
     bad += (b0 != b1) || (e0 != e1);
     const float lpf = Lp<PDT>::to_f32(b1);
     if (fabsf(lpf) >= fast::Ordinary<PDT>::kMin && fabsf(lpf) <= 3.0e38f)
+    {
       bad += fast::ecc_ordinary<PDT, ECC_BITS>(theta, lpf) != e1;
+      int p0, p1;
+      fast2::ecc_ordinary2<PDT, ECC_BITS>(make_float2(theta, -theta), make_float2(lpf, -lpf), p0, p1);
+      bad += (p0 != e1) || (p1 != -e1);
+    }
     // the packed conversion the hot path uses must agree with the scalar one
     float lo, hi;
     unpack2<PDT>(pack2<PDT>(theta, -theta), lo, hi);
@@ -88,7 +108,7 @@ FO_DEVI uint32_t mix(uint64_t x) {
 
 // random (value, group scale) pairs with |value| <= scale: codes through the reciprocal
 // shortcut vs the IEEE divisions; and the Adam denominator sqrt(nu)/sqrt(bc2) + eps.
-__global__ void selftest_group_div(unsigned long long pairs, unsigned long long* out) {
+__global__ void selftest_group_div(const float one, unsigned long long pairs, unsigned long long* out) {
   unsigned long long bad = 0;
   const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
   for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < pairs; i += stride) {
@@ -104,6 +124,13 @@ __global__ void selftest_group_div(unsigned long long pairs, unsigned long long*
     bad += fast::quant_m(-x, gs) != ieee::quant_m(-x, safe);
     bad += fast::quant_v(x, gs) != ieee::quant_v(x, safe);
     if (gs.tame) {
+      uint32_t c0, c1;
+      fast2::softsign_code_bits2(fast2::div_by_rcp2(make_float2(x, -x), fast2::sp(-safe), fast2::sp(gs.rcp)), fast2::sp(one), c0, c1);
+      bad += (int)(signed char)(c0 & 0xFFu) != ieee::quant_m(x, safe);
+      bad += (int)(signed char)(c1 & 0xFFu) != ieee::quant_m(-x, safe);
+      fast2::quant_v_bits2(make_float2(x, safe), fast2::sp(-safe), fast2::sp(gs.rcp), fast2::sp(one), c0, c1);
+      bad += (int)(c0 & 0xFFu) != ieee::quant_v(x, safe);
+      bad += (int)(c1 & 0xFFu) != 255;
       bad += (int)(signed char)(fast::softsign_code_bits(fast::div_by_rcp(x, safe, gs.rcp)) & 0xFFu) != ieee::quant_m(x, safe);
       bad += !same_float(gs.rcp, __frcp_rn(safe));
     }
@@ -111,6 +138,14 @@ __global__ void selftest_group_div(unsigned long long pairs, unsigned long long*
     float sq = __uint_as_float(((111u + r1 % 17u) << 23) | (r0 & 0x7FFFFFu));
     float eps = __uint_as_float(((87u + r3 % 41u) << 23) | (r2 & 0x7FFFFFu));
     float root = (r0 & 4u) ? x : __uint_as_float(((r2 >> 3) % 227u << 23) | (r1 & 0x7FFFFFu));
+    {
+      // the update division: numerator magnitude in [2^-40, 2^60], denominator in [1e-12, 1e20]
+      const float num = __uint_as_float((r3 & 0x80000000u) | ((87u + r1 % 101u) << 23) | (r2 & 0x7FFFFFu));
+      const float den = __uint_as_float(((88u + r0 % 105u) << 23) | (r3 & 0x7FFFFFu));
+      const float den2 = __uint_as_float(((88u + r2 % 105u) << 23) | (r1 & 0x7FFFFFu));
+      const float2 q = fast2::div2(make_float2(num, -num), make_float2(den, den2));
+      bad += !same_float(q.x, fdiv(num, den)) || !same_float(q.y, fdiv(-num, den2));
+    }
     if (adam_is_tame(eps, sq)) {
       float a = fadd(fast::div_by_rcp(root, sq, __frcp_rn(sq)), eps);
       float b = fadd(fdiv(root, sq), eps);
@@ -136,6 +171,30 @@ __global__ void selftest_rcp(unsigned long long* out) {
   tally(bad0, out);
   tally(bad1, out + 1);
   tally(bad2, out + 2);
+}
+
+// Are "product then sum" sequences of packed operations kept as two roundings?
+// out[0]: x*1 + y form (the one the kernels use), out[1]: plain add of a product.
+__global__ void selftest_packed(const float one, unsigned long long pairs, unsigned long long* out) {
+  unsigned long long bad0 = 0, bad1 = 0;
+  const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+  for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < pairs; i += stride) {
+    float x[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t r = mix(i * 8 + k);
+      x[k] = __uint_as_float((r & 0x80000000u) | ((100u + (r >> 8) % 40u) << 23) | (mix(i * 8 + k + 77) & 0x7FFFFFu));
+    }
+    using namespace fast2;
+    const f2 a = mk(x[0], x[1]), b = mk(x[2], x[3]), c = mk(x[4], x[5]), d = mk(x[6], x[7]);
+    const float w0 = fadd(fmul(a.x, b.x), fmul(c.x, d.x)), w1 = fadd(fmul(a.y, b.y), fmul(c.y, d.y));
+    const f2 s0 = sum2(mul2(a, b), mul2(c, d), sp(one));
+    const f2 s1 = add2(mul2(a, b), mul2(c, d));
+    bad0 += !same_float(s0.x, w0) || !same_float(s0.y, w1);
+    bad1 += !same_float(s1.x, w0) || !same_float(s1.y, w1);
+  }
+  tally(bad0, out);
+  tally(bad1, out + 1);
 }
 
 __global__ void selftest_code_tables(unsigned long long* out) {
@@ -165,15 +224,18 @@ extern "C" int fo_selftest(int32_t which, int64_t arg, uint64_t* mismatches, voi
   if (e != cudaSuccess) return fail(FO_ERR_CUDA, "fo_selftest: %s", cudaGetErrorString(e));
   cudaMemsetAsync(d, 0, 4 * sizeof(unsigned long long), s);
   const int grid = 148 * 8, block = 256;
+  volatile float one_src = 1.0f;  // a run-time 1.0f, as the step kernels receive it
+  const float one = one_src;
   int rc = FO_OK;
   switch (which) {
-    case FO_SELFTEST_SQRT: selftest_sqrt<<<grid, block, 0, s>>>(d); break;
-    case FO_SELFTEST_SOFTSIGN: selftest_softsign<<<grid, block, 0, s>>>(d); break;
+    case FO_SELFTEST_SQRT: selftest_sqrt<<<grid, block, 0, s>>>(one, d); break;
+    case FO_SELFTEST_SOFTSIGN: selftest_softsign<<<grid, block, 0, s>>>(one, d); break;
     case FO_SELFTEST_GROUP_DIV:
-      selftest_group_div<<<grid, block, 0, s>>>((unsigned long long)(arg > 0 ? arg : 1) * 1000000ull, d);
+      selftest_group_div<<<grid, block, 0, s>>>(one, (unsigned long long)(arg > 0 ? arg : 1) * 1000000ull, d);
       break;
     case FO_SELFTEST_CODE_TABLES: selftest_code_tables<<<64, block, 0, s>>>(d); break;
     case FO_SELFTEST_RCP: selftest_rcp<<<grid, block, 0, s>>>(d); break;
+    case FO_SELFTEST_PACKED: selftest_packed<<<grid, block, 0, s>>>(one, 1000000000ull, d); break;
     case FO_SELFTEST_RECONSTRUCT:
     case FO_SELFTEST_SPLIT: {
       const int pdt = (int)(arg / 100), eb = (int)(arg % 100);
@@ -181,8 +243,8 @@ extern "C" int fo_selftest(int32_t which, int64_t arg, uint64_t* mismatches, voi
 #define X(P, E)                                                                              \
   if (pdt == P && eb == E) {                                                                 \
     ok = true;                                                                               \
-    if (which == FO_SELFTEST_RECONSTRUCT) selftest_reconstruct<P, E><<<grid, block, 0, s>>>(d); \
-    else selftest_split<P, E><<<grid, block, 0, s>>>(d);                                     \
+    if (which == FO_SELFTEST_RECONSTRUCT) selftest_reconstruct<P, E><<<grid, block, 0, s>>>(one, d); \
+    else selftest_split<P, E><<<grid, block, 0, s>>>(one, d);                                     \
   }
       X(FO_BF16, 8) X(FO_BF16, 16) X(FO_F16, 8) X(FO_F16, 16)
 #undef X
@@ -198,7 +260,7 @@ extern "C" int fo_selftest(int32_t which, int64_t arg, uint64_t* mismatches, voi
     if (e == cudaSuccess) e = cudaMemcpy(h, d, sizeof(h), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) rc = fail(FO_ERR_CUDA, "fo_selftest: %s", cudaGetErrorString(e));
     // arg selects which counter of a multi-counter test is reported (FO_SELFTEST_RCP: 0 in use, 1 one step, 2 two steps)
-    *mismatches = (which == FO_SELFTEST_RCP && arg >= 0 && arg < 3) ? h[arg] : h[0];
+    *mismatches = ((which == FO_SELFTEST_RCP || which == FO_SELFTEST_PACKED) && arg >= 0 && arg < 3) ? h[arg] : h[0];
   }
   cudaFree(d);
   return rc;

@@ -29,13 +29,19 @@
 
 namespace fo {
 
+// Tuning (measured on B200): 256-thread blocks; Adam's working set wants 128 registers
+// (2 resident blocks per SM), Lion / SGD fit 3 blocks.
 #ifndef FO_THREADS
 #define FO_THREADS 256
 #endif
-#ifndef FO_MIN_BLOCKS
-#define FO_MIN_BLOCKS 3
+#ifndef FO_MIN_BLOCKS_ADAM
+#define FO_MIN_BLOCKS_ADAM 2
+#endif
+#ifndef FO_MIN_BLOCKS_MOMENTUM
+#define FO_MIN_BLOCKS_MOMENTUM 3
 #endif
 constexpr int kThreads = FO_THREADS;
+constexpr int min_blocks(int opt) { return opt == FO_OPT_ADAM ? FO_MIN_BLOCKS_ADAM : FO_MIN_BLOCKS_MOMENTUM; }
 constexpr int kPiece = 8;
 constexpr int kChunk = kThreads * kPiece;      // elements per chunk
 constexpr int kMaxLeaves = 320;                // leaves per launch (kernel-parameter table)
@@ -70,7 +76,7 @@ struct StepParams {
   int32_t n_leaves;
   int32_t grad_dtype;
   int32_t group_size;
-  int32_t pad;
+  float one;  // 1.0f the compiler cannot see through (see fast2::sum2)
 };
 
 // true when the quotient sqrt(nu)/sqrt(bc2) may be formed as div_by_rcp without changing
@@ -309,17 +315,6 @@ __device__ __noinline__ int ecc_slow(float theta) {
   return e;
 }
 
-FO_DEVI float min8(const float (&x)[8]) {
-  return fminf(fminf(fminf(x[0], x[1]), fminf(x[2], x[3])), fminf(fminf(x[4], x[5]), fminf(x[6], x[7])));
-}
-FO_DEVI float minabs8(const float (&x)[8]) {
-  return fminf(fminf(fminf(fabsf(x[0]), fabsf(x[1])), fminf(fabsf(x[2]), fabsf(x[3]))),
-               fminf(fminf(fabsf(x[4]), fabsf(x[5])), fminf(fabsf(x[6]), fabsf(x[7]))));
-}
-FO_DEVI float maxabs8(const float (&x)[8]) {
-  return fmaxf(fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3]))),
-               fmaxf(fmaxf(fabsf(x[4]), fabsf(x[5])), fmaxf(fabsf(x[6]), fabsf(x[7]))));
-}
 FO_DEVI float group_max(float a) {
   a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, 1));
   return fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, 2));
@@ -330,114 +325,181 @@ FO_DEVI uint32_t pack_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
 }
 FO_DEVI uint32_t pack_halves(uint32_t lo, uint32_t hi) { return __byte_perm(lo, hi, 0x5410); }
 
+// 3-input min / max (one instruction on sm_100)
+FO_DEVI float min3(float a, float b, float c) {
+  float d;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+FO_DEVI float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// what one thread loads for one chunk: its 8 elements of every stream, still packed
 template <int OPT, int PDT, int ECC_BITS, int STATE>
-FO_DEVI void hot_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const unsigned long long base,
-                       const float* lut_m, const float* lut_v) {
-  const unsigned long long i0 = base + (unsigned long long)threadIdx.x * kPiece;
-  const unsigned long long gi = i0 >> 5;
+struct Raw {
+  uint4 g0, g1;        // grad: 8 x 16-bit in g0, or 8 x fp32 in g0,g1
+  uint4 p0, p1;        // param: 8 x 16-bit in p0, or 8 x fp32 in p0,p1
+  uint4 e;             // ECC: 8 x int16 in e, or 8 x int8 in e.x,e.y
+  uint2 mq, vq;        // codes
+  __half msc, vsc;     // group scales
+  uint4 m0, m1, v0, v1;  // fp32 moments (FULL)
+};
 
-  // ---- loads (all issued before the first use) ----------------------------------------------
-  uint4 pw = make_uint4(0, 0, 0, 0), ew4 = make_uint4(0, 0, 0, 0);
-  uint2 ew2 = make_uint2(0, 0), mq = make_uint2(0, 0), vq = make_uint2(0, 0);
-  float4 fa[2], ma[2], va[2];
-  float msc = 0.0f, vsc = 0.0f;
+template <int OPT, int PDT, int ECC_BITS, int STATE>
+FO_DEVI void hot_load(const DevLeaf& L, const int gdt, const unsigned long long i0, Raw<OPT, PDT, ECC_BITS, STATE>& r) {
   if constexpr (PDT == FO_F32) {
-    fa[0] = __ldcs((const float4*)((const float*)L.param + i0));
-    fa[1] = __ldcs((const float4*)((const float*)L.param + i0) + 1);
+    r.p0 = __ldcs((const uint4*)((const float*)L.param + i0));
+    r.p1 = __ldcs((const uint4*)((const float*)L.param + i0) + 1);
   } else {
-    pw = __ldcs((const uint4*)((const unsigned short*)L.param + i0));
+    r.p0 = __ldcs((const uint4*)((const unsigned short*)L.param + i0));
   }
-  if constexpr (ECC_BITS == 16) ew4 = __ldcs((const uint4*)((const short*)L.ecc + i0));
-  if constexpr (ECC_BITS == 8) ew2 = __ldcs((const uint2*)((const signed char*)L.ecc + i0));
+  if constexpr (ECC_BITS == 16) r.e = __ldcs((const uint4*)((const short*)L.ecc + i0));
+  if constexpr (ECC_BITS == 8) {
+    const uint2 t = __ldcs((const uint2*)((const signed char*)L.ecc + i0));
+    r.e.x = t.x; r.e.y = t.y;
+  }
   if constexpr (STATE == FO_STATE_QUANT) {
-    mq = __ldcs((const uint2*)((const unsigned char*)L.mu + i0));
-    msc = __half2float(((const __half*)L.mu_scales)[gi]);
+    r.mq = __ldcs((const uint2*)((const unsigned char*)L.mu + i0));
+    r.msc = ((const __half*)L.mu_scales)[i0 >> 5];
     if constexpr (OPT == FO_OPT_ADAM) {
-      vq = __ldcs((const uint2*)((const unsigned char*)L.nu + i0));
-      vsc = __half2float(((const __half*)L.nu_scales)[gi]);
+      r.vq = __ldcs((const uint2*)((const unsigned char*)L.nu + i0));
+      r.vsc = ((const __half*)L.nu_scales)[i0 >> 5];
     }
   } else if constexpr (STATE == FO_STATE_FULL) {
-    ma[0] = __ldcs((const float4*)((const float*)L.mu + i0));
-    ma[1] = __ldcs((const float4*)((const float*)L.mu + i0) + 1);
+    r.m0 = __ldcs((const uint4*)((const float*)L.mu + i0));
+    r.m1 = __ldcs((const uint4*)((const float*)L.mu + i0) + 1);
     if constexpr (OPT == FO_OPT_ADAM) {
-      va[0] = __ldcs((const float4*)((const float*)L.nu + i0));
-      va[1] = __ldcs((const float4*)((const float*)L.nu + i0) + 1);
+      r.v0 = __ldcs((const uint4*)((const float*)L.nu + i0));
+      r.v1 = __ldcs((const uint4*)((const float*)L.nu + i0) + 1);
     }
   }
-  float g[8];
   if (gdt == FO_F32) {
-    const float4 a = __ldcs((const float4*)((const float*)L.grad + i0));
-    const float4 b = __ldcs((const float4*)((const float*)L.grad + i0) + 1);
-    g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; g[4] = b.x; g[5] = b.y; g[6] = b.z; g[7] = b.w;
+    r.g0 = __ldcs((const uint4*)((const float*)L.grad + i0));
+    r.g1 = __ldcs((const uint4*)((const float*)L.grad + i0) + 1);
   } else {
-    const uint4 w = __ldcs((const uint4*)((const unsigned short*)L.grad + i0));
-    if (gdt == FO_BF16) {
-      unpack2<FO_BF16>(w.x, g[0], g[1]); unpack2<FO_BF16>(w.y, g[2], g[3]);
-      unpack2<FO_BF16>(w.z, g[4], g[5]); unpack2<FO_BF16>(w.w, g[6], g[7]);
-    } else {
-      unpack2<FO_F16>(w.x, g[0], g[1]); unpack2<FO_F16>(w.y, g[2], g[3]);
-      unpack2<FO_F16>(w.z, g[4], g[5]); unpack2<FO_F16>(w.w, g[6], g[7]);
-    }
+    r.g0 = __ldcs((const uint4*)((const unsigned short*)L.grad + i0));
   }
+}
 
-  // ---- master weight ---------------------------------------------------------------------------
-  float theta[8], old_lp[8];
+// what survives of a chunk's loads once they are unpacked: fp32 pairs ready for the update
+// (pair k holds elements 2k and 2k+1 of the thread's piece)
+struct Unpacked {
+  float2 g[4];
+  float2 old_lp[4];   // stored param as fp32
+  float2 theta[4];    // master weight
+  float2 m[4], v[4];
+};
+
+FO_DEVI void pairs_of(const uint4& a, const uint4& b, float2 (&o)[4]) {
+  o[0] = make_float2(__uint_as_float(a.x), __uint_as_float(a.y));
+  o[1] = make_float2(__uint_as_float(a.z), __uint_as_float(a.w));
+  o[2] = make_float2(__uint_as_float(b.x), __uint_as_float(b.y));
+  o[3] = make_float2(__uint_as_float(b.z), __uint_as_float(b.w));
+}
+template <int DT>
+FO_DEVI void pairs_of16(const uint4& w, float2 (&o)[4]) {
+  unpack2<DT>(w.x, o[0].x, o[0].y); unpack2<DT>(w.y, o[1].x, o[1].y);
+  unpack2<DT>(w.z, o[2].x, o[2].y); unpack2<DT>(w.w, o[3].x, o[3].y);
+}
+FO_DEVI float min8(const float2 (&x)[4]) {
+  return min3(min3(x[0].x, x[0].y, x[1].x), min3(x[1].y, x[2].x, x[2].y), fminf(x[3].x, x[3].y));
+}
+FO_DEVI float max8(const float2 (&x)[4]) {
+  return max3(max3(x[0].x, x[0].y, x[1].x), max3(x[1].y, x[2].x, x[2].y), fmaxf(x[3].x, x[3].y));
+}
+FO_DEVI float minabs8(const float2 (&x)[4]) {
+  return min3(min3(fabsf(x[0].x), fabsf(x[0].y), fabsf(x[1].x)), min3(fabsf(x[1].y), fabsf(x[2].x), fabsf(x[2].y)),
+              fminf(fabsf(x[3].x), fabsf(x[3].y)));
+}
+FO_DEVI float maxabs8(const float2 (&x)[4]) {
+  return max3(max3(fabsf(x[0].x), fabsf(x[0].y), fabsf(x[1].x)), max3(fabsf(x[1].y), fabsf(x[2].x), fabsf(x[2].y)),
+              fmaxf(fabsf(x[3].x), fabsf(x[3].y)));
+}
+// byte k of a word as an index
+FO_DEVI uint32_t byte_of(uint32_t w, int k) { return __byte_perm(w, 0u, 0x4440u | (uint32_t)k); }
+
+template <int OPT, int PDT, int ECC_BITS, int STATE>
+FO_DEVI void hot_unpack(const Raw<OPT, PDT, ECC_BITS, STATE>& r, const int gdt, const float* lut_m, const float* lut_v,
+                        const float one, Unpacked& u) {
+  using namespace fast2;
+  const float2 one2 = sp(one);
+  if (gdt == FO_F32) pairs_of(r.g0, r.g1, u.g);
+  else if (gdt == FO_BF16) pairs_of16<FO_BF16>(r.g0, u.g);
+  else pairs_of16<FO_F16>(r.g0, u.g);
+
   if constexpr (PDT == FO_F32) {
-    theta[0] = fa[0].x; theta[1] = fa[0].y; theta[2] = fa[0].z; theta[3] = fa[0].w;
-    theta[4] = fa[1].x; theta[5] = fa[1].y; theta[6] = fa[1].z; theta[7] = fa[1].w;
+    pairs_of(r.p0, r.p1, u.theta);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) old_lp[j] = theta[j];
+    for (int k = 0; k < 4; ++k) u.old_lp[k] = u.theta[k];
   } else {
-    unpack2<PDT>(pw.x, old_lp[0], old_lp[1]); unpack2<PDT>(pw.y, old_lp[2], old_lp[3]);
-    unpack2<PDT>(pw.z, old_lp[4], old_lp[5]); unpack2<PDT>(pw.w, old_lp[6], old_lp[7]);
+    pairs_of16<PDT>(r.p0, u.old_lp);
     if constexpr (ECC_BITS == 0) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) theta[j] = old_lp[j];
+      for (int k = 0; k < 4; ++k) u.theta[k] = u.old_lp[k];
     } else {
       int e[8];
       if constexpr (ECC_BITS == 16) {
-        const uint32_t w[4] = {ew4.x, ew4.y, ew4.z, ew4.w};
+        const uint32_t w[4] = {r.e.x, r.e.y, r.e.z, r.e.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) { e[2 * k] = (int)(short)(w[k] & 0xFFFFu); e[2 * k + 1] = (int)w[k] >> 16; }
       } else {
-        const uint32_t w[2] = {ew2.x, ew2.y};
+        const uint32_t w[2] = {r.e.x, r.e.y};
 #pragma unroll
         for (int k = 0; k < 8; ++k) e[k] = (int)(signed char)((w[k >> 2] >> (8 * (k & 3))) & 0xFFu);
       }
       bool ordinary = true;
-      if constexpr (PDT == FO_BF16) ordinary = minabs8(old_lp) >= fast::Ordinary<PDT>::kMin;
+      if constexpr (PDT == FO_BF16) ordinary = minabs8(u.old_lp) >= fast::Ordinary<PDT>::kMin;
       if (ordinary) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) theta[j] = fast::reconstruct_ordinary<PDT, ECC_BITS>(old_lp[j], (float)e[j]);
+        for (int k = 0; k < 4; ++k)
+          u.theta[k] = reconstruct_ordinary2<PDT, ECC_BITS>(u.old_lp[k], mk((float)e[2 * k], (float)e[2 * k + 1]), one2);
       } else {
-        const uint32_t w[4] = {pw.x, pw.y, pw.z, pw.w};
+        const uint32_t w[4] = {r.p0.x, r.p0.y, r.p0.z, r.p0.w};
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          theta[j] = reconstruct_slow<PDT, ECC_BITS>((w[j >> 1] >> (16 * (j & 1))) & 0xFFFFu, e[j]);
+        for (int k = 0; k < 4; ++k) {
+          u.theta[k].x = reconstruct_slow<PDT, ECC_BITS>(w[k] & 0xFFFFu, e[2 * k]);
+          u.theta[k].y = reconstruct_slow<PDT, ECC_BITS>(w[k] >> 16, e[2 * k + 1]);
+        }
       }
     }
   }
 
-  // ---- moments -----------------------------------------------------------------------------------
-  float m[8], v[8], root[8];
   if constexpr (STATE == FO_STATE_QUANT) {
-    const uint32_t mw[2] = {mq.x, mq.y};
+    const float2 msc = sp(__half2float(r.msc));
+    const uint32_t mw[2] = {r.mq.x, r.mq.y};
 #pragma unroll
-    for (int j = 0; j < 8; ++j) m[j] = fmul(lut_m[(mw[j >> 2] >> (8 * (j & 3))) & 0xFFu], msc);   // quantization.py:52-55
+    for (int k = 0; k < 4; ++k)  // quantization.py:52-55
+      u.m[k] = mul2(mk(lut_m[byte_of(mw[k >> 1], 2 * (k & 1))], lut_m[byte_of(mw[k >> 1], 2 * (k & 1) + 1)]), msc);
     if constexpr (OPT == FO_OPT_ADAM) {
-      const uint32_t vw[2] = {vq.x, vq.y};
+      const float2 vsc = sp(__half2float(r.vsc));
+      const uint32_t vw[2] = {r.vq.x, r.vq.y};
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float s = fmul(lut_v[(vw[j >> 2] >> (8 * (j & 3))) & 0xFFu], vsc);                   // quantization.py:74-77
-        v[j] = fmul(s, s);
+      for (int k = 0; k < 4; ++k) {  // quantization.py:74-77
+        const float2 s = mul2(mk(lut_v[byte_of(vw[k >> 1], 2 * (k & 1))], lut_v[byte_of(vw[k >> 1], 2 * (k & 1) + 1)]), vsc);
+        u.v[k] = mul2(s, s);
       }
     }
   } else if constexpr (STATE == FO_STATE_FULL) {
-    m[0] = ma[0].x; m[1] = ma[0].y; m[2] = ma[0].z; m[3] = ma[0].w; m[4] = ma[1].x; m[5] = ma[1].y; m[6] = ma[1].z; m[7] = ma[1].w;
-    if constexpr (OPT == FO_OPT_ADAM) {
-      v[0] = va[0].x; v[1] = va[0].y; v[2] = va[0].z; v[3] = va[0].w; v[4] = va[1].x; v[5] = va[1].y; v[6] = va[1].z; v[7] = va[1].w;
-    }
+    pairs_of(r.m0, r.m1, u.m);
+    if constexpr (OPT == FO_OPT_ADAM) pairs_of(r.v0, r.v1, u.v);
   }
+}
+
+FO_DEVI float sign_of(float x);
+
+template <int OPT, int PDT, int ECC_BITS, int STATE>
+FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const unsigned long long i0, const float one, Unpacked& u) {
+  using namespace fast2;
+  const float2 one2 = sp(one);
+  float2 (&g)[4] = u.g;
+  float2 (&theta)[4] = u.theta;
+  float2 (&old_lp)[4] = u.old_lp;
+  float2 (&m)[4] = u.m;
+  float2 (&v)[4] = u.v;
+  float2 root[4];
+  const unsigned long long gi = i0 >> 5;
 
   // ---- update --------------------------------------------------------------------------------------
   const bool decoupled = (h.flags & FO_FLAG_DECOUPLED_WD) != 0;
@@ -445,91 +507,99 @@ FO_DEVI void hot_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const unsi
     // flashoptim_jax/adamw.py:95-106
     if (!decoupled) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) g[j] = fadd(g[j], fmul(h.wd, theta[j]));
+      for (int k = 0; k < 4; ++k) g[k] = sum2(mul2(sp(h.wd), theta[k]), g[k], one2);
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      m[j] = fadd(fmul(h.b1, m[j]), fmul(h.omb1, g[j]));
-      v[j] = fadd(fmul(h.b2, v[j]), fmul(h.omb2, fmul(g[j], g[j])));
+    for (int k = 0; k < 4; ++k) {
+      m[k] = sum2(mul2(sp(h.b1), m[k]), mul2(sp(h.omb1), g[k]), one2);
+      v[k] = sum2(mul2(sp(h.b2), v[k]), mul2(sp(h.omb2), mul2(g[k], g[k])), one2);
     }
     if (decoupled) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) theta[j] = fmul(theta[j], h.decay);
+      for (int k = 0; k < 4; ++k) theta[k] = mul2(theta[k], sp(h.decay));
     }
-    if (min8(v) >= 1.0e-30f) {
+    // Ranges in which the packed square root and division are exact: second moment in
+    // [1e-30, 1e30] (so the denominator lies in [eps, 1e20]) and numerator magnitudes in [2^-40, 2^60].
+    const float num_lo = fmul(minabs8(m), fabsf(h.lr_bc1)), num_hi = fmul(maxabs8(m), fabsf(h.lr_bc1));
+    if (min8(v) >= 1.0e-30f && max8(v) <= 1.0e30f && num_lo >= 9.094947e-13f && num_hi <= 1.1529215e18f) {
+      const float2 nsq = sp(-h.sqrt_bc2), rsq = sp(h.rcp_sqrt_bc2), eps = sp(h.eps), nlr = sp(-h.lr_bc1);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) root[j] = fast::sqrt_core(v[j]);
+      for (int k = 0; k < 4; ++k) {
+        root[k] = sqrt_core2(v[k]);
+        const float2 den = add2(div_by_rcp2(root[k], nsq, rsq), eps);
+        theta[k] = sum2(div2(mul2(nlr, m[k]), den), theta[k], one2);  // theta - (lr/bc1 * m) / den
+      }
     } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) root[j] = fsqrt(v[j]);
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float quo = fast::div_by_rcp(root[j], h.sqrt_bc2, h.rcp_sqrt_bc2);
-      theta[j] = fsub(theta[j], fdiv(fmul(h.lr_bc1, m[j]), fadd(quo, h.eps)));
+      for (int k = 0; k < 4; ++k) {
+        root[k] = mk(fsqrt(v[k].x), fsqrt(v[k].y));
+        const float dx = fadd(fast::div_by_rcp(root[k].x, h.sqrt_bc2, h.rcp_sqrt_bc2), h.eps);
+        const float dy = fadd(fast::div_by_rcp(root[k].y, h.sqrt_bc2, h.rcp_sqrt_bc2), h.eps);
+        theta[k].x = fsub(theta[k].x, fdiv(fmul(h.lr_bc1, m[k].x), dx));
+        theta[k].y = fsub(theta[k].y, fdiv(fmul(h.lr_bc1, m[k].y), dy));
+      }
     }
   } else if constexpr (OPT == FO_OPT_LION) {
     // flashoptim_jax/momentum_kernel.py:77-79 or flashoptim_jax/lion.py:50-52
-    float upd[8];
+    float2 upd[4];
     if (h.flags & FO_FLAG_LION_LERP) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float d = fsub(g[j], m[j]);
-        upd[j] = sign_of(fadd(m[j], fmul(h.omb1, d)));
-        m[j] = fadd(m[j], fmul(h.omb2, d));
+      for (int k = 0; k < 4; ++k) {
+        const float2 d = fma2(m[k], sp(-1.0f), g[k]);  // g - m
+        const float2 c = sum2(mul2(sp(h.omb1), d), m[k], one2);
+        upd[k] = mk(sign_of(c.x), sign_of(c.y));
+        m[k] = sum2(mul2(sp(h.omb2), d), m[k], one2);
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        upd[j] = sign_of(fadd(fmul(h.b1, m[j]), fmul(h.omb1, g[j])));
-        m[j] = fadd(fmul(h.b2, m[j]), fmul(h.omb2, g[j]));
+      for (int k = 0; k < 4; ++k) {
+        const float2 c = sum2(mul2(sp(h.b1), m[k]), mul2(sp(h.omb1), g[k]), one2);
+        upd[k] = mk(sign_of(c.x), sign_of(c.y));
+        m[k] = sum2(mul2(sp(h.b2), m[k]), mul2(sp(h.omb2), g[k]), one2);
       }
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) theta[j] = fsub(fmul(theta[j], h.decay), fmul(h.lr, upd[j]));
+    for (int k = 0; k < 4; ++k) theta[k] = sum2(mul2(theta[k], sp(h.decay)), mul2(sp(-h.lr), upd[k]), one2);  // theta*decay - lr*upd
   } else {
     // flashoptim_jax/momentum_kernel.py:74-75,80-86; flashoptim_jax/sgd.py:45-63
     if (!decoupled) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) g[j] = fadd(g[j], fmul(h.wd, theta[j]));
+      for (int k = 0; k < 4; ++k) g[k] = sum2(mul2(sp(h.wd), theta[k]), g[k], one2);
     }
-    float dir[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) dir[j] = g[j];
     if constexpr (STATE != FO_STATE_NONE) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) m[j] = fadd(fmul(h.b1, m[j]), fmul(h.omb1, g[j]));
+      for (int k = 0; k < 4; ++k) m[k] = sum2(mul2(sp(h.b1), m[k]), mul2(sp(h.omb1), g[k]), one2);
       if (h.flags & FO_FLAG_NESTEROV) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) dir[j] = fadd(g[j], fmul(h.b1, m[j]));
+        for (int k = 0; k < 4; ++k) g[k] = sum2(mul2(sp(h.b1), m[k]), g[k], one2);
       } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) dir[j] = m[j];
+        for (int k = 0; k < 4; ++k) g[k] = m[k];
       }
     }
     if (decoupled) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) theta[j] = fmul(theta[j], h.decay);
+      for (int k = 0; k < 4; ++k) theta[k] = mul2(theta[k], sp(h.decay));
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) theta[j] = fsub(theta[j], fmul(h.lr, dir[j]));
+    for (int k = 0; k < 4; ++k) theta[k] = sum2(mul2(sp(-h.lr), g[k]), theta[k], one2);  // theta - lr*dir
   }
 
   // ---- parameter (+ECC) back ---------------------------------------------------------------------
   if constexpr (PDT == FO_F32) {
     if (h.flags & FO_FLAG_LP_DELTA) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) theta[j] = fadd(old_lp[j], fsub(theta[j], old_lp[j]));
+      for (int k = 0; k < 4; ++k) theta[k] = add2(old_lp[k], fma2(old_lp[k], sp(-1.0f), theta[k]));
     }
-    __stcs((float4*)((float*)L.param + i0), make_float4(theta[0], theta[1], theta[2], theta[3]));
-    __stcs((float4*)((float*)L.param + i0) + 1, make_float4(theta[4], theta[5], theta[6], theta[7]));
+    __stcs((float4*)((float*)L.param + i0), make_float4(theta[0].x, theta[0].y, theta[1].x, theta[1].y));
+    __stcs((float4*)((float*)L.param + i0) + 1, make_float4(theta[2].x, theta[2].y, theta[3].x, theta[3].y));
   } else {
     uint32_t nw[4];
-    float new_lp[8];
+    float2 new_lp[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      nw[k] = pack2<PDT>(theta[2 * k], theta[2 * k + 1]);
-      unpack2<PDT>(nw[k], new_lp[2 * k], new_lp[2 * k + 1]);
+      nw[k] = pack2<PDT>(theta[k].x, theta[k].y);
+      unpack2<PDT>(nw[k], new_lp[k].x, new_lp[k].y);
     }
     if constexpr (ECC_BITS != 0) {
       int ne[8];
@@ -537,10 +607,13 @@ FO_DEVI void hot_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const unsi
       if constexpr (PDT == FO_BF16) ordinary = minabs8(new_lp) >= fast::Ordinary<PDT>::kMin;
       if (ordinary) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ne[j] = fast::ecc_ordinary<PDT, ECC_BITS>(theta[j], new_lp[j]);
+        for (int k = 0; k < 4; ++k) ecc_ordinary2<PDT, ECC_BITS>(theta[k], new_lp[k], ne[2 * k], ne[2 * k + 1]);
       } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ne[j] = ecc_slow<PDT, ECC_BITS>(theta[j]);
+        for (int k = 0; k < 4; ++k) {
+          ne[2 * k] = ecc_slow<PDT, ECC_BITS>(theta[k].x);
+          ne[2 * k + 1] = ecc_slow<PDT, ECC_BITS>(theta[k].y);
+        }
       }
       if constexpr (ECC_BITS == 16) {
         uint4 o;
@@ -558,9 +631,11 @@ FO_DEVI void hot_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const unsi
       // adamw.py:411,415,463: param + lp(new_lp - param), both roundings to the param dtype
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        float d0, d1;
-        unpack2<PDT>(pack2<PDT>(fsub(new_lp[2 * k], old_lp[2 * k]), fsub(new_lp[2 * k + 1], old_lp[2 * k + 1])), d0, d1);
-        nw[k] = pack2<PDT>(fadd(old_lp[2 * k], d0), fadd(old_lp[2 * k + 1], d1));
+        const float2 d = fma2(old_lp[k], sp(-1.0f), new_lp[k]);
+        float2 dr;
+        unpack2<PDT>(pack2<PDT>(d.x, d.y), dr.x, dr.y);
+        const float2 sum = add2(old_lp[k], dr);
+        nw[k] = pack2<PDT>(sum.x, sum.y);
       }
     }
     __stcs((uint4*)((unsigned short*)L.param + i0), make_uint4(nw[0], nw[1], nw[2], nw[3]));
@@ -568,48 +643,57 @@ FO_DEVI void hot_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const unsi
 
   // ---- moments back ------------------------------------------------------------------------------
   if constexpr (STATE == FO_STATE_FULL) {
-    __stcs((float4*)((float*)L.mu + i0), make_float4(m[0], m[1], m[2], m[3]));
-    __stcs((float4*)((float*)L.mu + i0) + 1, make_float4(m[4], m[5], m[6], m[7]));
+    __stcs((float4*)((float*)L.mu + i0), make_float4(m[0].x, m[0].y, m[1].x, m[1].y));
+    __stcs((float4*)((float*)L.mu + i0) + 1, make_float4(m[2].x, m[2].y, m[3].x, m[3].y));
     if constexpr (OPT == FO_OPT_ADAM) {
-      __stcs((float4*)((float*)L.nu + i0), make_float4(v[0], v[1], v[2], v[3]));
-      __stcs((float4*)((float*)L.nu + i0) + 1, make_float4(v[4], v[5], v[6], v[7]));
+      __stcs((float4*)((float*)L.nu + i0), make_float4(v[0].x, v[0].y, v[1].x, v[1].y));
+      __stcs((float4*)((float*)L.nu + i0) + 1, make_float4(v[2].x, v[2].y, v[3].x, v[3].y));
     }
   } else if constexpr (STATE == FO_STATE_QUANT) {
     const bool floor_mode = (h.flags & FO_FLAG_SCALE_FLOOR) != 0;
     const bool writer = (threadIdx.x & 3) == 0;
-    {
-      const float am = group_max(maxabs8(m));
-      uint32_t q[8];
-      if (am >= 1.0e-12f && am <= 1.0e30f) {
-        const float rcp = fast::rcp_rn(am);
+    const float am = group_max(maxabs8(m));
+    float av = 1.0f;
+    if constexpr (OPT == FO_OPT_ADAM) av = group_max(max8(root));
+    uint32_t qm[8], qv[8];
+    if (am >= 1.0e-12f && am <= 1.0e30f && av >= 1.0e-12f && av <= 1.0e30f) {
+      const float rm = fast::rcp_rn(am);
+      const float2 nam = sp(-am), rm2 = sp(rm);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) q[j] = fast::softsign_code_bits(fast::div_by_rcp(m[j], am, rcp));
-      } else {
-        const float safe = ieee::safe_scale(am, floor_mode);
+      for (int k = 0; k < 4; ++k) softsign_code_bits2(div_by_rcp2(m[k], nam, rm2), one2, qm[2 * k], qm[2 * k + 1]);
+      if constexpr (OPT == FO_OPT_ADAM) {
+        const float rv = fast::rcp_rn(av);
+        const float2 nav = sp(-av), rv2 = sp(rv);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) q[j] = (uint32_t)ieee::quant_m(m[j], safe);
+        for (int k = 0; k < 4; ++k) quant_v_bits2(root[k], nav, rv2, one2, qv[2 * k], qv[2 * k + 1]);
       }
+    } else {
+      const float sm = ieee::safe_scale(am, floor_mode);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        qm[2 * k] = (uint32_t)ieee::quant_m(m[k].x, sm);
+        qm[2 * k + 1] = (uint32_t)ieee::quant_m(m[k].y, sm);
+      }
+      if constexpr (OPT == FO_OPT_ADAM) {
+        const float sv = ieee::safe_scale(av, floor_mode);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          qv[2 * k] = (uint32_t)ieee::quant_v(root[k].x, sv);
+          qv[2 * k + 1] = (uint32_t)ieee::quant_v(root[k].y, sv);
+        }
+      }
+    }
+    {
       uint2 o;
-      o.x = pack_bytes(q[0], q[1], q[2], q[3]);
-      o.y = pack_bytes(q[4], q[5], q[6], q[7]);
+      o.x = pack_bytes(qm[0], qm[1], qm[2], qm[3]);
+      o.y = pack_bytes(qm[4], qm[5], qm[6], qm[7]);
       __stcs((uint2*)((signed char*)L.mu + i0), o);
       if (writer) ((__half*)L.mu_scales)[gi] = __float2half_rn(am);
     }
     if constexpr (OPT == FO_OPT_ADAM) {
-      const float av = group_max(maxabs8(root));
-      uint32_t q[8];
-      if (av >= 1.0e-12f && av <= 1.0e30f) {
-        const float rcp = fast::rcp_rn(av);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) q[j] = fast::quant_v_bits(root[j], av, rcp);
-      } else {
-        const float safe = ieee::safe_scale(av, floor_mode);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) q[j] = (uint32_t)ieee::quant_v(root[j], safe);
-      }
       uint2 o;
-      o.x = pack_bytes(q[0], q[1], q[2], q[3]);
-      o.y = pack_bytes(q[4], q[5], q[6], q[7]);
+      o.x = pack_bytes(qv[0], qv[1], qv[2], qv[3]);
+      o.y = pack_bytes(qv[4], qv[5], qv[6], qv[7]);
       __stcs((uint2*)((unsigned char*)L.nu + i0), o);
       if (writer) ((__half*)L.nu_scales)[gi] = __float2half_rn(av);
     }
@@ -625,30 +709,77 @@ FO_DEVI void build_luts(float* lut_m, float* lut_v) {
   __syncthreads();
 }
 
+// which chunk a block works on: the leaf it belongs to, its first element, and whether the
+// hot path may take it
+struct ChunkRef {
+  int leaf;
+  bool hot;
+  unsigned long long base;
+};
+
+template <int OPT>
+FO_DEVI bool leaf_is_hot(const StepParams& p, int l) {
+#ifdef FO_NAIVE_MATH
+  return false;
+#else
+  return p.aligned[l] != 0;
+#endif
+}
+
+template <int OPT>
+FO_DEVI ChunkRef locate(const StepParams& p, uint32_t c, int l_hint) {
+  ChunkRef r;
+  int l = l_hint;
+  while (c >= p.first_block[l + 1]) ++l;
+  r.leaf = l;
+  r.base = (unsigned long long)(c - p.first_block[l]) * kChunk;
+  r.hot = leaf_is_hot<OPT>(p, l) && r.base + kChunk <= p.leaf[l].n;
+  return r;
+}
+
 template <int OPT, int PDT, int ECC_BITS, int STATE>
-__global__ void __launch_bounds__(kThreads, FO_MIN_BLOCKS) step_kernel(const __grid_constant__ StepParams p) {
+__global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const __grid_constant__ StepParams p) {
   __shared__ float lut_m[256], lut_v[256];
   if constexpr (STATE == FO_STATE_QUANT) build_luts(lut_m, lut_v);
   const uint32_t total = p.first_block[p.n_leaves];
-  int l = 0;
+  uint32_t c = blockIdx.x;
+  if (c >= total) return;
+  const unsigned long long toff = (unsigned long long)threadIdx.x * kPiece;
+  ChunkRef cur = locate<OPT>(p, c, 0);
   int l_loaded = -1;
   Hyp h;
-  bool hot_ok = false;
-  for (uint32_t c = blockIdx.x; c < total; c += gridDim.x) {
-    while (c >= p.first_block[l + 1]) ++l;
-    if (l != l_loaded) {
-      h = load_hyper<OPT>(p.hyper[p.hyper_of[l]]);
-      l_loaded = l;
-      hot_ok = p.aligned[l] != 0;
-#ifdef FO_NAIVE_MATH
-      hot_ok = false;
-#endif
-      if constexpr (OPT == FO_OPT_ADAM) hot_ok = hot_ok && (h.flags & kFlagTameAdam) != 0;
+  bool hyper_ok = true;  // Adam: the hyper set allows the reciprocal shortcut in the denominator
+  Raw<OPT, PDT, ECC_BITS, STATE> raw;
+  bool loaded = false;
+  if (cur.hot) {
+    hot_load<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], p.grad_dtype, cur.base + toff, raw);
+    loaded = true;
+  }
+  while (true) {
+    if (cur.leaf != l_loaded) {
+      h = load_hyper<OPT>(p.hyper[p.hyper_of[cur.leaf]]);
+      l_loaded = cur.leaf;
+      if constexpr (OPT == FO_OPT_ADAM) hyper_ok = (h.flags & kFlagTameAdam) != 0;
     }
-    const DevLeaf& L = p.leaf[l];
-    const unsigned long long base = (unsigned long long)(c - p.first_block[l]) * kChunk;
-    if (hot_ok && base + kChunk <= L.n) hot_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, base, lut_m, lut_v);
-    else cold_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, base, lut_m, lut_v);
+    const uint32_t cn = c + gridDim.x;
+    const bool more = cn < total;
+    ChunkRef nxt = cur;
+    if (more) nxt = locate<OPT>(p, cn, cur.leaf);
+    if (cur.hot && hyper_ok) {
+      if (!loaded) hot_load<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], p.grad_dtype, cur.base + toff, raw);
+      Unpacked u;
+      hot_unpack<OPT, PDT, ECC_BITS, STATE>(raw, p.grad_dtype, lut_m, lut_v, p.one, u);
+      // the next chunk's loads fly while this one is computed
+      loaded = more && nxt.hot;
+      if (loaded) hot_load<OPT, PDT, ECC_BITS, STATE>(p.leaf[nxt.leaf], p.grad_dtype, nxt.base + toff, raw);
+      hot_finish<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], h, cur.base + toff, p.one, u);
+    } else {
+      cold_chunk<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], h, p.grad_dtype, cur.base, lut_m, lut_v);
+      loaded = false;
+    }
+    if (!more) break;
+    c = cn;
+    cur = nxt;
   }
 }
 
@@ -753,7 +884,7 @@ using LaunchFn = cudaError_t (*)(const StepParams&, const LaunchInfo&, cudaStrea
 
 template <int OPT, int PDT, int ECC_BITS, int STATE>
 cudaError_t launch_step(const StepParams& p, const LaunchInfo& info, cudaStream_t s) {
-  unsigned int grid = (unsigned int)info.sm_count * FO_MIN_BLOCKS;
+  unsigned int grid = (unsigned int)info.sm_count * min_blocks(OPT);
   if (grid > info.total_chunks) grid = info.total_chunks;
   step_kernel<OPT, PDT, ECC_BITS, STATE><<<grid, kThreads, 0, s>>>(p);
   return cudaGetLastError();

@@ -161,6 +161,7 @@ int fo_reconstruct(const void* param_lp, const void* ecc, float* theta, int32_t 
 #define FO_SELFTEST_SPLIT 3       /* every fp32 bit pattern; arg = param_dtype*100 + ecc_bits */
 #define FO_SELFTEST_GROUP_DIV 4   /* arg = number of random (a, b) pairs in millions */
 #define FO_SELFTEST_CODE_TABLES 5 /* every int8 / uint8 code and every int16 ECC value */
+#define FO_SELFTEST_PACKED 7      /* 1e9 random (a*b + c*d) pairs through the packed fp32x2 forms vs scalar; arg 0 = form in use, 1 = plain packed add */
 #define FO_SELFTEST_RCP 6         /* reciprocal of every fp32 in [1e-30, 1e30]; arg 0 = variant in use, 1 / 2 = one / two correction steps */
 int fo_selftest(int32_t which, int64_t arg, uint64_t* mismatches, void* cuda_stream);
 

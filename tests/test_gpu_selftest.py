@@ -73,3 +73,9 @@ def test_reciprocal_shortcut_matches_ieee_for_every_float_in_range():
     from flashoptim_jax_b200 import _lib
 
     assert _run(_lib.FO_SELFTEST_RCP, 0) == 0
+
+
+def test_packed_product_sum_keeps_two_roundings():
+    from flashoptim_jax_b200 import _lib
+
+    assert _run(_lib.FO_SELFTEST_PACKED, 0) == 0
