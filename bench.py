@@ -1,0 +1,353 @@
+"""Optimizer-step benchmark: Llama-3-8B-shaped pytree, flash AdamW with 32-bit master weights.
+
+    python bench.py --gpus N --steps K --warmup W            (this library)
+    python bench.py --impl reference ...                     (the reference's CPU path, restated)
+
+One step = one pass of the fused update over the whole pytree.  With N > 1 the step is
+ZeRO-1: NCCL reduce-scatter(mean) of the bf16 gradients, the fused kernel on the rank's
+slice, NCCL all-gather of the updated parameters (launch with torchrun, one rank per GPU).
+Inputs are synthetic (seeded normal draws with the configured shapes and scales).  Rank 0
+prints ONE JSON line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "optimizer-step params/sec"
+UNIT = "params/s"
+
+# algorithmic bytes per parameter of one in-place step (bf16 grads, group size 32):
+# read grad 2 + param 2 + ecc 2 + mu 1 + nu 1 + two fp16 scales per 32 elements; write the same minus the grad
+BYTES_PER_PARAM_BF16_ECC16 = (2 + 2 + 2 + 1 + 1 + 0.125) + (2 + 2 + 1 + 1 + 0.125)  # 14.25
+BYTES_PER_PARAM_F32 = (4 + 4 + 1 + 1 + 0.125) + (4 + 1 + 1 + 0.125)                   # 16.25
+# DRAM bytes per parameter seen by one ncu capture of the bf16 kernel (profiles/), scaled to a launch by its parameter count
+NCU_DRAM_BYTES_PER_PARAM = None
+
+
+def llama3_8b_shapes():
+    """Leaf shapes of the Llama-3-8B pytree: 291 leaves, 8,030,261,248 parameters."""
+    shapes = {"tok_embeddings": ((128256, 4096), "bf16"), "lm_head": ((128256, 4096), "bf16"), "norm": ((4096,), "f32")}
+    for i in range(32):
+        p = f"layers.{i:02d}."
+        shapes[p + "wq"] = ((4096, 4096), "bf16")
+        shapes[p + "wk"] = ((4096, 1024), "bf16")
+        shapes[p + "wv"] = ((4096, 1024), "bf16")
+        shapes[p + "wo"] = ((4096, 4096), "bf16")
+        shapes[p + "w1"] = ((4096, 14336), "bf16")
+        shapes[p + "w3"] = ((4096, 14336), "bf16")
+        shapes[p + "w2"] = ((14336, 4096), "bf16")
+        shapes[p + "attention_norm"] = ((4096,), "f32")
+        shapes[p + "ffn_norm"] = ((4096,), "f32")
+    return shapes
+
+
+def small_shapes():
+    """A 1/64-scale pytree with the same leaf mix, for quick checks (not the benchmark workload)."""
+    shapes = {"tok_embeddings": ((8192, 1024), "bf16"), "lm_head": ((8192, 1024), "bf16"), "norm": ((1024,), "f32")}
+    for i in range(8):
+        p = f"layers.{i:02d}."
+        for name, shp in (("wq", (1024, 1024)), ("wk", (1024, 256)), ("wv", (1024, 256)), ("wo", (1024, 1024)),
+                          ("w1", (1024, 3584)), ("w3", (1024, 3584)), ("w2", (3584, 1024))):
+            shapes[p + name] = (shp, "bf16")
+        shapes[p + "attention_norm"] = ((1024,), "f32")
+        shapes[p + "ffn_norm"] = ((1024,), "f32")
+    return shapes
+
+
+WORKLOADS = {"llama3_8b": llama3_8b_shapes, "llama3_8b_div64": small_shapes}
+HPARAMS = dict(learning_rate=3e-4, b1=0.9, b2=0.999, eps=1e-8, weight_decay=0.1, master_weight_bits=32)
+
+
+def numel(shape):
+    n = 1
+    for d in shape:
+        n *= d
+    return n
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons of one GPU, sampled every 200 ms while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_baseline(n_params: int, steps: int, threads: int = 0):
+    """The reference's CPU path (restated in C, OpenMP) on a bounded sample: AdamW on n_params bf16 parameters."""
+    import numpy as np
+
+    from oracle import c_oracle as C
+    from oracle import flashoptim_oracle as O
+    from tests import helpers as H
+
+    C.build()
+    cores = C.set_threads(threads)
+    rng = np.random.default_rng(0)
+    pnp = rng.standard_normal(n_params, dtype=np.float32) * np.float32(0.02)
+    leaf = H.fresh_leaf(pnp.astype(H.BF16), C.ADAM, C.STATE_QUANT, 16)
+    g = (rng.standard_normal(n_params, dtype=np.float32) * np.float32(1e-4)).astype(H.BF16)
+    times = []
+    for t in range(1, steps + 2):
+        hp = H.hyper_tuple(C.ADAM, O.UNFUSED, t, lr=HPARAMS["learning_rate"], wd=HPARAMS["weight_decay"])
+        t0 = time.perf_counter()
+        H.oracle_step(C.ADAM, g, leaf, C.STATE_QUANT, 32, hp)
+        times.append(time.perf_counter() - t0)
+    times = times[1:]  # first call pages memory in
+    per_step = sum(times) / len(times)
+    return {"value": n_params / per_step, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"AdamW (32-bit master) on one {n_params}-element bf16 leaf, {len(times)} steps, C restatement of the reference's CPU path with OpenMP"}, per_step
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n = 1 << 26
+    base, per_step = cpu_baseline(n, max(1, args.steps))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": {"workload": args.workload, "optimizer": "flash_adamw", **{k: v for k, v in HPARAMS.items()},
+                                                        "note": "JAX is not installed, so the reference's CPU (unfused) path runs as its C restatement on a bounded sample"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from flashoptim_jax_b200 import _engine as eng
+    from flashoptim_jax_b200.zero1 import Zero1Optimizer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    shapes = WORKLOADS[args.workload]()
+    total_params = sum(numel(s) for s, _ in shapes.values())
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1234)  # same draws on every rank: parameters are replicated
+    params = {}
+    for name, (shape, kind) in shapes.items():
+        if kind == "bf16":
+            params[name] = (torch.randn(shape, device=device, generator=gen) * 0.02).to(torch.bfloat16)
+        else:
+            params[name] = torch.ones(shape, device=device, dtype=torch.float32)
+
+    kernel_ms = {}  # per (param dtype code) -> list of launch durations
+    pending = []
+
+    def timed_launch(opt, work):
+        by_bucket = {}
+        for w in work:
+            by_bucket.setdefault(w.bucket, []).append(w)
+        calls = 0
+        for bucket, items in by_bucket.items():
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            calls += eng.launch(opt, items)
+            e1.record()
+            pending.append((bucket[1], sum(w.param.numel() for w in items), e0, e1))
+        return calls
+
+    launches = [0]
+
+    def counting_launch(opt, work):
+        n = timed_launch(opt, work)
+        launches[0] += n
+        return n
+
+    zero = Zero1Optimizer("adamw", params, step_fn=counting_launch, **HPARAMS)
+    del params
+    torch.cuda.empty_cache()
+    ggen = torch.Generator(device=device)
+    ggen.manual_seed(99 + rank)
+    from flashoptim_jax_b200 import tree as pytree
+
+    for g in pytree.tree_leaves(zero.grads):
+        g.copy_((torch.randn(g.shape, device=device, generator=ggen) * 1e-4).to(g.dtype))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        zero.step()
+    barrier()
+    pending.clear()
+    launches[0] = 0
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        zero.step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    elapsed_ms = e0.elapsed_time(e1)
+    n_launch = launches[0]
+    for code, n_par, a, b in pending:
+        kernel_ms.setdefault(code, []).append((n_par, a.elapsed_time(b)))
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t)
+    ms_per_step = elapsed_ms / args.steps
+    value = total_params / (ms_per_step * 1e-3)
+
+    # roofline of the dominant kernel (the bf16 / int16-ECC AdamW launch), from its own CUDA-event durations
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    bf16_launches = kernel_ms.get(1, [])
+    n_par = bf16_launches[0][0] if bf16_launches else 0
+    avg_ms = sum(ms for _, ms in bf16_launches) / max(1, len(bf16_launches))
+    achieved = n_par * BYTES_PER_PARAM_BF16_ECC16 / (avg_ms * 1e-3) / 1e9 if avg_ms else 0.0
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None if NCU_DRAM_BYTES_PER_PARAM is None else NCU_DRAM_BYTES_PER_PARAM * n_par,
+                "kernel": "step_kernel<adam, bf16, ecc16, quant>", "params_per_launch": n_par, "avg_launch_ms": avg_ms,
+                "algorithmic_bytes_per_param": BYTES_PER_PARAM_BF16_ECC16, "peak_source": peak_src}
+
+    # end to end through the public API with gradients arriving from pinned host memory every step
+    e2e_steps = max(1, min(args.steps, 2))
+    stage_elems = 1 << 28
+    stage = torch.empty(stage_elems, dtype=torch.bfloat16, pin_memory=True)
+    stage.copy_((torch.randn(stage_elems, device=device, generator=ggen) * 1e-4).to(torch.bfloat16).cpu())
+    stage32 = torch.full((4096,), 1e-4, dtype=torch.float32).pin_memory()
+    grad_leaves = pytree.tree_leaves(zero.grads)
+    h2d = sum(g.numel() * g.element_size() for g in grad_leaves)
+    probe = torch.empty(1, dtype=torch.float32).pin_memory()
+    first_param = pytree.tree_leaves(zero.params)[0].view(-1)
+
+    def e2e_step():
+        off = 0
+        for g in grad_leaves:  # host -> device copy of this step's gradients
+            flat = g.view(-1)
+            n = flat.numel()
+            if g.dtype == torch.float32:
+                flat.copy_(stage32[:n], non_blocking=True)
+                continue
+            done = 0
+            while done < n:
+                take = min(n - done, stage_elems - off)
+                flat[done:done + take].copy_(stage[off:off + take], non_blocking=True)
+                done += take
+                off = (off + take) % stage_elems
+        zero.step()
+        probe.copy_(first_param[:1].float(), non_blocking=True)  # device -> host read of a result
+        torch.cuda.current_stream().synchronize()
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t)
+    e2e = {"value": total_params / e2e_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+           "ms_per_step": e2e_s * 1e3, "steps": e2e_steps}
+
+    if rank == 0:
+        base = None
+        if world == 1 and not args.no_cpu_baseline:
+            base, _ = cpu_baseline(1 << 26, 3)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "leaves": len(shapes), "params": total_params, "optimizer": "flash_adamw",
+                       **HPARAMS, "grad_dtype": "bf16", "parallelism": "single" if world == 1 else f"zero1x{world}",
+                       "l2": "working set per step (>= 14 B/param) exceeds the 126 MB L2, no flush needed"},
+            "roofline": roofline, "cpu_baseline": base, "e2e": e2e, "gpu_launches": n_launch, "clocks": clocks,
+            "hbm_gbs_whole_step": total_params * BYTES_PER_PARAM_BF16_ECC16 / (ms_per_step * 1e-3) / 1e9,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="llama3_8b")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

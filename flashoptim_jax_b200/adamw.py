@@ -32,6 +32,18 @@ class FlashAdamState(NamedTuple):
     ecc: Any
 
 
+def adam_hyper(config: Dict[str, Any], lr: float, count: int, decoupled_weight_decay: bool):
+    """The 0-d operands of the Adam kernel for one param group at step `count` (adamw.py:526-528)."""
+    is_fused = bool(config["fused"])
+    flags = (_lib.FO_FLAG_DECOUPLED_WD if decoupled_weight_decay else 0)
+    flags |= _lib.FO_FLAG_SCALE_FLOOR if is_fused else _lib.FO_FLAG_LP_DELTA
+    return (
+        eng.F32(lr), eng.F32(config["weight_decay"]), eng.F32(config["b1"]), eng.F32(config["b2"]),
+        eng.one_minus(config["b1"], is_fused), eng.one_minus(config["b2"], is_fused), eng.F32(config["eps"]),
+        eng.bias_correction(config["b1"], count), eng.bias_correction(config["b2"], count), flags,
+    )
+
+
 def _make_adam_transform(learning_rate, b1, b2, eps, weight_decay, quantize, master_weight_bits, group_size, fused,
                          decoupled_weight_decay, param_groups, name, donate) -> utils.FlashOptimizer:
     utils._validate_master_weight_bits(master_weight_bits)
@@ -62,14 +74,7 @@ def _make_adam_transform(learning_rate, b1, b2, eps, weight_decay, quantize, mas
             leaf = as_tensor(leaf)
             config = utils._group_config_for_path(path, leaf, defaults, param_groups)
             lr = utils._resolve_learning_rate(config["learning_rate"], old_count)  # zero-based count (adamw.py:526)
-            is_fused = bool(config["fused"])
-            flags = (_lib.FO_FLAG_DECOUPLED_WD if decoupled_weight_decay else 0)
-            flags |= _lib.FO_FLAG_SCALE_FLOOR if is_fused else _lib.FO_FLAG_LP_DELTA
-            hyper = (
-                eng.F32(lr), eng.F32(config["weight_decay"]), eng.F32(config["b1"]), eng.F32(config["b2"]),
-                eng.one_minus(config["b1"], is_fused), eng.one_minus(config["b2"], is_fused), eng.F32(config["eps"]),
-                eng.bias_correction(config["b1"], count), eng.bias_correction(config["b2"], count), flags,
-            )
+            hyper = adam_hyper(config, lr, count, decoupled_weight_decay)
             w, p_out, e_out, m_out, v_out = eng.make_work(leaf, g, e, m, v, config, hyper, donate, has_nu=True)
             work.append(w)
             new_p.append(p_out); new_e.append(e_out); new_m.append(m_out); new_v.append(v_out)

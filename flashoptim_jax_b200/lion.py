@@ -23,6 +23,17 @@ class FlashLionState(NamedTuple):
     ecc: Any
 
 
+def lion_hyper(config: Dict[str, Any], lr: float):
+    """The 0-d operands of the momentum kernel in Lion mode for one param group (lion.py:92-104)."""
+    is_fused = bool(config["fused"])
+    flags = _lib.FO_FLAG_DECOUPLED_WD | (_lib.FO_FLAG_SCALE_FLOOR if is_fused else _lib.FO_FLAG_LION_LERP)
+    return (
+        eng.F32(lr), eng.F32(config["weight_decay"]), eng.F32(config["b1"]), eng.F32(config["b2"]),
+        eng.one_minus(config["b1"], is_fused), eng.one_minus(config["b2"], is_fused),
+        eng.F32(0.0), eng.F32(1.0), eng.F32(1.0), flags,
+    )
+
+
 def flash_lion(learning_rate=1e-4, b1: float = 0.9, b2: float = 0.99, weight_decay: float = 0.0, quantize: bool = True,
                master_weight_bits: Optional[int] = 24, group_size: int = 32, fused: bool = True,
                param_groups: Optional[List[Dict[str, Any]]] = None, donate: bool = False) -> utils.FlashOptimizer:
@@ -49,13 +60,7 @@ def flash_lion(learning_rate=1e-4, b1: float = 0.9, b2: float = 0.99, weight_dec
             leaf = as_tensor(leaf)
             config = utils._group_config_for_path(path, leaf, defaults, param_groups)
             lr = utils._resolve_learning_rate(config["learning_rate"], old_count)
-            is_fused = bool(config["fused"])
-            flags = _lib.FO_FLAG_DECOUPLED_WD | (_lib.FO_FLAG_SCALE_FLOOR if is_fused else _lib.FO_FLAG_LION_LERP)
-            hyper = (
-                eng.F32(lr), eng.F32(config["weight_decay"]), eng.F32(config["b1"]), eng.F32(config["b2"]),
-                eng.one_minus(config["b1"], is_fused), eng.one_minus(config["b2"], is_fused),
-                eng.F32(0.0), eng.F32(1.0), eng.F32(1.0), flags,
-            )
+            hyper = lion_hyper(config, lr)
             w, p_out, e_out, m_out, _ = eng.make_work(leaf, g, e, m, None, config, hyper, donate, has_nu=False)
             work.append(w)
             new_p.append(p_out); new_e.append(e_out); new_m.append(m_out)

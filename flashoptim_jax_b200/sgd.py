@@ -31,6 +31,17 @@ def _validate_sgd_hparams(momentum: float, dampening: float, nesterov: bool) -> 
         raise ValueError("Nesterov momentum requires positive momentum and zero dampening")
 
 
+def sgd_hyper(config: Dict[str, Any], lr: float, decoupled_weight_decay: bool):
+    """The 0-d operands of the momentum kernel in SGD mode for one param group (sgd.py:102-116)."""
+    flags = (_lib.FO_FLAG_DECOUPLED_WD if decoupled_weight_decay else 0)
+    flags |= _lib.FO_FLAG_NESTEROV if config["nesterov"] else 0
+    flags |= _lib.FO_FLAG_SCALE_FLOOR if config["fused"] else 0
+    return (
+        eng.F32(lr), eng.F32(config["weight_decay"]), eng.F32(config["momentum"]), eng.F32(0.0),
+        eng.F32(1.0 - float(config["dampening"])), eng.F32(0.0), eng.F32(0.0), eng.F32(1.0), eng.F32(1.0), flags,
+    )
+
+
 def _make_sgd_transform(learning_rate, momentum, dampening, weight_decay, nesterov, quantize, master_weight_bits,
                         group_size, fused, decoupled_weight_decay, param_groups, name, donate) -> utils.FlashOptimizer:
     utils._validate_master_weight_bits(master_weight_bits)
@@ -67,13 +78,7 @@ def _make_sgd_transform(learning_rate, momentum, dampening, weight_decay, nester
             use_momentum = config["momentum"] > 0.0
             if use_momentum and not utils._has_state_leaf(m):
                 raise ValueError(f"{name}: momentum > 0 needs a momentum buffer in the state; re-run init()")
-            flags = (_lib.FO_FLAG_DECOUPLED_WD if decoupled_weight_decay else 0)
-            flags |= _lib.FO_FLAG_NESTEROV if config["nesterov"] else 0
-            flags |= _lib.FO_FLAG_SCALE_FLOOR if config["fused"] else 0
-            hyper = (
-                eng.F32(lr), eng.F32(config["weight_decay"]), eng.F32(config["momentum"]), eng.F32(0.0),
-                eng.F32(1.0 - float(config["dampening"])), eng.F32(0.0), eng.F32(0.0), eng.F32(1.0), eng.F32(1.0), flags,
-            )
+            hyper = sgd_hyper(config, lr, decoupled_weight_decay)
             w, p_out, e_out, m_out, _ = eng.make_work(leaf, g, e, m, None, config, hyper, donate, has_nu=False,
                                                       use_momentum=use_momentum)
             work.append(w)

@@ -1,0 +1,387 @@
+"""ZeRO-1 sharding of the optimizer step across the GPUs of one node.
+
+The reference replicates optimizer state on every device and all-reduces gradients
+(examples/train_gpt2_pretrain.py:412-441).  Here each rank keeps the ECC and the
+quantized moments of only its slice of every dtype bucket:
+
+    reduce-scatter(mean) of the gradients  ->  fused step on the local slice
+                                           ->  all-gather of the updated parameters
+
+Every quantization group of 32 consecutive elements is an independent unit, so a slice
+boundary that falls on a group boundary changes no result: the sharded step is
+bit-identical to the single-device step whenever the averaged gradient is.
+
+Layout.  All leaves of one parameter dtype live in one flat buffer, each leaf starting at a
+multiple of 32 elements (a group boundary; also 16-byte alignment for the vector path).
+The buffer is padded to world_size * shard, shard a multiple of 2048 elements (one kernel
+chunk).  Rank r owns flat[r*shard, (r+1)*shard); a leaf that straddles ranks is cut at
+group boundaries.  The parameter and gradient trees handed back to the caller are views
+into these buffers, so no copy sits between backward and the collectives.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Callable, Dict, List, NamedTuple, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _engine as eng
+from . import _lib
+from . import tree as pytree
+from . import utils
+from ._dev import DTYPE_CODE, as_tensor
+from .adamw import adam_hyper
+from .lion import lion_hyper
+from .sgd import sgd_hyper
+
+LEAF_ALIGN = 32      # elements: one quantization group
+SHARD_ALIGN = 2048   # elements: one kernel chunk
+
+
+class Segment(NamedTuple):
+    """The part of one leaf that one rank owns."""
+
+    leaf: int     # index into the flattened parameter list
+    lo: int       # first element of the leaf in this segment (multiple of 32)
+    hi: int       # one past the last element
+    offset: int   # position of `lo` in the rank's shard
+
+
+class BucketLayout(NamedTuple):
+    dtype: torch.dtype
+    leaves: List[int]          # leaf indices in this bucket, in tree order
+    starts: List[int]          # start of each leaf in the flat buffer
+    sizes: List[int]
+    total: int                 # padded length = world_size * shard
+    shard: int
+    segments: List[List[Segment]]  # per rank
+
+
+def plan_bucket(dtype: torch.dtype, leaf_ids: List[int], sizes: List[int], world_size: int) -> BucketLayout:
+    """Place leaves in a flat buffer and cut it into world_size equal shards."""
+    starts, pos = [], 0
+    for n in sizes:
+        starts.append(pos)
+        pos += -(-n // LEAF_ALIGN) * LEAF_ALIGN
+    shard = -(-pos // (world_size * SHARD_ALIGN)) * SHARD_ALIGN if pos else SHARD_ALIGN
+    total = shard * world_size
+    segments: List[List[Segment]] = []
+    for r in range(world_size):
+        lo_r, hi_r = r * shard, (r + 1) * shard
+        segs = []
+        for leaf, start, n in zip(leaf_ids, starts, sizes):
+            lo, hi = max(start, lo_r), min(start + n, hi_r)
+            if lo < hi:
+                segs.append(Segment(leaf, lo - start, hi - start, lo - lo_r))
+        segments.append(segs)
+    return BucketLayout(dtype, list(leaf_ids), starts, list(sizes), total, shard, segments)
+
+
+class ShardState(NamedTuple):
+    """Optimizer state of one segment (same tensors as the unsharded state, for [lo, hi) only)."""
+
+    ecc: Optional[torch.Tensor]
+    mu: Optional[torch.Tensor]
+    mu_scales: Optional[torch.Tensor]
+    nu: Optional[torch.Tensor]
+    nu_scales: Optional[torch.Tensor]
+
+
+def _reduce_scatter_mean(out: torch.Tensor, full: torch.Tensor, group, world_size: int) -> None:
+    """out <- mean over ranks of this rank's slice of `full` (the reference's pmean, train_gpt2_pretrain.py:429)."""
+    if world_size == 1:
+        if out.data_ptr() != full.data_ptr():
+            out.copy_(full[: out.numel()])
+        return
+    backend = dist.get_backend(group)
+    if backend == "nccl":
+        dist.reduce_scatter_tensor(out, full, op=dist.ReduceOp.AVG, group=group)
+        return
+    # backends without a mean / low-precision reduce-scatter (gloo, used by the CPU tests)
+    rank = dist.get_rank(group)
+    acc = full.to(torch.float32)
+    dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=group)
+    n = out.numel()
+    out.copy_((acc[rank * n:(rank + 1) * n] / world_size).to(out.dtype))
+
+
+def _all_gather_inplace(full: torch.Tensor, shard: int, group, world_size: int) -> None:
+    """Every rank's slice of `full` is sent to all others, in place."""
+    if world_size == 1:
+        return
+    rank = dist.get_rank(group)
+    mine = full[rank * shard:(rank + 1) * shard]
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(full, mine, group=group)
+    else:
+        parts = [torch.empty_like(mine) for _ in range(world_size)]
+        dist.all_gather(parts, mine.clone(), group=group)
+        for r, part in enumerate(parts):
+            full[r * shard:(r + 1) * shard].copy_(part)
+
+
+StepFn = Callable[[int, List[eng.LeafWork]], int]
+
+
+class Zero1Optimizer:
+    """flash_adamw / flash_adam / flash_lion / flash_sgd / flash_sgdw with sharded state.
+
+    optimizer   one of "adamw", "adam", "lion", "sgd", "sgdw"
+    params      pytree of tensors, identical on every rank; fp32 / bf16 / fp16 leaves
+    hparams     the keyword arguments of the matching flash_* factory (param_groups included)
+    group       torch.distributed process group (None = default group; no group = one rank)
+    step_fn     how a list of LeafWork is executed; the default launches the CUDA kernels
+    """
+
+    def __init__(self, optimizer: str, params: Any, *, group=None, step_fn: Optional[StepFn] = None, **hparams):
+        self.kind = optimizer
+        if optimizer not in ("adamw", "adam", "lion", "sgd", "sgdw"):
+            raise ValueError(f"unknown optimizer {optimizer!r}")
+        self.group = group
+        self.distributed = dist.is_available() and dist.is_initialized()
+        self.world_size = dist.get_world_size(group) if self.distributed else 1
+        self.rank = dist.get_rank(group) if self.distributed else 0
+        self._step_fn = step_fn or eng.launch
+        self.param_groups = hparams.pop("param_groups", None)
+        self.defaults = self._defaults(optimizer, hparams)
+        self.name = "flash_" + optimizer
+        self.opt_code = {"adamw": _lib.FO_OPT_ADAM, "adam": _lib.FO_OPT_ADAM, "lion": _lib.FO_OPT_LION,
+                         "sgd": _lib.FO_OPT_SGD, "sgdw": _lib.FO_OPT_SGD}[optimizer]
+        self.decoupled = optimizer in ("adamw", "sgdw", "lion")
+        self.count = 0
+
+        utils._validate_master_weight_bits(self.defaults["master_weight_bits"])
+        utils._validate_fused_group_size(self.defaults["group_size"], quantize=self.defaults["quantize"],
+                                         fused=self.defaults["fused"])
+        utils._validate_param_dtypes(params, self.defaults, self.param_groups, self.name)
+        utils._validate_meaningful_master_weight_bits(params, self.defaults, self.param_groups, self.name)
+        path_leaves, self.treedef = utils._tree_leaves_with_paths(params)
+        self.paths = [p for p, _ in path_leaves]
+        leaves = [as_tensor(leaf) for _, leaf in path_leaves]
+        self.shapes = [tuple(t.shape) for t in leaves]
+        self.configs = [utils._group_config_for_path(p, t, self.defaults, self.param_groups) for p, t in zip(self.paths, leaves)]
+        # leaves of one param group share one config object, so per-step scalars are derived once per group
+        interned: Dict[Any, Dict[str, Any]] = {}
+        self.configs = [interned.setdefault(tuple(sorted(c.items(), key=lambda kv: kv[0])), c) for c in self.configs]
+        for c in self.configs:
+            if c["quantize"] and c["group_size"] != 32:
+                raise ValueError("Zero1Optimizer shards on 32-element group boundaries: group_size must be 32")
+
+        device = leaves[0].device if leaves else torch.device("cpu")
+        self.device = device
+        self.buckets: List[BucketLayout] = []
+        self.flat_params: List[torch.Tensor] = []
+        self.flat_grads: List[torch.Tensor] = []
+        self.grad_shards: List[torch.Tensor] = []
+        by_dtype: Dict[torch.dtype, List[int]] = {}
+        for i, t in enumerate(leaves):
+            by_dtype.setdefault(t.dtype, []).append(i)
+        param_views: List[Optional[torch.Tensor]] = [None] * len(leaves)
+        grad_views: List[Optional[torch.Tensor]] = [None] * len(leaves)
+        for dtype, ids in by_dtype.items():
+            layout = plan_bucket(dtype, ids, [leaves[i].numel() for i in ids], self.world_size)
+            flat_p = torch.zeros(layout.total, dtype=dtype, device=device)
+            flat_g = torch.zeros(layout.total, dtype=dtype, device=device)
+            for i, start in zip(ids, layout.starts):
+                n = leaves[i].numel()
+                flat_p[start:start + n].copy_(leaves[i].reshape(-1))
+                param_views[i] = flat_p[start:start + n].view(self.shapes[i])
+                grad_views[i] = flat_g[start:start + n].view(self.shapes[i])
+            self.buckets.append(layout)
+            self.flat_params.append(flat_p)
+            self.flat_grads.append(flat_g)
+            # one rank owns everything: the "scattered" gradient is the flat buffer itself
+            self.grad_shards.append(flat_g if self.world_size == 1 else torch.zeros(layout.shard, dtype=dtype, device=device))
+        self.params = self.treedef.unflatten(param_views)
+        self.grads = self.treedef.unflatten(grad_views)
+        # state of the segments this rank owns, keyed by (bucket, segment index)
+        self.state: Dict[Tuple[int, int], ShardState] = {}
+        for b, layout in enumerate(self.buckets):
+            for s, seg in enumerate(layout.segments[self.rank]):
+                self.state[(b, s)] = self._init_segment(layout.dtype, seg)
+
+    # ---- construction helpers ---------------------------------------------------------------------
+
+    @staticmethod
+    def _defaults(optimizer: str, hp: Dict[str, Any]) -> Dict[str, Any]:
+        common = {"quantize": True, "master_weight_bits": 24, "group_size": 32, "fused": True}
+        if optimizer in ("adamw", "adam"):
+            d = {"learning_rate": 1e-3, "b1": 0.9, "b2": 0.999, "eps": 1e-8,
+                 "weight_decay": 1e-2 if optimizer == "adamw" else 0.0}
+        elif optimizer == "lion":
+            d = {"learning_rate": 1e-4, "b1": 0.9, "b2": 0.99, "weight_decay": 0.0}
+        else:
+            d = {"learning_rate": 1e-3, "momentum": 0.0, "dampening": 0.0, "weight_decay": 0.0, "nesterov": False}
+        d.update(common)
+        unknown = set(hp) - set(d)
+        if unknown:
+            raise TypeError(f"unexpected hyper-parameters for {optimizer}: {sorted(unknown)}")
+        d.update(hp)
+        return d
+
+    def _uses_momentum(self, config) -> bool:
+        return self.opt_code != _lib.FO_OPT_SGD or config["momentum"] > 0.0
+
+    def _init_segment(self, dtype: torch.dtype, seg: Segment) -> ShardState:
+        config = self.configs[seg.leaf]
+        n = seg.hi - seg.lo
+        dev = self.device
+        ecc = None
+        if dtype in (torch.bfloat16, torch.float16) and config["master_weight_bits"] in (24, 32):
+            ecc = torch.zeros(n, dtype=torch.int8 if config["master_weight_bits"] == 24 else torch.int16, device=dev)
+        mu = mu_s = nu = nu_s = None
+        if self._uses_momentum(config):
+            groups = -(-n // 32)
+            if config["quantize"]:
+                mu, mu_s = torch.zeros(n, dtype=torch.int8, device=dev), torch.zeros(groups, dtype=torch.float16, device=dev)
+                if self.opt_code == _lib.FO_OPT_ADAM:
+                    nu, nu_s = torch.zeros(n, dtype=torch.uint8, device=dev), torch.zeros(groups, dtype=torch.float16, device=dev)
+            else:
+                mu = torch.zeros(n, dtype=torch.float32, device=dev)
+                if self.opt_code == _lib.FO_OPT_ADAM:
+                    nu = torch.zeros(n, dtype=torch.float32, device=dev)
+        return ShardState(ecc, mu, mu_s, nu, nu_s)
+
+    # ---- the step --------------------------------------------------------------------------------
+
+    def _hyper(self, config, lr: float, count: int):
+        if self.opt_code == _lib.FO_OPT_ADAM:
+            return adam_hyper(config, lr, count, self.decoupled)
+        if self.opt_code == _lib.FO_OPT_LION:
+            return lion_hyper(config, lr)
+        return sgd_hyper(config, lr, self.decoupled)
+
+    def local_work(self) -> List[eng.LeafWork]:
+        """LeafWork of every segment this rank owns, for the step about to run."""
+        count_before = torch.tensor(self.count, dtype=torch.int32)
+        if getattr(self, "_static_work", None) is not None:
+            # buffers never move: only the hyper-parameters change from step to step
+            out = []
+            cache: Dict[int, Any] = {}
+            for w, leaf in self._static_work:
+                config = self.configs[leaf]
+                key = id(config)
+                if key not in cache:
+                    lr = utils._resolve_learning_rate(config["learning_rate"], count_before)
+                    cache[key] = self._hyper(config, lr, self.count + 1)
+                out.append(w._replace(hyper=cache[key]))
+            return out
+        work: List[eng.LeafWork] = []
+        leaf_of: List[int] = []
+        dev_index = self.device.index if self.device.type == "cuda" else -1
+        for b, layout in enumerate(self.buckets):
+            base = self.rank * layout.shard
+            flat_p, g_shard = self.flat_params[b], self.grad_shards[b]
+            for s, seg in enumerate(layout.segments[self.rank]):
+                config = self.configs[seg.leaf]
+                lr = utils._resolve_learning_rate(config["learning_rate"], count_before)
+                st = self.state[(b, s)]
+                n = seg.hi - seg.lo
+                if st.mu is None:
+                    state_kind = _lib.FO_STATE_NONE
+                elif config["quantize"]:
+                    state_kind = _lib.FO_STATE_QUANT
+                else:
+                    state_kind = _lib.FO_STATE_FULL
+                ecc_bits = 0 if st.ecc is None else st.ecc.element_size() * 8
+                bucket = (dev_index, DTYPE_CODE[layout.dtype], DTYPE_CODE[layout.dtype], ecc_bits, state_kind, 32)
+                work.append(eng.LeafWork(
+                    bucket, g_shard[seg.offset:seg.offset + n], flat_p[base + seg.offset: base + seg.offset + n],
+                    st.ecc, st.mu, st.mu_scales, st.nu, st.nu_scales, self._hyper(config, lr, self.count + 1)))
+                leaf_of.append(seg.leaf)
+        self._static_work = list(zip(work, leaf_of))
+        return work
+
+    def reduce_scatter_grads(self) -> None:
+        for b, layout in enumerate(self.buckets):
+            _reduce_scatter_mean(self.grad_shards[b], self.flat_grads[b], self.group, self.world_size)
+
+    def all_gather_params(self) -> None:
+        for b, layout in enumerate(self.buckets):
+            _all_gather_inplace(self.flat_params[b], layout.shard, self.group, self.world_size)
+
+    def step(self, grads: Any = None) -> Any:
+        """One optimizer step.  `grads` (optional) is copied into the flat gradient buffers;
+        leave it out when backward already wrote into `self.grads`.  Returns `self.params`."""
+        if grads is not None:
+            leaves, treedef = pytree.tree_flatten(grads)
+            if treedef != self.treedef:
+                raise ValueError(f"{self.name} gradients must match parameter structure")
+            for mine, theirs in zip(pytree.tree_leaves(self.grads), leaves):
+                mine.copy_(as_tensor(theirs).to(mine.dtype).reshape(mine.shape))
+        self.reduce_scatter_grads()
+        self._step_fn(self.opt_code, self.local_work())
+        self.count += 1
+        self.all_gather_params()
+        return self.params
+
+    # ---- checkpoint / export -------------------------------------------------------------------------
+
+    def local_state_dict(self) -> Dict[str, Any]:
+        """This rank's shard: segment table plus tensors (save one per rank, reload with load_local_state_dict)."""
+        out = {"count": self.count, "world_size": self.world_size, "rank": self.rank, "segments": {}}
+        for (b, s), st in self.state.items():
+            seg = self.buckets[b].segments[self.rank][s]
+            out["segments"][(b, s)] = {"leaf": seg.leaf, "lo": seg.lo, "hi": seg.hi,
+                                       **{k: v for k, v in st._asdict().items() if v is not None}}
+        return out
+
+    def load_local_state_dict(self, sd: Dict[str, Any]) -> None:
+        if sd["world_size"] != self.world_size or sd["rank"] != self.rank:
+            raise ValueError("shard was saved for a different world size or rank")
+        self.count = int(sd["count"])
+        for key, entry in sd["segments"].items():
+            seg = self.buckets[key[0]].segments[self.rank][key[1]]
+            if (entry["leaf"], entry["lo"], entry["hi"]) != (seg.leaf, seg.lo, seg.hi):
+                raise ValueError(f"segment {key} does not match this layout")
+            st = self.state[key]
+            for name, mine in st._asdict().items():
+                if mine is not None:
+                    mine.copy_(entry[name])
+
+    def gather_state(self, dst: int = 0) -> Optional[Dict[str, Any]]:
+        """Assemble the reference's unsharded state on rank `dst`: {"count", "mu", "nu", "ecc"} trees with
+        the layout tx.init() gives (QuantizedArray leaves, 0-d int32 sentinels)."""
+        from .quantization import QuantizedArray
+
+        pieces = {name: [None] * len(self.shapes) for name in ("ecc", "mu", "mu_scales", "nu", "nu_scales")}
+        gathered: List[Any] = [None] * self.world_size
+        mine = [(self.buckets[b].segments[self.rank][s], {k: v.cpu() for k, v in st._asdict().items() if v is not None})
+                for (b, s), st in self.state.items()]
+        if self.world_size > 1:
+            dist.gather_object(mine, gathered if self.rank == dst else None, dst=dst, group=self.group)
+        else:
+            gathered = [mine]
+        if self.rank != dst:
+            return None
+        full: Dict[str, List[Any]] = {k: [None] * len(self.shapes) for k in pieces}
+        for rank_items in gathered:
+            for seg, tensors in rank_items:
+                n = 1
+                for d in self.shapes[seg.leaf]:
+                    n *= d
+                for name, t in tensors.items():
+                    if full[name][seg.leaf] is None:
+                        length = -(-n // 32) if name.endswith("scales") else n
+                        full[name][seg.leaf] = torch.zeros(length, dtype=t.dtype)
+                    if name.endswith("scales"):
+                        full[name][seg.leaf][seg.lo // 32: seg.lo // 32 + t.numel()] = t
+                    else:
+                        full[name][seg.leaf][seg.lo:seg.hi] = t
+        ecc, mu, nu = [], [], []
+        for i, shape in enumerate(self.shapes):
+            ecc.append(full["ecc"][i].view(shape) if full["ecc"][i] is not None else torch.zeros((), dtype=torch.int32))
+            for vals, scales, out in (("mu", "mu_scales", mu), ("nu", "nu_scales", nu)):
+                v, s = full[vals][i], full[scales][i]
+                if v is None:
+                    out.append(torch.zeros((), dtype=torch.int32))
+                elif s is not None:
+                    out.append(QuantizedArray(values=v.view(shape), scales=s))
+                else:
+                    out.append(v.view(shape))
+        state = {"count": torch.tensor(self.count, dtype=torch.int32), "mu": self.treedef.unflatten(mu),
+                 "ecc": self.treedef.unflatten(ecc)}
+        if self.opt_code == _lib.FO_OPT_ADAM:
+            state["nu"] = self.treedef.unflatten(nu)
+        return state
