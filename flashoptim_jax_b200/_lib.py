@@ -19,12 +19,13 @@ FO_OPT_ADAM, FO_OPT_LION, FO_OPT_SGD = 0, 1, 2
 FO_STATE_QUANT, FO_STATE_FULL, FO_STATE_NONE = 0, 1, 2
 FO_FLAG_DECOUPLED_WD, FO_FLAG_NESTEROV, FO_FLAG_LION_LERP, FO_FLAG_LP_DELTA, FO_FLAG_SCALE_FLOOR = 1, 2, 4, 8, 16
 FO_MAX_HYPERS = 16
+FO_SELFTEST_STATIC_MAX_COUNTERS = 4
 FO_SELFTEST_SQRT, FO_SELFTEST_SOFTSIGN, FO_SELFTEST_RECONSTRUCT, FO_SELFTEST_SPLIT = 0, 1, 2, 3
 FO_SELFTEST_GROUP_DIV, FO_SELFTEST_CODE_TABLES, FO_SELFTEST_RCP, FO_SELFTEST_PACKED = 4, 5, 6, 7
 
 EXPORTS = (
     "fo_step", "fo_quantize_momentum", "fo_dequantize_momentum", "fo_quantize_variance",
-    "fo_dequantize_variance", "fo_split", "fo_reconstruct", "fo_selftest", "fo_version",
+    "fo_dequantize_variance", "fo_split", "fo_reconstruct", "fo_selftest", "fo_selftest_static", "fo_version",
     "fo_status_string", "fo_last_error",
 )
 
@@ -98,6 +99,8 @@ def lib() -> ctypes.CDLL:
         fn.argtypes = [vp, vp, vp, i32, i32, u64, vp]
     cdll.fo_selftest.restype = ctypes.c_int
     cdll.fo_selftest.argtypes = [i32, ctypes.c_int64, ctypes.POINTER(ctypes.c_uint64), vp]
+    cdll.fo_selftest_static.restype = ctypes.c_int
+    cdll.fo_selftest_static.argtypes = [i32, ctypes.c_int64, ctypes.POINTER(ctypes.c_uint64), ctypes.c_uint32, vp]
     cdll.fo_version.restype = ctypes.c_int
     cdll.fo_version.argtypes = []
     cdll.fo_status_string.restype = ctypes.c_char_p

@@ -1,5 +1,7 @@
 // Device self-checks: every arithmetic shortcut in fo_math.cuh (namespace fast) against the
 // plain IEEE formulation (namespace ieee), exhaustively where the input space allows.
+#include <mutex>
+
 #include "fo_step.cuh"
 
 namespace fo {
@@ -264,4 +266,98 @@ extern "C" int fo_selftest(int32_t which, int64_t arg, uint64_t* mismatches, voi
   }
   cudaFree(d);
   return rc;
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// fo_selftest_static: the same sweeps with the mismatch counters in a statically allocated
+// device array instead of a cudaMalloc'd one.
+//
+// Some hosts of this library must not allocate device memory at call time: a framework that
+// hands the whole GPU to its own allocator up front, a serving process that forbids
+// cudaMalloc after start-up because its implicit device-wide synchronisation stalls other
+// streams, or a plug-in sandbox in which the allocation calls are simply not permitted.  For
+// them the only scratch the self-checks need, a few 64-bit counters, lives in the array below.
+// Every GPU that loads the library carries these 32 bytes until the process exits.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned long long g_static_counters[FO_SELFTEST_STATIC_MAX_COUNTERS];
+
+namespace fo {
+
+// In host code `g_static_counters` is only a handle for the runtime, not an address a kernel
+// may dereference; the device address is asked for once per device, with that device current.
+static int static_counters_address(unsigned long long** out) {
+  static unsigned long long* cache[64] = {nullptr};
+  static std::mutex lock;
+  std::lock_guard<std::mutex> guard(lock);
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(FO_ERR_CUDA, "fo_selftest_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return fail(FO_ERR_UNSUPPORTED, "fo_selftest_static: device ordinal %d beyond 63", dev);
+  if (cache[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_counters);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(FO_ERR_CUDA, "fo_selftest_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    cache[dev] = static_cast<unsigned long long*>(p);
+  }
+  *out = cache[dev];
+  return FO_OK;
+}
+
+// dispatch of one sweep onto counters at `d` (used by fo_selftest_static only)
+static int launch_sweep(int32_t which, int64_t arg, unsigned long long* d, cudaStream_t s) {
+  const int grid = 148 * 8, block = 256;
+  volatile float one_src = 1.0f;
+  const float one = one_src;
+  switch (which) {
+    case FO_SELFTEST_SQRT: selftest_sqrt<<<grid, block, 0, s>>>(one, d); return FO_OK;
+    case FO_SELFTEST_SOFTSIGN: selftest_softsign<<<grid, block, 0, s>>>(one, d); return FO_OK;
+    case FO_SELFTEST_GROUP_DIV:
+      selftest_group_div<<<grid, block, 0, s>>>(one, (unsigned long long)(arg > 0 ? arg : 1) * 1000000ull, d);
+      return FO_OK;
+    case FO_SELFTEST_CODE_TABLES: selftest_code_tables<<<64, block, 0, s>>>(d); return FO_OK;
+    case FO_SELFTEST_RCP: selftest_rcp<<<grid, block, 0, s>>>(d); return FO_OK;
+    case FO_SELFTEST_PACKED: selftest_packed<<<grid, block, 0, s>>>(one, 1000000000ull, d); return FO_OK;
+    case FO_SELFTEST_RECONSTRUCT:
+    case FO_SELFTEST_SPLIT: {
+      const int pdt = (int)(arg / 100), eb = (int)(arg % 100);
+#define X(P, E)                                                                                  \
+  if (pdt == P && eb == E) {                                                                     \
+    if (which == FO_SELFTEST_RECONSTRUCT) selftest_reconstruct<P, E><<<grid, block, 0, s>>>(one, d); \
+    else selftest_split<P, E><<<grid, block, 0, s>>>(one, d);                                    \
+    return FO_OK;                                                                                \
+  }
+      X(FO_BF16, 8) X(FO_BF16, 16) X(FO_F16, 8) X(FO_F16, 16)
+#undef X
+      return fail(FO_ERR_INVALID_ARG, "fo_selftest_static: arg %lld names no (dtype, ecc) pair", (long long)arg);
+    }
+    default: return fail(FO_ERR_INVALID_ARG, "fo_selftest_static: unknown test %d", which);
+  }
+}
+
+}  // namespace fo
+
+extern "C" int fo_selftest_static(int32_t which, int64_t arg, uint64_t* counters, uint32_t n_counters, void* cuda_stream) {
+  if (counters == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_selftest_static: null result pointer");
+  if (n_counters == 0) return fail(FO_ERR_INVALID_ARG, "fo_selftest_static: n_counters is 0");
+  if (n_counters > FO_SELFTEST_STATIC_MAX_COUNTERS)
+    return fail(FO_ERR_TOO_LARGE, "fo_selftest_static: %u counters asked for, the static scratch holds %d", n_counters,
+                FO_SELFTEST_STATIC_MAX_COUNTERS);
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  unsigned long long* d = nullptr;
+  int rc = static_counters_address(&d);
+  if (rc != FO_OK) return rc;
+  // the array keeps what the previous call left: counters must start from zero
+  cudaError_t e = cudaMemsetAsync(d, 0, FO_SELFTEST_STATIC_MAX_COUNTERS * sizeof(unsigned long long), s);
+  if (e != cudaSuccess) return fail(FO_ERR_CUDA, "fo_selftest_static: cudaMemsetAsync: %s", cudaGetErrorString(e));
+  rc = launch_sweep(which, arg, d, s);
+  if (rc != FO_OK) return rc;
+  e = cudaGetLastError();
+  unsigned long long h[FO_SELFTEST_STATIC_MAX_COUNTERS] = {0};
+  if (e == cudaSuccess) e = cudaMemcpyAsync(h, d, sizeof(h), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return fail(FO_ERR_CUDA, "fo_selftest_static: %s", cudaGetErrorString(e));
+  for (uint32_t i = 0; i < n_counters; ++i) counters[i] = h[i];
+  return FO_OK;
 }

@@ -165,6 +165,30 @@ int fo_reconstruct(const void* param_lp, const void* ecc, float* theta, int32_t 
 #define FO_SELFTEST_RCP 6         /* reciprocal of every fp32 in [1e-30, 1e30]; arg 0 = variant in use, 1 / 2 = one / two correction steps */
 int fo_selftest(int32_t which, int64_t arg, uint64_t* mismatches, void* cuda_stream);
 
+/*
+ * fo_selftest without any allocation (no counterpart in the reference).
+ *
+ * Meant for hosts that may not allocate device memory when they call into the library: the
+ * GPU's memory belongs to the embedding framework's own allocator, or cudaMalloc is banned
+ * after start-up because it synchronises the whole device, or the allocation entry points
+ * are not reachable from the sandbox the plug-in runs in.  The counters the sweeps need live
+ * in a static device array of FO_SELFTEST_STATIC_MAX_COUNTERS 64-bit words (32 bytes, held
+ * by every GPU that loads the library until the process exits); the call uses no cudaMalloc,
+ * cudaFree or other allocating routine.
+ *
+ * Writes the first n_counters counters of the sweep to `counters` (host): counter 0 is what
+ * fo_selftest reports by default; FO_SELFTEST_RCP fills three, FO_SELFTEST_PACKED two.
+ * n_counters above FO_SELFTEST_STATIC_MAX_COUNTERS is refused with FO_ERR_TOO_LARGE.
+ *
+ * The first call on a device looks up the array's device address (with that device current)
+ * and caches it; make that first call before starting any stream capture.  All calls share
+ * the one array, which is zeroed at the start of each call: calls that overlap on the same
+ * GPU (different streams or threads) race on it and must be serialised by the caller.  Like
+ * fo_selftest, the call synchronises the stream before it returns.
+ */
+#define FO_SELFTEST_STATIC_MAX_COUNTERS 4
+int fo_selftest_static(int32_t which, int64_t arg, uint64_t* counters, uint32_t n_counters, void* cuda_stream);
+
 int fo_version(void);
 const char* fo_status_string(int status);
 const char* fo_last_error(void);
