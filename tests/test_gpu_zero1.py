@@ -1,0 +1,110 @@
+"""ZeRO-1 on GPUs: one rank must equal the plain tx.step; two NCCL ranks (when two GPUs are
+visible) must equal one rank bit for bit when every rank holds the same gradients."""
+
+import os
+import socket
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _params(device):
+    import torch
+
+    g = torch.Generator(device="cpu").manual_seed(0)
+    return {
+        "emb": (torch.randn(3000, 70, generator=g) * 0.02).to(torch.bfloat16).to(device),
+        "layers": [{"w": (torch.randn(640, 65, generator=g) * 0.02).to(torch.bfloat16).to(device), "norm": torch.ones(65, device=device)}
+                   for _ in range(3)],
+        "bias": torch.zeros(7, device=device),
+    }
+
+
+def _grads(step, device):
+    import torch
+
+    g = torch.Generator(device="cpu").manual_seed(100 + step)
+    return {
+        "emb": (torch.randn(3000, 70, generator=g) * 1e-3).to(torch.bfloat16).to(device),
+        "layers": [{"w": (torch.randn(640, 65, generator=g) * 1e-3).to(torch.bfloat16).to(device),
+                    "norm": (torch.randn(65, generator=g) * 1e-3).to(device)} for _ in range(3)],
+        "bias": (torch.randn(7, generator=g) * 1e-3).to(device),
+    }
+
+
+HP = dict(learning_rate=1e-3, weight_decay=1e-2, master_weight_bits=32)
+
+
+def test_one_rank_equals_plain_step():
+    import torch
+
+    import flashoptim_jax_b200 as fo
+    from flashoptim_jax_b200 import tree
+    from flashoptim_jax_b200.zero1 import Zero1Optimizer
+
+    dev = torch.device("cuda", 0)
+    z = Zero1Optimizer("adamw", _params(dev), **HP)
+    tx = fo.flash_adamw(donate=True, **HP)
+    params = _params(dev)
+    state = tx.init(params)
+    for t in range(3):
+        z.step(_grads(t, dev))
+        params, state = tx.step(params, state, _grads(t, dev))
+    torch.cuda.synchronize()
+    for a, b in zip(tree.tree_leaves(z.params), tree.tree_leaves(params)):
+        assert torch.equal(a, b)
+    zs = z.gather_state()
+    for name in ("mu", "nu", "ecc"):
+        for a, b in zip(tree.tree_leaves(zs[name]), tree.tree_leaves(getattr(state, name))):
+            assert a.dtype == b.dtype and torch.equal(a.cpu(), b.cpu())
+
+
+def _worker(rank, world, port, out):
+    import torch
+    import torch.distributed as dist
+
+    from flashoptim_jax_b200 import tree
+    from flashoptim_jax_b200.zero1 import Zero1Optimizer
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        z = Zero1Optimizer("adamw", _params(dev), **HP)
+        for t in range(3):
+            z.step(_grads(t, dev))
+        torch.cuda.synchronize()
+        state = z.gather_state(dst=0)
+        if rank == 0:
+            torch.save({"params": [p.cpu() for p in tree.tree_leaves(z.params)], "state": [s.cpu() for s in tree.tree_leaves(state)]}, out)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_nccl_ranks_equal_one_rank(tmp_path):
+    import torch
+    import torch.multiprocessing as mp
+
+    from flashoptim_jax_b200 import tree
+    from flashoptim_jax_b200.zero1 import Zero1Optimizer
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    dev = torch.device("cuda", 0)
+    single = Zero1Optimizer("adamw", _params(dev), **HP)
+    for t in range(3):
+        single.step(_grads(t, dev))
+    want_p = [p.cpu() for p in tree.tree_leaves(single.params)]
+    want_s = [s.cpu() for s in tree.tree_leaves(single.gather_state())]
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    out = str(tmp_path / "r0.pt")
+    mp.spawn(_worker, args=(2, port, out), nprocs=2, join=True)
+    got = torch.load(out, weights_only=False)
+    for a, b in zip(got["params"], want_p):
+        assert torch.equal(a, b)
+    for a, b in zip(got["state"], want_s):
+        assert a.dtype == b.dtype and torch.equal(a, b)
