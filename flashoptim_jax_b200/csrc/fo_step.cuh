@@ -302,19 +302,6 @@ FO_DEVI uint32_t pack2(float lo, float hi) {
   }
 }
 
-// per-element IEEE conversions kept out of line: they only run for unusual values
-template <int PDT, int ECC_BITS>
-__device__ __noinline__ float reconstruct_slow(uint32_t bits, int e) {
-  return ieee::reconstruct<PDT, ECC_BITS>(bits, e);
-}
-template <int PDT, int ECC_BITS>
-__device__ __noinline__ int ecc_slow(float theta) {
-  uint32_t bits;
-  int e;
-  ieee::split<PDT, ECC_BITS>(theta, bits, e);
-  return e;
-}
-
 FO_DEVI float group_max(float a) {
   a = fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, 1));
   return fmaxf(a, __shfl_xor_sync(0xFFFFFFFFu, a, 2));
@@ -421,10 +408,11 @@ FO_DEVI float maxabs8(const float2 (&x)[4]) {
 FO_DEVI uint32_t byte_of(uint32_t w, int k) { return __byte_perm(w, 0u, 0x4440u | (uint32_t)k); }
 
 template <int OPT, int PDT, int ECC_BITS, int STATE>
-FO_DEVI void hot_unpack(const Raw<OPT, PDT, ECC_BITS, STATE>& r, const int gdt, const float* lut_m, const float* lut_v,
+FO_DEVI bool hot_unpack(const Raw<OPT, PDT, ECC_BITS, STATE>& r, const int gdt, const float* lut_m, const float* lut_v,
                         const float one, Unpacked& u) {
   using namespace fast2;
   const float2 one2 = sp(one);
+  bool rare = false;
   if (gdt == FO_F32) pairs_of(r.g0, r.g1, u.g);
   else if (gdt == FO_BF16) pairs_of16<FO_BF16>(r.g0, u.g);
   else pairs_of16<FO_F16>(r.g0, u.g);
@@ -449,20 +437,11 @@ FO_DEVI void hot_unpack(const Raw<OPT, PDT, ECC_BITS, STATE>& r, const int gdt, 
 #pragma unroll
         for (int k = 0; k < 8; ++k) e[k] = (int)(signed char)((w[k >> 2] >> (8 * (k & 3))) & 0xFFu);
       }
-      bool ordinary = true;
-      if constexpr (PDT == FO_BF16) ordinary = minabs8(u.old_lp) >= fast::Ordinary<PDT>::kMin;
-      if (ordinary) {
+      // values too small for the exponent-field shortcut send the whole piece to the IEEE path later
+      if constexpr (PDT == FO_BF16) rare = !(minabs8(u.old_lp) >= fast::Ordinary<PDT>::kMin);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          u.theta[k] = reconstruct_ordinary2<PDT, ECC_BITS>(u.old_lp[k], mk((float)e[2 * k], (float)e[2 * k + 1]), one2);
-      } else {
-        const uint32_t w[4] = {r.p0.x, r.p0.y, r.p0.z, r.p0.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          u.theta[k].x = reconstruct_slow<PDT, ECC_BITS>(w[k] & 0xFFFFu, e[2 * k]);
-          u.theta[k].y = reconstruct_slow<PDT, ECC_BITS>(w[k] >> 16, e[2 * k + 1]);
-        }
-      }
+      for (int k = 0; k < 4; ++k)
+        u.theta[k] = reconstruct_ordinary2<PDT, ECC_BITS>(u.old_lp[k], mk((float)e[2 * k], (float)e[2 * k + 1]), one2);
     }
   }
 
@@ -485,12 +464,18 @@ FO_DEVI void hot_unpack(const Raw<OPT, PDT, ECC_BITS, STATE>& r, const int gdt, 
     pairs_of(r.m0, r.m1, u.m);
     if constexpr (OPT == FO_OPT_ADAM) pairs_of(r.v0, r.v1, u.v);
   }
+  return rare;
 }
 
 FO_DEVI float sign_of(float x);
 
+// Second half of a hot chunk: update, split, requantize, store.  The arithmetic is straight-line;
+// every condition under which a shortcut is not proven exact only raises `rare`.  Nothing is
+// stored until the end: if any lane of the warp saw a rare value, the warp's 256 elements are
+// redone from memory by the IEEE path (cold_chunk), otherwise the results are written.
 template <int OPT, int PDT, int ECC_BITS, int STATE>
-FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const unsigned long long i0, const float one, Unpacked& u) {
+FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const unsigned long long base, const float one,
+                        bool rare, Unpacked& u, const float* lut_m, const float* lut_v) {
   using namespace fast2;
   const float2 one2 = sp(one);
   float2 (&g)[4] = u.g;
@@ -499,10 +484,12 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const unsigned long long
   float2 (&m)[4] = u.m;
   float2 (&v)[4] = u.v;
   float2 root[4];
+  const unsigned long long i0 = base + (unsigned long long)threadIdx.x * kPiece;
   const unsigned long long gi = i0 >> 5;
 
   // ---- update --------------------------------------------------------------------------------------
   const bool decoupled = (h.flags & FO_FLAG_DECOUPLED_WD) != 0;
+  float am_lane = 0.0f, av_lane = 1.0f;
   if constexpr (OPT == FO_OPT_ADAM) {
     // flashoptim_jax/adamw.py:95-106
     if (!decoupled) {
@@ -518,27 +505,20 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const unsigned long long
 #pragma unroll
       for (int k = 0; k < 4; ++k) theta[k] = mul2(theta[k], sp(h.decay));
     }
-    // Ranges in which the packed square root and division are exact: second moment in
-    // [1e-30, 1e30] (so the denominator lies in [eps, 1e20]) and numerator magnitudes in [2^-40, 2^60].
-    const float num_lo = fmul(minabs8(m), fabsf(h.lr_bc1)), num_hi = fmul(maxabs8(m), fabsf(h.lr_bc1));
-    if (min8(v) >= 1.0e-30f && max8(v) <= 1.0e30f && num_lo >= 9.094947e-13f && num_hi <= 1.1529215e18f) {
-      const float2 nsq = sp(-h.sqrt_bc2), rsq = sp(h.rcp_sqrt_bc2), eps = sp(h.eps), nlr = sp(-h.lr_bc1);
+    const float2 nsq = sp(-h.sqrt_bc2), rsq = sp(h.rcp_sqrt_bc2), eps = sp(h.eps), nlr = sp(-h.lr_bc1);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        root[k] = sqrt_core2(v[k]);
-        const float2 den = add2(div_by_rcp2(root[k], nsq, rsq), eps);
-        theta[k] = sum2(div2(mul2(nlr, m[k]), den), theta[k], one2);  // theta - (lr/bc1 * m) / den
-      }
-    } else {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        root[k] = mk(fsqrt(v[k].x), fsqrt(v[k].y));
-        const float dx = fadd(fast::div_by_rcp(root[k].x, h.sqrt_bc2, h.rcp_sqrt_bc2), h.eps);
-        const float dy = fadd(fast::div_by_rcp(root[k].y, h.sqrt_bc2, h.rcp_sqrt_bc2), h.eps);
-        theta[k].x = fsub(theta[k].x, fdiv(fmul(h.lr_bc1, m[k].x), dx));
-        theta[k].y = fsub(theta[k].y, fdiv(fmul(h.lr_bc1, m[k].y), dy));
-      }
+    for (int k = 0; k < 4; ++k) {
+      root[k] = sqrt_core2(v[k]);
+      const float2 den = add2(div_by_rcp2(root[k], nsq, rsq), eps);
+      theta[k] = sum2(div2(mul2(nlr, m[k]), den), theta[k], one2);  // theta - (lr/bc1 * m) / den
     }
+    // Ranges in which the packed square root and division are exact: second moment in [1e-30, 1e30]
+    // (so the denominator lies in [eps, 1e20]) and numerator magnitudes in [2^-40, 2^60].
+    am_lane = maxabs8(m);
+    av_lane = max8(root);
+    const float lrb = fabsf(h.lr_bc1);
+    rare = rare || !(min8(v) >= 1.0e-30f) || !(av_lane <= 1.0e15f) || !(fmul(minabs8(m), lrb) >= 9.094947e-13f) ||
+           !(fmul(am_lane, lrb) <= 1.1529215e18f);
   } else if constexpr (OPT == FO_OPT_LION) {
     // flashoptim_jax/momentum_kernel.py:77-79 or flashoptim_jax/lion.py:50-52
     float2 upd[4];
@@ -560,6 +540,7 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const unsigned long long
     }
 #pragma unroll
     for (int k = 0; k < 4; ++k) theta[k] = sum2(mul2(theta[k], sp(h.decay)), mul2(sp(-h.lr), upd[k]), one2);  // theta*decay - lr*upd
+    am_lane = maxabs8(m);
   } else {
     // flashoptim_jax/momentum_kernel.py:74-75,80-86; flashoptim_jax/sgd.py:45-63
     if (!decoupled) {
@@ -576,6 +557,7 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const unsigned long long
 #pragma unroll
         for (int k = 0; k < 4; ++k) g[k] = m[k];
       }
+      am_lane = maxabs8(m);
     }
     if (decoupled) {
 #pragma unroll
@@ -585,16 +567,15 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const unsigned long long
     for (int k = 0; k < 4; ++k) theta[k] = sum2(mul2(sp(-h.lr), g[k]), theta[k], one2);  // theta - lr*dir
   }
 
-  // ---- parameter (+ECC) back ---------------------------------------------------------------------
+  // ---- parameter (+ECC) in stored form --------------------------------------------------------------
+  uint32_t nw[4] = {0, 0, 0, 0};
+  uint4 ecc_out = make_uint4(0, 0, 0, 0);
   if constexpr (PDT == FO_F32) {
     if (h.flags & FO_FLAG_LP_DELTA) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) theta[k] = add2(old_lp[k], fma2(old_lp[k], sp(-1.0f), theta[k]));
     }
-    __stcs((float4*)((float*)L.param + i0), make_float4(theta[0].x, theta[0].y, theta[1].x, theta[1].y));
-    __stcs((float4*)((float*)L.param + i0) + 1, make_float4(theta[2].x, theta[2].y, theta[3].x, theta[3].y));
   } else {
-    uint32_t nw[4];
     float2 new_lp[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -603,28 +584,15 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const unsigned long long
     }
     if constexpr (ECC_BITS != 0) {
       int ne[8];
-      bool ordinary = true;
-      if constexpr (PDT == FO_BF16) ordinary = minabs8(new_lp) >= fast::Ordinary<PDT>::kMin;
-      if (ordinary) {
+      if constexpr (PDT == FO_BF16) rare = rare || !(minabs8(new_lp) >= fast::Ordinary<PDT>::kMin);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) ecc_ordinary2<PDT, ECC_BITS>(theta[k], new_lp[k], ne[2 * k], ne[2 * k + 1]);
-      } else {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          ne[2 * k] = ecc_slow<PDT, ECC_BITS>(theta[k].x);
-          ne[2 * k + 1] = ecc_slow<PDT, ECC_BITS>(theta[k].y);
-        }
-      }
+      for (int k = 0; k < 4; ++k) ecc_ordinary2<PDT, ECC_BITS>(theta[k], new_lp[k], ne[2 * k], ne[2 * k + 1]);
       if constexpr (ECC_BITS == 16) {
-        uint4 o;
-        o.x = pack_halves(ne[0], ne[1]); o.y = pack_halves(ne[2], ne[3]);
-        o.z = pack_halves(ne[4], ne[5]); o.w = pack_halves(ne[6], ne[7]);
-        __stcs((uint4*)((short*)L.ecc + i0), o);
+        ecc_out.x = pack_halves(ne[0], ne[1]); ecc_out.y = pack_halves(ne[2], ne[3]);
+        ecc_out.z = pack_halves(ne[4], ne[5]); ecc_out.w = pack_halves(ne[6], ne[7]);
       } else {
-        uint2 o;
-        o.x = pack_bytes(ne[0], ne[1], ne[2], ne[3]);
-        o.y = pack_bytes(ne[4], ne[5], ne[6], ne[7]);
-        __stcs((uint2*)((signed char*)L.ecc + i0), o);
+        ecc_out.x = pack_bytes(ne[0], ne[1], ne[2], ne[3]);
+        ecc_out.y = pack_bytes(ne[4], ne[5], ne[6], ne[7]);
       }
     }
     if (h.flags & FO_FLAG_LP_DELTA) {
@@ -638,10 +606,44 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const unsigned long long
         nw[k] = pack2<PDT>(sum.x, sum.y);
       }
     }
-    __stcs((uint4*)((unsigned short*)L.param + i0), make_uint4(nw[0], nw[1], nw[2], nw[3]));
   }
 
-  // ---- moments back ------------------------------------------------------------------------------
+  // ---- moments in stored form ------------------------------------------------------------------------
+  uint2 mq = make_uint2(0, 0), vq = make_uint2(0, 0);
+  float am = 0.0f, av = 0.0f;
+  if constexpr (STATE == FO_STATE_QUANT) {
+    am = group_max(am_lane);
+    rare = rare || !(am >= 1.0e-12f && am <= 1.0e30f);
+    uint32_t q[8];
+    const float2 nam = sp(-am), rm2 = sp(fast::rcp_rn(am));
+#pragma unroll
+    for (int k = 0; k < 4; ++k) softsign_code_bits2(div_by_rcp2(m[k], nam, rm2), one2, q[2 * k], q[2 * k + 1]);
+    mq.x = pack_bytes(q[0], q[1], q[2], q[3]);
+    mq.y = pack_bytes(q[4], q[5], q[6], q[7]);
+    if constexpr (OPT == FO_OPT_ADAM) {
+      av = group_max(av_lane);
+      rare = rare || !(av >= 1.0e-12f && av <= 1.0e30f);
+      const float2 nav = sp(-av), rv2 = sp(fast::rcp_rn(av));
+#pragma unroll
+      for (int k = 0; k < 4; ++k) quant_v_bits2(root[k], nav, rv2, one2, q[2 * k], q[2 * k + 1]);
+      vq.x = pack_bytes(q[0], q[1], q[2], q[3]);
+      vq.y = pack_bytes(q[4], q[5], q[6], q[7]);
+    }
+  }
+
+  // ---- one decision per warp, then the stores ----------------------------------------------------------
+  if (__any_sync(0xFFFFFFFFu, rare)) {
+    cold_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, lut_m, lut_v);
+    return;
+  }
+  if constexpr (PDT == FO_F32) {
+    __stcs((float4*)((float*)L.param + i0), make_float4(theta[0].x, theta[0].y, theta[1].x, theta[1].y));
+    __stcs((float4*)((float*)L.param + i0) + 1, make_float4(theta[2].x, theta[2].y, theta[3].x, theta[3].y));
+  } else {
+    __stcs((uint4*)((unsigned short*)L.param + i0), make_uint4(nw[0], nw[1], nw[2], nw[3]));
+    if constexpr (ECC_BITS == 16) __stcs((uint4*)((short*)L.ecc + i0), ecc_out);
+    if constexpr (ECC_BITS == 8) __stcs((uint2*)((signed char*)L.ecc + i0), make_uint2(ecc_out.x, ecc_out.y));
+  }
   if constexpr (STATE == FO_STATE_FULL) {
     __stcs((float4*)((float*)L.mu + i0), make_float4(m[0].x, m[0].y, m[1].x, m[1].y));
     __stcs((float4*)((float*)L.mu + i0) + 1, make_float4(m[2].x, m[2].y, m[3].x, m[3].y));
@@ -650,51 +652,11 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const unsigned long long
       __stcs((float4*)((float*)L.nu + i0) + 1, make_float4(v[2].x, v[2].y, v[3].x, v[3].y));
     }
   } else if constexpr (STATE == FO_STATE_QUANT) {
-    const bool floor_mode = (h.flags & FO_FLAG_SCALE_FLOOR) != 0;
     const bool writer = (threadIdx.x & 3) == 0;
-    const float am = group_max(maxabs8(m));
-    float av = 1.0f;
-    if constexpr (OPT == FO_OPT_ADAM) av = group_max(max8(root));
-    uint32_t qm[8], qv[8];
-    if (am >= 1.0e-12f && am <= 1.0e30f && av >= 1.0e-12f && av <= 1.0e30f) {
-      const float rm = fast::rcp_rn(am);
-      const float2 nam = sp(-am), rm2 = sp(rm);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) softsign_code_bits2(div_by_rcp2(m[k], nam, rm2), one2, qm[2 * k], qm[2 * k + 1]);
-      if constexpr (OPT == FO_OPT_ADAM) {
-        const float rv = fast::rcp_rn(av);
-        const float2 nav = sp(-av), rv2 = sp(rv);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) quant_v_bits2(root[k], nav, rv2, one2, qv[2 * k], qv[2 * k + 1]);
-      }
-    } else {
-      const float sm = ieee::safe_scale(am, floor_mode);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        qm[2 * k] = (uint32_t)ieee::quant_m(m[k].x, sm);
-        qm[2 * k + 1] = (uint32_t)ieee::quant_m(m[k].y, sm);
-      }
-      if constexpr (OPT == FO_OPT_ADAM) {
-        const float sv = ieee::safe_scale(av, floor_mode);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          qv[2 * k] = (uint32_t)ieee::quant_v(root[k].x, sv);
-          qv[2 * k + 1] = (uint32_t)ieee::quant_v(root[k].y, sv);
-        }
-      }
-    }
-    {
-      uint2 o;
-      o.x = pack_bytes(qm[0], qm[1], qm[2], qm[3]);
-      o.y = pack_bytes(qm[4], qm[5], qm[6], qm[7]);
-      __stcs((uint2*)((signed char*)L.mu + i0), o);
-      if (writer) ((__half*)L.mu_scales)[gi] = __float2half_rn(am);
-    }
+    __stcs((uint2*)((signed char*)L.mu + i0), mq);
+    if (writer) ((__half*)L.mu_scales)[gi] = __float2half_rn(am);
     if constexpr (OPT == FO_OPT_ADAM) {
-      uint2 o;
-      o.x = pack_bytes(qv[0], qv[1], qv[2], qv[3]);
-      o.y = pack_bytes(qv[4], qv[5], qv[6], qv[7]);
-      __stcs((uint2*)((unsigned char*)L.nu + i0), o);
+      __stcs((uint2*)((unsigned char*)L.nu + i0), vq);
       if (writer) ((__half*)L.nu_scales)[gi] = __float2half_rn(av);
     }
   }
@@ -768,11 +730,11 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
     if (cur.hot && hyper_ok) {
       if (!loaded) hot_load<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], p.grad_dtype, cur.base + toff, raw);
       Unpacked u;
-      hot_unpack<OPT, PDT, ECC_BITS, STATE>(raw, p.grad_dtype, lut_m, lut_v, p.one, u);
+      const bool rare = hot_unpack<OPT, PDT, ECC_BITS, STATE>(raw, p.grad_dtype, lut_m, lut_v, p.one, u);
       // the next chunk's loads fly while this one is computed
       loaded = more && nxt.hot;
       if (loaded) hot_load<OPT, PDT, ECC_BITS, STATE>(p.leaf[nxt.leaf], p.grad_dtype, nxt.base + toff, raw);
-      hot_finish<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], h, cur.base + toff, p.one, u);
+      hot_finish<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], h, p.grad_dtype, cur.base, p.one, rare, u, lut_m, lut_v);
     } else {
       cold_chunk<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], h, p.grad_dtype, cur.base, lut_m, lut_v);
       loaded = false;
