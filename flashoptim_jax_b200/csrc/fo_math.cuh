@@ -370,7 +370,7 @@ FO_DEVI f2 rcp2(f2 d, f2 nd) {
 
 // RN(a/d) per component, proven: y = RN(1/d) (checked exhaustively), first correction
 // gives a faithful quotient, the second the correctly rounded one (Markstein).  Needs
-// d in [1e-30, 1e30], |a| in [2^-40, 2^60], |a/d| in [2^-110, 2^110].
+// d in [1e-12, 2^47], |a| in [2^-70, 2^60] (so |a/d| stays a normal number and both residuals are exact).
 FO_DEVI f2 div2(f2 a, f2 d) {
   f2 nd = mul2(d, sp(-1.0f));
   f2 y = rcp2(d, nd);

@@ -138,13 +138,13 @@ __global__ void selftest_group_div(const float one, unsigned long long pairs, un
     }
     // Adam denominator: sqrt_bc2 in [2^-16, 2), eps in [1e-12, 1], root anywhere in [0, 1e30]
     float sq = __uint_as_float(((111u + r1 % 17u) << 23) | (r0 & 0x7FFFFFu));
-    float eps = __uint_as_float(((87u + r3 % 41u) << 23) | (r2 & 0x7FFFFFu));
+    float eps = __uint_as_float(((87u + r3 % 40u) << 23) | (r2 & 0x7FFFFFu));
     float root = (r0 & 4u) ? x : __uint_as_float(((r2 >> 3) % 227u << 23) | (r1 & 0x7FFFFFu));
     {
-      // the update division: numerator magnitude in [2^-40, 2^60], denominator in [1e-12, 1e20]
-      const float num = __uint_as_float((r3 & 0x80000000u) | ((87u + r1 % 101u) << 23) | (r2 & 0x7FFFFFu));
-      const float den = __uint_as_float(((88u + r0 % 105u) << 23) | (r3 & 0x7FFFFFu));
-      const float den2 = __uint_as_float(((88u + r2 % 105u) << 23) | (r1 & 0x7FFFFFu));
+      // the update division: numerator magnitude in [2^-70, 2^60], denominator in [2^-39, 2^47]
+      const float num = __uint_as_float((r3 & 0x80000000u) | ((57u + r1 % 131u) << 23) | (r2 & 0x7FFFFFu));
+      const float den = __uint_as_float(((88u + r0 % 86u) << 23) | (r3 & 0x7FFFFFu));
+      const float den2 = __uint_as_float(((88u + r2 % 86u) << 23) | (r1 & 0x7FFFFFu));
       const float2 q = fast2::div2(make_float2(num, -num), make_float2(den, den2));
       bad += !same_float(q.x, fdiv(num, den)) || !same_float(q.y, fdiv(-num, den2));
     }

@@ -83,7 +83,7 @@ struct StepParams {
 // (quotient + eps): for sqrt(nu) >= 2^-100 the shortcut is exact, below it the quotient is
 // under half an ULP of eps either way.
 __host__ __device__ inline bool adam_is_tame(float eps, float sqrt_bc2) {
-  return eps >= 1.0e-12f && eps <= 1.0e12f && sqrt_bc2 >= 1.52587890625e-05f && sqrt_bc2 <= 2.0f;
+  return eps >= 1.0e-12f && eps <= 1.0f && sqrt_bc2 >= 1.52587890625e-05f && sqrt_bc2 <= 2.0f;
 }
 
 struct Hyp {
@@ -374,7 +374,6 @@ FO_DEVI void hot_load(const DevLeaf& L, const int gdt, const unsigned long long 
 // (pair k holds elements 2k and 2k+1 of the thread's piece)
 struct Unpacked {
   float2 g[4];
-  float2 old_lp[4];   // stored param as fp32
   float2 theta[4];    // master weight
   float2 m[4], v[4];
 };
@@ -419,13 +418,12 @@ FO_DEVI bool hot_unpack(const Raw<OPT, PDT, ECC_BITS, STATE>& r, const int gdt, 
 
   if constexpr (PDT == FO_F32) {
     pairs_of(r.p0, r.p1, u.theta);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) u.old_lp[k] = u.theta[k];
   } else {
-    pairs_of16<PDT>(r.p0, u.old_lp);
+    float2 old_lp[4];  // stored param as fp32
+    pairs_of16<PDT>(r.p0, old_lp);
     if constexpr (ECC_BITS == 0) {
 #pragma unroll
-      for (int k = 0; k < 4; ++k) u.theta[k] = u.old_lp[k];
+      for (int k = 0; k < 4; ++k) u.theta[k] = old_lp[k];
     } else {
       int e[8];
       if constexpr (ECC_BITS == 16) {
@@ -438,10 +436,10 @@ FO_DEVI bool hot_unpack(const Raw<OPT, PDT, ECC_BITS, STATE>& r, const int gdt, 
         for (int k = 0; k < 8; ++k) e[k] = (int)(signed char)((w[k >> 2] >> (8 * (k & 3))) & 0xFFu);
       }
       // values too small for the exponent-field shortcut send the whole piece to the IEEE path later
-      if constexpr (PDT == FO_BF16) rare = !(minabs8(u.old_lp) >= fast::Ordinary<PDT>::kMin);
+      if constexpr (PDT == FO_BF16) rare = !(minabs8(old_lp) >= fast::Ordinary<PDT>::kMin);
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        u.theta[k] = reconstruct_ordinary2<PDT, ECC_BITS>(u.old_lp[k], mk((float)e[2 * k], (float)e[2 * k + 1]), one2);
+        u.theta[k] = reconstruct_ordinary2<PDT, ECC_BITS>(old_lp[k], mk((float)e[2 * k], (float)e[2 * k + 1]), one2);
     }
   }
 
@@ -480,7 +478,6 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uns
   const float2 one2 = sp(one);
   float2 (&g)[4] = u.g;
   float2 (&theta)[4] = u.theta;
-  float2 (&old_lp)[4] = u.old_lp;
   float2 (&m)[4] = u.m;
   float2 (&v)[4] = u.v;
   float2 root[4];
@@ -512,12 +509,12 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uns
       const float2 den = add2(div_by_rcp2(root[k], nsq, rsq), eps);
       theta[k] = sum2(div2(mul2(nlr, m[k]), den), theta[k], one2);  // theta - (lr/bc1 * m) / den
     }
-    // Ranges in which the packed square root and division are exact: second moment in [1e-30, 1e30]
-    // (so the denominator lies in [eps, 1e20]) and numerator magnitudes in [2^-40, 2^60].
+    // Ranges in which the packed square root and division are exact: second moment >= 1e-30 with
+    // sqrt <= 2^30 (so the denominator lies in [eps, 2^47]) and numerator magnitudes in [2^-70, 2^60].
     am_lane = maxabs8(m);
     av_lane = max8(root);
     const float lrb = fabsf(h.lr_bc1);
-    rare = rare || !(min8(v) >= 1.0e-30f) || !(av_lane <= 1.0e15f) || !(fmul(minabs8(m), lrb) >= 9.094947e-13f) ||
+    rare = rare || !(min8(v) >= 1.0e-30f) || !(av_lane <= 1.0737418e9f) || !(fmul(minabs8(m), lrb) >= 8.4703295e-22f) ||
            !(fmul(am_lane, lrb) <= 1.1529215e18f);
   } else if constexpr (OPT == FO_OPT_LION) {
     // flashoptim_jax/momentum_kernel.py:77-79 or flashoptim_jax/lion.py:50-52
@@ -570,12 +567,7 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uns
   // ---- parameter (+ECC) in stored form --------------------------------------------------------------
   uint32_t nw[4] = {0, 0, 0, 0};
   uint4 ecc_out = make_uint4(0, 0, 0, 0);
-  if constexpr (PDT == FO_F32) {
-    if (h.flags & FO_FLAG_LP_DELTA) {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) theta[k] = add2(old_lp[k], fma2(old_lp[k], sp(-1.0f), theta[k]));
-    }
-  } else {
+  if constexpr (PDT != FO_F32) {
     float2 new_lp[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -593,17 +585,6 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uns
       } else {
         ecc_out.x = pack_bytes(ne[0], ne[1], ne[2], ne[3]);
         ecc_out.y = pack_bytes(ne[4], ne[5], ne[6], ne[7]);
-      }
-    }
-    if (h.flags & FO_FLAG_LP_DELTA) {
-      // adamw.py:411,415,463: param + lp(new_lp - param), both roundings to the param dtype
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 d = fma2(old_lp[k], sp(-1.0f), new_lp[k]);
-        float2 dr;
-        unpack2<PDT>(pack2<PDT>(d.x, d.y), dr.x, dr.y);
-        const float2 sum = add2(old_lp[k], dr);
-        nw[k] = pack2<PDT>(sum.x, sum.y);
       }
     }
   }
@@ -721,7 +702,9 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
     if (cur.leaf != l_loaded) {
       h = load_hyper<OPT>(p.hyper[p.hyper_of[cur.leaf]]);
       l_loaded = cur.leaf;
-      if constexpr (OPT == FO_OPT_ADAM) hyper_ok = (h.flags & kFlagTameAdam) != 0;
+      // the CPU-path parameter hand-back (FO_FLAG_LP_DELTA) needs the old stored value to the end: IEEE path only
+      hyper_ok = (h.flags & FO_FLAG_LP_DELTA) == 0;
+      if constexpr (OPT == FO_OPT_ADAM) hyper_ok = hyper_ok && (h.flags & kFlagTameAdam) != 0;
     }
     const uint32_t cn = c + gridDim.x;
     const bool more = cn < total;
