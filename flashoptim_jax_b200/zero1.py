@@ -13,10 +13,13 @@ bit-identical to the single-device step whenever the averaged gradient is.
 
 Layout.  All leaves of one parameter dtype live in one flat buffer, each leaf starting at a
 multiple of 32 elements (a group boundary; also 16-byte alignment for the vector path).
-The buffer is padded to world_size * shard, shard a multiple of 2048 elements (one kernel
-chunk).  Rank r owns flat[r*shard, (r+1)*shard); a leaf that straddles ranks is cut at
-group boundaries.  The parameter and gradient trees handed back to the caller are views
-into these buffers, so no copy sits between backward and the collectives.
+The buffer is cut into n_slices slices of world_size pieces, a piece being a multiple of 2048
+elements (one kernel chunk): rank r owns piece r of every slice; a leaf that straddles
+pieces is cut at group boundaries.  One slice is the unit of the collectives, so that the
+step of slice s runs while slice s+1 is still being reduce-scattered and the all-gathers
+queue up behind the reduce-scatters on the communication stream.  The parameter and
+gradient trees handed back to the caller are views into the flat buffers, so no copy sits
+between backward and the collectives.
 """
 
 from __future__ import annotations
@@ -46,6 +49,7 @@ class Segment(NamedTuple):
     lo: int       # first element of the leaf in this segment (multiple of 32)
     hi: int       # one past the last element
     offset: int   # position of `lo` in the rank's shard
+    slice: int = 0  # which slice of the bucket the segment lies in
 
 
 class BucketLayout(NamedTuple):
@@ -53,29 +57,46 @@ class BucketLayout(NamedTuple):
     leaves: List[int]          # leaf indices in this bucket, in tree order
     starts: List[int]          # start of each leaf in the flat buffer
     sizes: List[int]
-    total: int                 # padded length = world_size * shard
-    shard: int
-    segments: List[List[Segment]]  # per rank
+    total: int                 # padded length = n_slices * world_size * piece
+    shard: int                 # elements one rank owns = n_slices * piece
+    segments: List[List[Segment]]  # per rank, ordered by slice
+    piece: int = 0             # elements of one rank in one slice
+    n_slices: int = 1
 
 
-def plan_bucket(dtype: torch.dtype, leaf_ids: List[int], sizes: List[int], world_size: int) -> BucketLayout:
-    """Place leaves in a flat buffer and cut it into world_size equal shards."""
+SLICE_TARGET = 1 << 24  # aim for pieces of at least this many elements before cutting a bucket into more slices
+MAX_SLICES = 8
+
+
+def plan_bucket(dtype: torch.dtype, leaf_ids: List[int], sizes: List[int], world_size: int,
+                n_slices: Optional[int] = None) -> BucketLayout:
+    """Place leaves in a flat buffer and cut it into n_slices x world_size pieces."""
     starts, pos = [], 0
     for n in sizes:
         starts.append(pos)
         pos += -(-n // LEAF_ALIGN) * LEAF_ALIGN
-    shard = -(-pos // (world_size * SHARD_ALIGN)) * SHARD_ALIGN if pos else SHARD_ALIGN
-    total = shard * world_size
+    if n_slices is None:
+        n_slices = 1 if world_size == 1 else max(1, min(MAX_SLICES, pos // (world_size * SLICE_TARGET)))
+    piece = -(-pos // (world_size * n_slices * SHARD_ALIGN)) * SHARD_ALIGN if pos else SHARD_ALIGN
+    slice_len = piece * world_size
     segments: List[List[Segment]] = []
     for r in range(world_size):
-        lo_r, hi_r = r * shard, (r + 1) * shard
         segs = []
-        for leaf, start, n in zip(leaf_ids, starts, sizes):
-            lo, hi = max(start, lo_r), min(start + n, hi_r)
-            if lo < hi:
-                segs.append(Segment(leaf, lo - start, hi - start, lo - lo_r))
+        for sl in range(n_slices):
+            lo_r = sl * slice_len + r * piece
+            hi_r = lo_r + piece
+            for leaf, start, n in zip(leaf_ids, starts, sizes):
+                lo, hi = max(start, lo_r), min(start + n, hi_r)
+                if lo < hi:
+                    segs.append(Segment(leaf, lo - start, hi - start, sl * piece + lo - lo_r, sl))
         segments.append(segs)
-    return BucketLayout(dtype, list(leaf_ids), starts, list(sizes), total, shard, segments)
+    return BucketLayout(dtype, list(leaf_ids), starts, list(sizes), slice_len * n_slices, piece * n_slices, segments, piece, n_slices)
+
+
+def flat_position(layout: BucketLayout, rank: int, offset: int) -> int:
+    """Position in the flat buffer of element `offset` of rank `rank`'s shard."""
+    sl, within = divmod(offset, layout.piece)
+    return (sl * (layout.total // layout.shard) + rank) * layout.piece + within
 
 
 class ShardState(NamedTuple):
@@ -132,9 +153,11 @@ class Zero1Optimizer:
     hparams     the keyword arguments of the matching flash_* factory (param_groups included)
     group       torch.distributed process group (None = default group; no group = one rank)
     step_fn     how a list of LeafWork is executed; the default launches the CUDA kernels
+    n_slices    slices per bucket (None: chosen from the bucket size; 1 disables the pipeline)
     """
 
-    def __init__(self, optimizer: str, params: Any, *, group=None, step_fn: Optional[StepFn] = None, **hparams):
+    def __init__(self, optimizer: str, params: Any, *, group=None, step_fn: Optional[StepFn] = None,
+                 n_slices: Optional[int] = None, **hparams):
         self.kind = optimizer
         if optimizer not in ("adamw", "adam", "lion", "sgd", "sgdw"):
             raise ValueError(f"unknown optimizer {optimizer!r}")
@@ -180,7 +203,7 @@ class Zero1Optimizer:
         param_views: List[Optional[torch.Tensor]] = [None] * len(leaves)
         grad_views: List[Optional[torch.Tensor]] = [None] * len(leaves)
         for dtype, ids in by_dtype.items():
-            layout = plan_bucket(dtype, ids, [leaves[i].numel() for i in ids], self.world_size)
+            layout = plan_bucket(dtype, ids, [leaves[i].numel() for i in ids], self.world_size, n_slices)
             flat_p = torch.zeros(layout.total, dtype=dtype, device=device)
             flat_g = torch.zeros(layout.total, dtype=dtype, device=device)
             for i, start in zip(ids, layout.starts):
@@ -259,7 +282,7 @@ class Zero1Optimizer:
             # buffers never move: only the hyper-parameters change from step to step
             out = []
             cache: Dict[int, Any] = {}
-            for w, leaf in self._static_work:
+            for w, leaf, _, _ in self._static_work:
                 config = self.configs[leaf]
                 key = id(config)
                 if key not in cache:
@@ -268,10 +291,9 @@ class Zero1Optimizer:
                 out.append(w._replace(hyper=cache[key]))
             return out
         work: List[eng.LeafWork] = []
-        leaf_of: List[int] = []
+        meta: List[Tuple[int, int, int]] = []
         dev_index = self.device.index if self.device.type == "cuda" else -1
         for b, layout in enumerate(self.buckets):
-            base = self.rank * layout.shard
             flat_p, g_shard = self.flat_params[b], self.grad_shards[b]
             for s, seg in enumerate(layout.segments[self.rank]):
                 config = self.configs[seg.leaf]
@@ -286,20 +308,67 @@ class Zero1Optimizer:
                     state_kind = _lib.FO_STATE_FULL
                 ecc_bits = 0 if st.ecc is None else st.ecc.element_size() * 8
                 bucket = (dev_index, DTYPE_CODE[layout.dtype], DTYPE_CODE[layout.dtype], ecc_bits, state_kind, 32)
+                at = flat_position(layout, self.rank, seg.offset)
                 work.append(eng.LeafWork(
-                    bucket, g_shard[seg.offset:seg.offset + n], flat_p[base + seg.offset: base + seg.offset + n],
+                    bucket, g_shard[seg.offset:seg.offset + n], flat_p[at:at + n],
                     st.ecc, st.mu, st.mu_scales, st.nu, st.nu_scales, self._hyper(config, lr, self.count + 1)))
-                leaf_of.append(seg.leaf)
-        self._static_work = list(zip(work, leaf_of))
+                meta.append((seg.leaf, b, seg.slice))
+        self._static_work = [(w, leaf, b, sl) for w, (leaf, b, sl) in zip(work, meta)]
         return work
 
+    def _slices(self) -> List[Tuple[int, int]]:
+        """(bucket, slice) pairs in the order the collectives are issued."""
+        return [(b, sl) for b, layout in enumerate(self.buckets) for sl in range(layout.n_slices)]
+
+    def _rs_args(self, b: int, sl: int):
+        layout = self.buckets[b]
+        slice_len = layout.piece * self.world_size
+        return (self.grad_shards[b][sl * layout.piece:(sl + 1) * layout.piece],
+                self.flat_grads[b][sl * slice_len:(sl + 1) * slice_len])
+
+    def _ag_args(self, b: int, sl: int):
+        layout = self.buckets[b]
+        slice_len = layout.piece * self.world_size
+        return self.flat_params[b][sl * slice_len:(sl + 1) * slice_len], layout.piece
+
     def reduce_scatter_grads(self) -> None:
-        for b, layout in enumerate(self.buckets):
-            _reduce_scatter_mean(self.grad_shards[b], self.flat_grads[b], self.group, self.world_size)
+        for b, sl in self._slices():
+            out, full = self._rs_args(b, sl)
+            _reduce_scatter_mean(out, full, self.group, self.world_size)
 
     def all_gather_params(self) -> None:
-        for b, layout in enumerate(self.buckets):
-            _all_gather_inplace(self.flat_params[b], layout.shard, self.group, self.world_size)
+        for b, sl in self._slices():
+            full, piece = self._ag_args(b, sl)
+            _all_gather_inplace(full, piece, self.group, self.world_size)
+
+    def _pipelined(self) -> bool:
+        return (self.world_size > 1 and dist.get_backend(self.group) == "nccl" and self.device.type == "cuda"
+                and any(layout.n_slices > 1 for layout in self.buckets))
+
+    def _step_pipelined(self) -> None:
+        """Slice by slice: the kernels of slice s run while the reduce-scatter of slice s+1 is in flight, and
+        each all-gather is queued as soon as its slice is updated (NCCL serialises them behind the
+        reduce-scatters on its own stream).  Device-side ordering only; the host never waits."""
+        work = self.local_work()
+        per_slice: Dict[Tuple[int, int], List[eng.LeafWork]] = {}
+        for w, (_, _, b, sl) in zip(work, self._static_work):
+            per_slice.setdefault((b, sl), []).append(w)
+        order = self._slices()
+        rs = []
+        for b, sl in order:
+            out, full = self._rs_args(b, sl)
+            rs.append(dist.reduce_scatter_tensor(out, full, op=dist.ReduceOp.AVG, group=self.group, async_op=True))
+        ag = []
+        for handle, (b, sl) in zip(rs, order):
+            handle.wait()  # the compute stream waits for this slice's gradients
+            items = per_slice.get((b, sl))
+            if items:
+                self._step_fn(self.opt_code, items)
+            full, piece = self._ag_args(b, sl)
+            mine = full[self.rank * piece:(self.rank + 1) * piece]
+            ag.append(dist.all_gather_into_tensor(full, mine, group=self.group, async_op=True))
+        for handle in ag:
+            handle.wait()
 
     def step(self, grads: Any = None) -> Any:
         """One optimizer step.  `grads` (optional) is copied into the flat gradient buffers;
@@ -310,6 +379,10 @@ class Zero1Optimizer:
                 raise ValueError(f"{self.name} gradients must match parameter structure")
             for mine, theirs in zip(pytree.tree_leaves(self.grads), leaves):
                 mine.copy_(as_tensor(theirs).to(mine.dtype).reshape(mine.shape))
+        if self._pipelined():
+            self._step_pipelined()
+            self.count += 1
+            return self.params
         self.reduce_scatter_grads()
         self._step_fn(self.opt_code, self.local_work())
         self.count += 1

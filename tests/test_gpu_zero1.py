@@ -72,7 +72,7 @@ def _worker(rank, world, port, out):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        z = Zero1Optimizer("adamw", _params(dev), **HP)
+        z = Zero1Optimizer("adamw", _params(dev), n_slices=3, **HP)  # three slices: the pipelined path
         for t in range(3):
             z.step(_grads(t, dev))
         torch.cuda.synchronize()

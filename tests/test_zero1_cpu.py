@@ -21,16 +21,19 @@ from flashoptim_jax_b200.zero1 import LEAF_ALIGN, SHARD_ALIGN, Zero1Optimizer, p
 
 def test_plan_bucket_covers_every_element_once_on_group_boundaries():
     sizes = [5, 4096, 33, 100000, 2048, 1]
-    for world in (1, 2, 3, 4, 8):
-        lay = plan_bucket(torch.bfloat16, list(range(len(sizes))), sizes, world)
-        assert lay.shard % SHARD_ALIGN == 0 and lay.total == lay.shard * world
+    from flashoptim_jax_b200.zero1 import flat_position
+
+    for world, n_slices in ((1, 1), (2, 1), (3, 2), (4, 4), (8, 3), (2, None)):
+        lay = plan_bucket(torch.bfloat16, list(range(len(sizes))), sizes, world, n_slices)
+        assert lay.piece % SHARD_ALIGN == 0 and lay.shard == lay.piece * lay.n_slices and lay.total == lay.shard * world
         assert all(s % LEAF_ALIGN == 0 for s in lay.starts)
         seen = {i: [] for i in range(len(sizes))}
         for r, segs in enumerate(lay.segments):
             for seg in segs:
                 assert 0 <= seg.offset and seg.offset + (seg.hi - seg.lo) <= lay.shard
+                assert seg.offset // lay.piece == seg.slice == (seg.offset + seg.hi - seg.lo - 1) // lay.piece
                 assert seg.lo % 32 == 0  # a cut inside a leaf falls on a group boundary
-                assert lay.starts[seg.leaf] + seg.lo == r * lay.shard + seg.offset
+                assert lay.starts[seg.leaf] + seg.lo == flat_position(lay, r, seg.offset)
                 seen[seg.leaf].append((seg.lo, seg.hi))
         for i, n in enumerate(sizes):
             spans = sorted(seen[i])
@@ -77,8 +80,8 @@ def _make_grads(step: int):
     }
 
 
-def _run(kind, hp, steps=3):
-    z = Zero1Optimizer(kind, _make_params(), step_fn=oracle_step_fn, **hp)
+def _run(kind, hp, steps=3, n_slices=None):
+    z = Zero1Optimizer(kind, _make_params(), step_fn=oracle_step_fn, n_slices=n_slices, **hp)
     for t in range(steps):
         z.step(_make_grads(t))
     return z
@@ -88,7 +91,7 @@ def _worker(rank, world, port, kind, hp, out):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        z = _run(kind, hp)
+        z = _run(kind, hp, n_slices=3 if kind == "adamw" else None)  # adamw: three slices per bucket
         state = z.gather_state(dst=0)
         local = z.local_state_dict()
         z.load_local_state_dict(local)  # round trip of the per-rank shard
