@@ -200,7 +200,7 @@ def run_ours(args):
     kernel_ms = {}  # per (param dtype code) -> list of launch durations
     pending = []
 
-    def timed_launch(opt, work):
+    def timed_launch(opt, work, peers=None):
         by_bucket = {}
         for w in work:
             by_bucket.setdefault(w.bucket, []).append(w)
@@ -208,19 +208,19 @@ def run_ours(args):
         for bucket, items in by_bucket.items():
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            calls += eng.launch(opt, items)
+            calls += eng.launch(opt, items, peers)
             e1.record()
             pending.append((bucket[1], sum(w.param.numel() for w in items), e0, e1))
         return calls
 
     launches = [0]
 
-    def counting_launch(opt, work):
-        n = timed_launch(opt, work)
+    def counting_launch(opt, work, peers=None):
+        n = timed_launch(opt, work, peers)
         launches[0] += n
         return n
 
-    zero = Zero1Optimizer("adamw", params, step_fn=counting_launch, **HPARAMS)
+    zero = Zero1Optimizer("adamw", params, step_fn=counting_launch, fused_allgather=(world > 1 and not args.nccl_allgather), **HPARAMS)
     del params
     torch.cuda.empty_cache()
     ggen = torch.Generator(device=device)
@@ -344,6 +344,7 @@ def finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline
             "data": "synthetic",
             "config": {"workload": args.workload, "leaves": len(shapes), "params": total_params, "optimizer": "flash_adamw",
                        **HPARAMS, "grad_dtype": "bf16", "parallelism": "single" if world == 1 else f"zero1x{world}",
+                       "allgather": None if world == 1 else ("nccl" if args.nccl_allgather else "fused into the step kernel (peer stores)"),
                        "l2": "working set per step (>= 14 B/param) exceeds the 126 MB L2, no flush needed"},
             "roofline": roofline, "cpu_baseline": base, "e2e": e2e, "gpu_launches": n_launch, "clocks": clocks,
             "hbm_gbs_whole_step": total_params * BYTES_PER_PARAM_BF16_ECC16 / (ms_per_step * 1e-3) / 1e9,
@@ -362,6 +363,7 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="llama3_8b")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (used for ncu captures)")
+    ap.add_argument("--nccl-allgather", action="store_true", help="N > 1: NCCL all-gather after the step instead of peer stores inside it")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

@@ -79,8 +79,12 @@ def _ptr(t: Optional[torch.Tensor]) -> int:
     return 0 if t is None else t.data_ptr()
 
 
-def launch(opt: int, work: List[LeafWork]) -> int:
-    """Issue one fo_step per bucket (per <=16 hyper sets); returns the number of calls."""
+def launch(opt: int, work: List[LeafWork], peer_param_offsets: Optional[List[int]] = None) -> int:
+    """Issue one fo_step per bucket (per <=16 hyper sets); returns the number of calls.
+
+    peer_param_offsets: byte distances from every param address to the same element of each peer
+    GPU's replica; when given, the kernel also stores the updated parameters there."""
+    peers = np.asarray(peer_param_offsets or [], dtype=np.int64)
     buckets: Dict[Tuple[Any, ...], List[LeafWork]] = {}
     for w in work:
         buckets.setdefault(w.bucket, []).append(w)
@@ -113,6 +117,7 @@ def launch(opt: int, work: List[LeafWork]) -> int:
                 struct_size=ctypes.sizeof(_lib.FoStepDesc), opt=opt, param_dtype=pdt, grad_dtype=gdt, ecc_bits=ecc_bits,
                 state=state, group_size=group_size, n_leaves=len(pending), n_hypers=len(hyper_index),
                 leaves=leaves.ctypes.data, hypers=hypers.ctypes.data,
+                n_peers=len(peers), peer_param_offsets=peers.ctypes.data if len(peers) else None,
             )
             device = torch.device("cuda", dev_index)
             with torch.cuda.device(device):

@@ -19,6 +19,7 @@ FO_OPT_ADAM, FO_OPT_LION, FO_OPT_SGD = 0, 1, 2
 FO_STATE_QUANT, FO_STATE_FULL, FO_STATE_NONE = 0, 1, 2
 FO_FLAG_DECOUPLED_WD, FO_FLAG_NESTEROV, FO_FLAG_LION_LERP, FO_FLAG_LP_DELTA, FO_FLAG_SCALE_FLOOR = 1, 2, 4, 8, 16
 FO_MAX_HYPERS = 16
+FO_MAX_PEERS = 7
 FO_SELFTEST_STATIC_MAX_COUNTERS = 4
 FO_SELFTEST_SQRT, FO_SELFTEST_SOFTSIGN, FO_SELFTEST_RECONSTRUCT, FO_SELFTEST_SPLIT = 0, 1, 2, 3
 FO_SELFTEST_GROUP_DIV, FO_SELFTEST_CODE_TABLES, FO_SELFTEST_RCP, FO_SELFTEST_PACKED = 4, 5, 6, 7
@@ -58,6 +59,7 @@ class FoStepDesc(ctypes.Structure):
         ("ecc_bits", ctypes.c_int32), ("state", ctypes.c_int32), ("group_size", ctypes.c_int32),
         ("n_leaves", ctypes.c_uint32), ("n_hypers", ctypes.c_uint32),
         ("leaves", ctypes.c_void_p), ("hypers", ctypes.c_void_p),
+        ("n_peers", ctypes.c_uint32), ("reserved", ctypes.c_uint32), ("peer_param_offsets", ctypes.c_void_p),
     ]
 
 

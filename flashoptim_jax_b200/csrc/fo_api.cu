@@ -95,6 +95,9 @@ extern "C" int fo_step(const FoStepDesc* d, void* cuda_stream) {
     if (d->group_size > kGenericTile) return fail(FO_ERR_UNSUPPORTED, "fo_step: group_size %d > %d", d->group_size, kGenericTile);
     generic = d->group_size != 32;
   }
+  if (d->n_peers > (uint32_t)kMaxPeers) return fail(FO_ERR_TOO_LARGE, "fo_step: %u peers, at most %d", d->n_peers, kMaxPeers);
+  if (d->n_peers > 0 && d->peer_param_offsets == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_step: n_peers without peer_param_offsets");
+  if (d->n_peers > 0 && generic) return fail(FO_ERR_UNSUPPORTED, "fo_step: peer replicas need group_size 32");
   LaunchFn launch = find_launcher(d->opt, d->param_dtype, d->ecc_bits, d->state, generic);
   if (launch == nullptr) return fail(FO_ERR_UNSUPPORTED, "fo_step: no kernel for this combination");
 
@@ -126,6 +129,8 @@ extern "C" int fo_step(const FoStepDesc* d, void* cuda_stream) {
   p.grad_dtype = d->grad_dtype;
   p.group_size = d->state == FO_STATE_QUANT ? d->group_size : 32;
   p.one = 1.0f;
+  p.peers.n = (int)d->n_peers;
+  for (uint32_t r = 0; r < d->n_peers; ++r) p.peers.delta[r] = (long long)d->peer_param_offsets[r];
 
   int count = 0;
   unsigned long long blocks = 0;

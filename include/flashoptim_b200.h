@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define FO_ABI_VERSION 1
+#define FO_ABI_VERSION 2
 
 /* status codes */
 #define FO_OK 0
@@ -119,7 +119,18 @@ typedef struct FoStepDesc {
   uint32_t n_hypers;
   const FoLeaf* leaves;   /* host table */
   const FoHyper* hypers;  /* host table */
+  /* ZeRO-1 all-gather folded into the step (no counterpart in the reference, which replicates
+   * state and all-reduces gradients, examples/train_gpt2_pretrain.py:412-441): every updated
+   * parameter vector is also stored at (param address + peer_param_offsets[r]) for r < n_peers,
+   * i.e. into the same element of peer r's replica of the parameter array.  The offsets are byte
+   * distances between peer-mapped allocations (host table, at most FO_MAX_PEERS); plain stores,
+   * the kernel never waits on a peer.  The caller orders the launch after the peers' last reads
+   * of their replicas and makes the peers wait for this stream before they read again. */
+  uint32_t n_peers;
+  uint32_t reserved;
+  const int64_t* peer_param_offsets;
 } FoStepDesc;
+#define FO_MAX_PEERS 7
 
 /* Replaces pl.pallas_call(...) of _fused_flash_adamw_leaf_impl (adamw.py:225-353) and of
  * fused_momentum_leaf_impl (momentum_kernel.py:183-302), for a whole pytree at once. */

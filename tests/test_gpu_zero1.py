@@ -60,7 +60,7 @@ def test_one_rank_equals_plain_step():
             assert a.dtype == b.dtype and torch.equal(a.cpu(), b.cpu())
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, fused=False):
     import torch
     import torch.distributed as dist
 
@@ -72,7 +72,8 @@ def _worker(rank, world, port, out):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        z = Zero1Optimizer("adamw", _params(dev), n_slices=3, **HP)  # three slices: the pipelined path
+        # three slices exercise the pipelined NCCL path; fused: all-gather by peer stores inside the kernel
+        z = Zero1Optimizer("adamw", _params(dev), n_slices=1 if fused else 3, fused_allgather=fused, **HP)
         for t in range(3):
             z.step(_grads(t, dev))
         torch.cuda.synchronize()
@@ -83,7 +84,8 @@ def _worker(rank, world, port, out):
         dist.destroy_process_group()
 
 
-def test_two_nccl_ranks_equal_one_rank(tmp_path):
+@pytest.mark.parametrize("fused", [False, True], ids=["nccl_allgather", "fused_allgather"])
+def test_two_nccl_ranks_equal_one_rank(tmp_path, fused):
     import torch
     import torch.multiprocessing as mp
 
@@ -102,7 +104,7 @@ def test_two_nccl_ranks_equal_one_rank(tmp_path):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     out = str(tmp_path / "r0.pt")
-    mp.spawn(_worker, args=(2, port, out), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, out, fused), nprocs=2, join=True)
     got = torch.load(out, weights_only=False)
     for a, b in zip(got["params"], want_p):
         assert torch.equal(a, b)
