@@ -340,6 +340,28 @@ FO_DEVI float max3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
+// Per-lane repairs of the second-chance path (REPAIR = true below), kept out of line: they run only
+// for lanes that hold a value outside the range a shortcut is proven for (zeros, subnormals, huge
+// values) and redo that stage with IEEE operations.
+template <int PDT, int ECC_BITS>
+__device__ __noinline__ float repair_master(uint32_t bits, int e) {
+  return ieee::reconstruct<PDT, ECC_BITS>(bits, e);
+}
+template <int PDT, int ECC_BITS>
+__device__ __noinline__ int repair_ecc(float theta) {
+  uint32_t bits;
+  int e;
+  ieee::split<PDT, ECC_BITS>(theta, bits, e);
+  return e;
+}
+// root = sqrt(v); returns theta - (lr_bc1 * m) / (root / sqrt_bc2 + eps)   (adamw.py:104-106)
+static __device__ __noinline__ float repair_adam(float v, float m, float theta, float lr_bc1, float sqrt_bc2, float eps, float& root) {
+  root = fsqrt(v);
+  return fsub(theta, fdiv(fmul(lr_bc1, m), fadd(fdiv(root, sqrt_bc2), eps)));
+}
+static __device__ __noinline__ uint32_t repair_code_m(float x, float safe) { return (uint32_t)ieee::quant_m(x, safe); }
+static __device__ __noinline__ uint32_t repair_code_v(float r, float safe) { return (uint32_t)ieee::quant_v(r, safe); }
+
 // what one thread loads for one chunk: its 8 elements of every stream, still packed
 template <int OPT, int PDT, int ECC_BITS, int STATE>
 struct Raw {
@@ -423,7 +445,10 @@ FO_DEVI float maxabs8(const float2 (&x)[4]) {
 // byte k of a word as an index
 FO_DEVI uint32_t byte_of(uint32_t w, int k) { return __byte_perm(w, 0u, 0x4440u | (uint32_t)k); }
 
-template <int OPT, int PDT, int ECC_BITS, int STATE>
+// REPAIR = false: straight-line code; returns true when a value lies outside a shortcut's proven
+// range (the results are then not to be stored).  REPAIR = true: the affected lane redoes the stage
+// with IEEE operations and the results are always good.
+template <bool REPAIR, int OPT, int PDT, int ECC_BITS, int STATE>
 FO_DEVI bool hot_unpack(const Raw<OPT, PDT, ECC_BITS, STATE>& r, const int gdt, const float* lut_m, const float* lut_v,
                         const float one, Unpacked& u) {
   using namespace fast2;
@@ -452,11 +477,23 @@ FO_DEVI bool hot_unpack(const Raw<OPT, PDT, ECC_BITS, STATE>& r, const int gdt, 
 #pragma unroll
         for (int k = 0; k < 8; ++k) e[k] = (int)(signed char)((w[k >> 2] >> (8 * (k & 3))) & 0xFFu);
       }
-      // values too small for the exponent-field shortcut send the whole piece to the IEEE path later
-      if constexpr (PDT == FO_BF16) rare = !(minabs8(old_lp) >= fast::Ordinary<PDT>::kMin);
 #pragma unroll
       for (int k = 0; k < 4; ++k)
         u.theta[k] = reconstruct_ordinary2<PDT, ECC_BITS>(old_lp[k], mk((float)e[2 * k], (float)e[2 * k + 1]), one2);
+      if constexpr (PDT == FO_BF16) {
+        // a value too small for the exponent-field shortcut (zero included)
+        if (!(minabs8(old_lp) >= fast::Ordinary<PDT>::kMin)) {
+          rare = true;
+          if constexpr (REPAIR) {
+            const uint32_t w[4] = {r.p0.x, r.p0.y, r.p0.z, r.p0.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              u.theta[k].x = repair_master<PDT, ECC_BITS>(w[k] & 0xFFFFu, e[2 * k]);
+              u.theta[k].y = repair_master<PDT, ECC_BITS>(w[k] >> 16, e[2 * k + 1]);
+            }
+          }
+        }
+      }
     }
   }
 
@@ -484,11 +521,19 @@ FO_DEVI bool hot_unpack(const Raw<OPT, PDT, ECC_BITS, STATE>& r, const int gdt, 
 
 FO_DEVI float sign_of(float x);
 
-// Second half of a hot chunk: update, split, requantize, store.  The arithmetic is straight-line;
-// every condition under which a shortcut is not proven exact only raises `rare`.  Nothing is
-// stored until the end: if any lane of the warp saw a rare value, the warp's 256 elements are
-// redone from memory by the IEEE path (cold_chunk), otherwise the results are written.
 template <int OPT, int PDT, int ECC_BITS, int STATE>
+__device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const unsigned long long base,
+                                        const float one, const float* lut_m, const float* lut_v, const Peers& peers);
+
+// Second half of a hot chunk: update, split, requantize, store.  Each stage runs its packed
+// shortcut unconditionally.
+// REPAIR = false (first pass): a value outside the range a shortcut is proven for only raises
+// `rare`; nothing is stored until the end, and if any lane of the warp saw such a value the warp's
+// 256 elements are redone from memory by warm_chunk, otherwise the results are written.
+// REPAIR = true (warm_chunk): the lane that holds such a value (exact zeros are the common case:
+// untouched rows, padding, zero gradients) redoes that stage with IEEE operations, then stores.
+// The stored bits are those of the IEEE path in every case.
+template <bool REPAIR, int OPT, int PDT, int ECC_BITS, int STATE>
 FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const unsigned long long base, const float one,
                         bool rare, Unpacked& u, const float* lut_m, const float* lut_v, const Peers& peers) {
   using namespace fast2;
@@ -520,19 +565,31 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uns
       for (int k = 0; k < 4; ++k) theta[k] = mul2(theta[k], sp(h.decay));
     }
     const float2 nsq = sp(-h.sqrt_bc2), rsq = sp(h.rcp_sqrt_bc2), eps = sp(h.eps), nlr = sp(-h.lr_bc1);
+    float2 tn[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       root[k] = sqrt_core2(v[k]);
       const float2 den = add2(div_by_rcp2(root[k], nsq, rsq), eps);
-      theta[k] = sum2(div2(mul2(nlr, m[k]), den), theta[k], one2);  // theta - (lr/bc1 * m) / den
+      tn[k] = sum2(div2(mul2(nlr, m[k]), den), theta[k], one2);  // theta - (lr/bc1 * m) / den
     }
     // Ranges in which the packed square root and division are exact: second moment >= 1e-30 with
     // sqrt <= 2^30 (so the denominator lies in [eps, 2^47]) and numerator magnitudes in [2^-70, 2^60].
     am_lane = maxabs8(m);
-    av_lane = max8(root);
     const float lrb = fabsf(h.lr_bc1);
-    rare = rare || !(min8(v) >= 1.0e-30f) || !(av_lane <= 1.0737418e9f) || !(fmul(minabs8(m), lrb) >= 8.4703295e-22f) ||
-           !(fmul(am_lane, lrb) <= 1.1529215e18f);
+    if (!(min8(v) >= 1.0e-30f) || !(max8(v) <= 1.0e18f) || !(fmul(minabs8(m), lrb) >= 8.4703295e-22f) ||
+        !(fmul(am_lane, lrb) <= 1.1529215e18f)) {
+      rare = true;
+      if constexpr (REPAIR) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          tn[k].x = repair_adam(v[k].x, m[k].x, theta[k].x, h.lr_bc1, h.sqrt_bc2, h.eps, root[k].x);
+          tn[k].y = repair_adam(v[k].y, m[k].y, theta[k].y, h.lr_bc1, h.sqrt_bc2, h.eps, root[k].y);
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) theta[k] = tn[k];
+    av_lane = max8(root);
   } else if constexpr (OPT == FO_OPT_LION) {
     // flashoptim_jax/momentum_kernel.py:77-79 or flashoptim_jax/lion.py:50-52
     float2 upd[4];
@@ -593,9 +650,20 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uns
     }
     if constexpr (ECC_BITS != 0) {
       int ne[8];
-      if constexpr (PDT == FO_BF16) rare = rare || !(minabs8(new_lp) >= fast::Ordinary<PDT>::kMin);
 #pragma unroll
       for (int k = 0; k < 4; ++k) ecc_ordinary2<PDT, ECC_BITS>(theta[k], new_lp[k], ne[2 * k], ne[2 * k + 1]);
+      if constexpr (PDT == FO_BF16) {
+        if (!(minabs8(new_lp) >= fast::Ordinary<PDT>::kMin)) {
+          rare = true;
+          if constexpr (REPAIR) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              ne[2 * k] = repair_ecc<PDT, ECC_BITS>(theta[k].x);
+              ne[2 * k + 1] = repair_ecc<PDT, ECC_BITS>(theta[k].y);
+            }
+          }
+        }
+      }
       if constexpr (ECC_BITS == 16) {
         ecc_out.x = pack_halves(ne[0], ne[1]); ecc_out.y = pack_halves(ne[2], ne[3]);
         ecc_out.z = pack_halves(ne[4], ne[5]); ecc_out.w = pack_halves(ne[6], ne[7]);
@@ -610,30 +678,54 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uns
   uint2 mq = make_uint2(0, 0), vq = make_uint2(0, 0);
   float am = 0.0f, av = 0.0f;
   if constexpr (STATE == FO_STATE_QUANT) {
+    const bool floor_mode = (h.flags & FO_FLAG_SCALE_FLOOR) != 0;
     am = group_max(am_lane);
-    rare = rare || !(am >= 1.0e-12f && am <= 1.0e30f);
     uint32_t q[8];
     const float2 nam = sp(-am), rm2 = sp(fast::rcp_rn(am));
 #pragma unroll
     for (int k = 0; k < 4; ++k) softsign_code_bits2(div_by_rcp2(m[k], nam, rm2), one2, q[2 * k], q[2 * k + 1]);
+    if (!(am >= 1.0e-12f && am <= 1.0e30f)) {  // all-zero group, or a scale outside the reciprocal's range
+      rare = true;
+      if constexpr (REPAIR) {
+        const float safe = ieee::safe_scale(am, floor_mode);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          q[2 * k] = repair_code_m(m[k].x, safe);
+          q[2 * k + 1] = repair_code_m(m[k].y, safe);
+        }
+      }
+    }
     mq.x = pack_bytes(q[0], q[1], q[2], q[3]);
     mq.y = pack_bytes(q[4], q[5], q[6], q[7]);
     if constexpr (OPT == FO_OPT_ADAM) {
       av = group_max(av_lane);
-      rare = rare || !(av >= 1.0e-12f && av <= 1.0e30f);
       const float2 nav = sp(-av), rv2 = sp(fast::rcp_rn(av));
 #pragma unroll
       for (int k = 0; k < 4; ++k) quant_v_bits2(root[k], nav, rv2, one2, q[2 * k], q[2 * k + 1]);
+      if (!(av >= 1.0e-12f && av <= 1.0e30f)) {
+        rare = true;
+        if constexpr (REPAIR) {
+          const float safe = ieee::safe_scale(av, floor_mode);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            q[2 * k] = repair_code_v(root[k].x, safe);
+            q[2 * k + 1] = repair_code_v(root[k].y, safe);
+          }
+        }
+      }
       vq.x = pack_bytes(q[0], q[1], q[2], q[3]);
       vq.y = pack_bytes(q[4], q[5], q[6], q[7]);
     }
   }
 
-  // ---- one decision per warp, then the stores ----------------------------------------------------------
-  if (__any_sync(0xFFFFFFFFu, rare)) {
-    cold_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, lut_m, lut_v, peers);
-    return;
+  // ---- first pass: one decision per warp -----------------------------------------------------------------
+  if constexpr (!REPAIR) {
+    if (__any_sync(0xFFFFFFFFu, rare)) {
+      warm_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, one, lut_m, lut_v, peers);
+      return;
+    }
   }
+  // ---- stores ---------------------------------------------------------------------------------------------
   if constexpr (PDT == FO_F32) {
     const float4 lo = make_float4(theta[0].x, theta[0].y, theta[1].x, theta[1].y);
     const float4 hi = make_float4(theta[2].x, theta[2].y, theta[3].x, theta[3].y);
@@ -664,6 +756,19 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uns
       if (writer) ((__half*)L.nu_scales)[gi] = __float2half_rn(av);
     }
   }
+}
+
+// Second chance for a warp whose first pass met a value outside a shortcut's range: the same
+// packed arithmetic from a fresh load, with per-lane IEEE repairs.  About twice the cost of a
+// first pass for that warp, against about seven times for the scalar IEEE path.
+template <int OPT, int PDT, int ECC_BITS, int STATE>
+__device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const unsigned long long base,
+                                        const float one, const float* lut_m, const float* lut_v, const Peers& peers) {
+  Raw<OPT, PDT, ECC_BITS, STATE> raw;
+  hot_load<OPT, PDT, ECC_BITS, STATE>(L, gdt, base + (unsigned long long)threadIdx.x * kPiece, raw);
+  Unpacked u;
+  hot_unpack<true, OPT, PDT, ECC_BITS, STATE>(raw, gdt, lut_m, lut_v, one, u);
+  hot_finish<true, OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, one, false, u, lut_m, lut_v, peers);
 }
 
 // exact dequantization tables, one entry per code byte (built once per block)
@@ -736,11 +841,11 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
     if (cur.hot && hyper_ok) {
       if (!loaded) hot_load<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], p.grad_dtype, cur.base + toff, raw);
       Unpacked u;
-      const bool rare = hot_unpack<OPT, PDT, ECC_BITS, STATE>(raw, p.grad_dtype, lut_m, lut_v, p.one, u);
+      const bool rare = hot_unpack<false, OPT, PDT, ECC_BITS, STATE>(raw, p.grad_dtype, lut_m, lut_v, p.one, u);
       // the next chunk's loads fly while this one is computed
       loaded = more && nxt.hot;
       if (loaded) hot_load<OPT, PDT, ECC_BITS, STATE>(p.leaf[nxt.leaf], p.grad_dtype, nxt.base + toff, raw);
-      hot_finish<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], h, p.grad_dtype, cur.base, p.one, rare, u, lut_m, lut_v, p.peers);
+      hot_finish<false, OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], h, p.grad_dtype, cur.base, p.one, rare, u, lut_m, lut_v, p.peers);
     } else {
       cold_chunk<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], h, p.grad_dtype, cur.base, lut_m, lut_v, p.peers);
       loaded = false;
