@@ -145,23 +145,40 @@ extern "C" int fo_step(const FoStepDesc* d, void* cuda_stream) {
     if (e != cudaSuccess) return fail(FO_ERR_CUDA, "fo_step: launch failed: %s", cudaGetErrorString(e));
     return FO_OK;
   };
+  // The 32-group kernels address elements with 32-bit offsets: a longer leaf goes in as several
+  // leaves of 2^31 elements (a multiple of the chunk and of the group, so every piece keeps
+  // its alignment and its own whole groups).
+  const unsigned long long kMaxLeafElems = generic ? ~0ull : (1ull << 31);
+  const size_t grad_size = d->grad_dtype == FO_F32 ? 4 : 2, param_size = d->param_dtype == FO_F32 ? 4 : 2;
+  const size_t ecc_size = (size_t)d->ecc_bits / 8, moment_size = d->state == FO_STATE_FULL ? 4 : 1;
+  auto advance = [](const void* base, unsigned long long elems, size_t size) -> void* {
+    return base == nullptr ? nullptr : (void*)((const char*)base + elems * size);
+  };
   for (uint32_t i = 0; i < d->n_leaves; ++i) {
     const FoLeaf& L = d->leaves[i];
-    if (L.n == 0) continue;
-    const unsigned long long nb = (L.n + chunk - 1) / chunk;
-    if (nb > kMaxBlocks) return fail(FO_ERR_TOO_LARGE, "fo_step: leaf %u with %llu elements exceeds one launch", i, (unsigned long long)L.n);
-    if (count == kMaxLeaves || blocks + nb > kMaxBlocks) {
-      int rc = flush();
-      if (rc != FO_OK) return rc;
+    for (unsigned long long done = 0; done < L.n; done += kMaxLeafElems) {
+      const unsigned long long n = L.n - done < kMaxLeafElems ? L.n - done : kMaxLeafElems;
+      const unsigned long long nb = (n + chunk - 1) / chunk;
+      if (nb > kMaxBlocks) return fail(FO_ERR_TOO_LARGE, "fo_step: leaf %u with %llu elements exceeds one launch", i, (unsigned long long)L.n);
+      if (count == kMaxLeaves || blocks + nb > kMaxBlocks) {
+        int rc = flush();
+        if (rc != FO_OK) return rc;
+      }
+      DevLeaf& D = p.leaf[count];
+      D.grad = advance(L.grad, done, grad_size);
+      D.param = advance(L.param, done, param_size);
+      D.ecc = advance(L.ecc, done, ecc_size);
+      D.mu = advance(L.mu, done, moment_size);
+      D.nu = advance(L.nu, done, moment_size);
+      D.mu_scales = advance(L.mu_scales, done / 32, 2);
+      D.nu_scales = advance(L.nu_scales, done / 32, 2);
+      D.n = n;
+      p.first_block[count] = (uint32_t)blocks;
+      p.hyper_of[count] = (uint8_t)L.hyper;
+      p.aligned[count] = aligned16(D.grad) && aligned16(D.param) && aligned16(D.ecc) && aligned16(D.mu) && aligned16(D.nu);
+      blocks += nb;
+      ++count;
     }
-    DevLeaf& D = p.leaf[count];
-    D.grad = L.grad; D.param = L.param; D.ecc = L.ecc; D.mu = L.mu; D.mu_scales = L.mu_scales;
-    D.nu = L.nu; D.nu_scales = L.nu_scales; D.n = L.n;
-    p.first_block[count] = (uint32_t)blocks;
-    p.hyper_of[count] = (uint8_t)L.hyper;
-    p.aligned[count] = aligned16(L.grad) && aligned16(L.param) && aligned16(L.ecc) && aligned16(L.mu) && aligned16(L.nu);
-    blocks += nb;
-    ++count;
   }
   return flush();
 }

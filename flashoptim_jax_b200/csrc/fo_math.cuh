@@ -354,41 +354,51 @@ FO_DEVI float rsqrt_approx(float x) {
   return y;
 }
 
+// Packed operations take no negated operands, and a packed negation is a whole instruction.
+// The sequences below therefore carry signs through their intermediate values (rounding to
+// nearest is symmetric: RN(-x) == -RN(x)), so that every residual a - b*q is formed as an fma
+// of operands that already have the right signs.  Scalar negations feeding a special-function
+// unit are free (source modifier).
+
 // a / b given nb = -b and y = RN(1/b)
 FO_DEVI f2 div_by_rcp2(f2 a, f2 nb, f2 y) {
   f2 q0 = mul2(a, y);
   f2 r = fma2(nb, q0, a);
   return fma2(r, y, q0);
 }
-
-// RN(1/d) per component for d in [1e-30, 1e30]; nd = -d
-FO_DEVI f2 rcp2(f2 d, f2 nd) {
-  f2 y0 = mk(rcp_approx(d.x), rcp_approx(d.y));
-  f2 e = fma2(nd, y0, sp(1.0f));
-  return fma2(e, y0, y0);
+// a / b given na = -a, b and ny = -RN(1/b)
+FO_DEVI f2 div_negnum_by_rcp2(f2 na, f2 b, f2 ny) {
+  f2 q0 = mul2(na, ny);      // a*y
+  f2 nr = fma2(b, q0, na);   // b*q0 - a = -(a - b*q0)
+  return fma2(nr, ny, q0);   // q0 + (a - b*q0)*y
 }
 
-// RN(a/d) per component, proven: y = RN(1/d) (checked exhaustively), first correction
+// -RN(1/d) per component for d in [1e-30, 1e30]
+FO_DEVI f2 neg_rcp2(f2 d) {
+  f2 ny0 = mk(rcp_approx(-d.x), rcp_approx(-d.y));
+  f2 e = fma2(d, ny0, sp(1.0f));  // 1 - d*y0
+  return fma2(e, ny0, ny0);       // -(y0 + e*y0)
+}
+
+// RN(-a/d) per component, proven: y = RN(1/d) (checked exhaustively), first correction
 // gives a faithful quotient, the second the correctly rounded one (Markstein).  Needs
 // d in [1e-12, 2^47], |a| in [2^-70, 2^60] (so |a/d| stays a normal number and both residuals are exact).
-FO_DEVI f2 div2(f2 a, f2 d) {
-  f2 nd = mul2(d, sp(-1.0f));
-  f2 y = rcp2(d, nd);
-  f2 q = mul2(a, y);
-  f2 r = fma2(nd, q, a);
-  q = fma2(r, y, q);
-  r = fma2(nd, q, a);
-  return fma2(r, y, q);
+FO_DEVI f2 neg_div2(f2 a, f2 d) {
+  f2 ny = neg_rcp2(d);
+  f2 q = mul2(a, ny);        // -a*y
+  f2 nr = fma2(d, q, a);     // a + d*q = -((-a) - d*q)
+  q = fma2(nr, ny, q);
+  nr = fma2(d, q, a);
+  return fma2(nr, ny, q);
 }
 
-// sqrt per component for 1e-30 <= v < inf
-FO_DEVI f2 sqrt_core2(f2 v) {
-  f2 y = mk(rsqrt_approx(v.x), rsqrt_approx(v.y));
-  f2 r = mul2(v, y);
+// -sqrt(v) per component given nv = -v, for 1e-30 <= v < inf
+FO_DEVI f2 neg_sqrt_core2(f2 nv) {
+  f2 y = mk(rsqrt_approx(-nv.x), rsqrt_approx(-nv.y));
+  f2 nr = mul2(nv, y);        // -r, r = v*y
   f2 h = mul2(y, sp(0.5f));
-  f2 nr = mul2(r, sp(-1.0f));
-  f2 e = fma2(nr, r, v);
-  return fma2(e, h, r);
+  f2 ne = fma2(nr, nr, nv);   // r*r - v
+  return fma2(ne, h, nr);     // -(r + (v - r*r)*h)
 }
 
 // power-of-two scales folded into the ECC constants: the fraction comes out pre-multiplied by
@@ -396,8 +406,10 @@ FO_DEVI f2 sqrt_core2(f2 v) {
 template <int PDT, int ECC_BITS>
 struct EccConst {
   static constexpr float kFold = PDT == FO_BF16 ? 256.0f : 2048.0f;           // 2^(MANT+1)
-  static constexpr float kNegDiv = -(Ecc<ECC_BITS>::MAX * kFold);              // -(MAX * 2^(MANT+1)), exact
-  static FO_DEVI float rcp() { return __uint_as_float(Ecc<ECC_BITS>::RCP_BITS) * (1.0f / kFold); }  // RN(1/MAX) * 2^-(MANT+1), exact
+  // 1/MAX as an unevaluated sum hi + lo of two floats, both times 2^-(MANT+1) (exact scalings).
+  // 1/127 and 1/32767 have periodic binary expansions, so lo is hi shifted down by 28 resp. 30 bits.
+  static FO_DEVI float rcp_hi() { return __uint_as_float(Ecc<ECC_BITS>::RCP_BITS) * (1.0f / kFold); }
+  static FO_DEVI float rcp_lo() { return rcp_hi() * (ECC_BITS == 8 ? 3.7252902984619140625e-9f : 9.31322574615478515625e-10f); }
 };
 template <int PDT>
 FO_DEVI uint32_t exp_field(float lpf) {
@@ -409,7 +421,10 @@ FO_DEVI uint32_t exp_field(float lpf) {
 template <int PDT, int ECC_BITS>
 FO_DEVI f2 reconstruct_ordinary2(f2 lpf, f2 ef, f2 one) {
   using K = EccConst<PDT, ECC_BITS>;
-  f2 fr = div_by_rcp2(ef, sp(K::kNegDiv), sp(K::rcp()));
+  // RN(e / MAX) for every integer e of the ECC type: e*hi + RN(e*lo) carries the quotient to
+  // about 2^-48, which no e/MAX comes that close to a rounding boundary without being exact
+  // (all 2^ECC_BITS values are compared with the IEEE division by the self-test)
+  f2 fr = fma2(ef, sp(K::rcp_hi()), mul2(ef, sp(K::rcp_lo())));
   f2 sc = mk(__uint_as_float(exp_field<PDT>(lpf.x)), __uint_as_float(exp_field<PDT>(lpf.y)));
   return sum2(mul2(fr, sc), lpf, one);
 }
@@ -431,19 +446,18 @@ FO_DEVI void ecc_ordinary2(f2 theta, f2 lpf, int& e0, int& e1) {
 // bits whose low byte is floor(127 * 2n/(1+|n|) + 0.5), |n| <= 1
 FO_DEVI void softsign_code_bits2(f2 n, f2 one, uint32_t& c0, uint32_t& c1) {
   f2 d = add2(mk(fabsf(n.x), fabsf(n.y)), sp(1.0f));
-  f2 nd = mul2(d, sp(-1.0f));
-  f2 y = rcp2(d, nd);
-  f2 q0 = mul2(n, y);
-  f2 r = fma2(nd, q0, n);
-  f2 q = fma2(r, y, q0);                       // n/(1+|n|); 2n/(1+|n|) * 127 == q * 254 exactly
-  f2 c = sum2(mul2(q, sp(254.0f)), sp(0.5f), one);
+  f2 ny = neg_rcp2(d);
+  f2 nq0 = mul2(n, ny);
+  f2 r = fma2(d, nq0, n);                      // n - d*q0
+  f2 nq = fma2(r, ny, nq0);                    // -n/(1+|n|); 2n/(1+|n|) * 127 == nq * -254 exactly
+  f2 c = sum2(mul2(nq, sp(-254.0f)), sp(0.5f), one);
   f2 fl = add2_rd(c, sp(12582912.0f));
   c0 = __float_as_uint(fl.x);
   c1 = __float_as_uint(fl.y);
 }
-// bits whose low byte is floor(255 * root/av + 0.5); nav = -av, rcp = RN(1/av)
-FO_DEVI void quant_v_bits2(f2 root, f2 nav, f2 rcp, f2 one, uint32_t& c0, uint32_t& c1) {
-  f2 t = div_by_rcp2(root, nav, rcp);
+// bits whose low byte is floor(255 * root/av + 0.5); nroot = -root, nrcp = -RN(1/av)
+FO_DEVI void quant_v_bits2(f2 nroot, f2 av, f2 nrcp, f2 one, uint32_t& c0, uint32_t& c1) {
+  f2 t = div_negnum_by_rcp2(nroot, av, nrcp);
   f2 c = sum2(mul2(t, sp(255.0f)), sp(0.5f), one);
   f2 fl = add2_rd(c, sp(12582912.0f));
   c0 = __float_as_uint(fl.x);

@@ -26,8 +26,8 @@ __global__ void selftest_sqrt(const float one, unsigned long long* out) {
     if (v >= 1.0e-30f) {
       bad += !same_float(fast::sqrt_core(v), fsqrt(v));
       const float w = __uint_as_float(0x7F7FFFFFu - (uint32_t)b + __float_as_uint(1.0e-30f));  // a second, unrelated lane
-      const float2 r2 = fast2::sqrt_core2(make_float2(v, w));
-      bad += !same_float(r2.x, fsqrt(v)) || !same_float(r2.y, fsqrt(w));
+      const float2 r2 = fast2::neg_sqrt_core2(make_float2(-v, -w));
+      bad += !same_float(r2.x, -fsqrt(v)) || !same_float(r2.y, -fsqrt(w));
     }
   }
   tally(bad, out);
@@ -130,7 +130,7 @@ __global__ void selftest_group_div(const float one, unsigned long long pairs, un
       fast2::softsign_code_bits2(fast2::div_by_rcp2(make_float2(x, -x), fast2::sp(-safe), fast2::sp(gs.rcp)), fast2::sp(one), c0, c1);
       bad += (int)(signed char)(c0 & 0xFFu) != ieee::quant_m(x, safe);
       bad += (int)(signed char)(c1 & 0xFFu) != ieee::quant_m(-x, safe);
-      fast2::quant_v_bits2(make_float2(x, safe), fast2::sp(-safe), fast2::sp(gs.rcp), fast2::sp(one), c0, c1);
+      fast2::quant_v_bits2(make_float2(-x, -safe), fast2::sp(safe), fast2::sp(-gs.rcp), fast2::sp(one), c0, c1);
       bad += (int)(c0 & 0xFFu) != ieee::quant_v(x, safe);
       bad += (int)(c1 & 0xFFu) != 255;
       bad += (int)(signed char)(fast::softsign_code_bits(fast::div_by_rcp(x, safe, gs.rcp)) & 0xFFu) != ieee::quant_m(x, safe);
@@ -145,8 +145,8 @@ __global__ void selftest_group_div(const float one, unsigned long long pairs, un
       const float num = __uint_as_float((r3 & 0x80000000u) | ((57u + r1 % 131u) << 23) | (r2 & 0x7FFFFFu));
       const float den = __uint_as_float(((88u + r0 % 86u) << 23) | (r3 & 0x7FFFFFu));
       const float den2 = __uint_as_float(((88u + r2 % 86u) << 23) | (r1 & 0x7FFFFFu));
-      const float2 q = fast2::div2(make_float2(num, -num), make_float2(den, den2));
-      bad += !same_float(q.x, fdiv(num, den)) || !same_float(q.y, fdiv(-num, den2));
+      const float2 q = fast2::neg_div2(make_float2(num, -num), make_float2(den, den2));
+      bad += !same_float(q.x, fdiv(-num, den)) || !same_float(q.y, fdiv(num, den2));
     }
     if (adam_is_tame(eps, sq)) {
       float a = fadd(fast::div_by_rcp(root, sq, __frcp_rn(sq)), eps);
@@ -167,6 +167,10 @@ __global__ void selftest_rcp(unsigned long long* out) {
     const float s = __uint_as_float((uint32_t)b);
     const float want = __frcp_rn(s);
     bad0 += !same_float(fast::rcp_rn(s), want);
+    {  // the packed form, which starts from the reciprocal of -s
+      const float2 ny = fast2::neg_rcp2(make_float2(s, s));
+      bad0 += !same_float(ny.x, -want) || !same_float(ny.y, -want);
+    }
     bad1 += !same_float(fast::rcp_steps<1>(s), want);
     bad2 += !same_float(fast::rcp_steps<2>(s), want);
   }

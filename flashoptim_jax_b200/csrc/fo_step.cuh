@@ -374,7 +374,7 @@ struct Raw {
 };
 
 template <int OPT, int PDT, int ECC_BITS, int STATE>
-FO_DEVI void hot_load(const DevLeaf& L, const int gdt, const unsigned long long i0, Raw<OPT, PDT, ECC_BITS, STATE>& r) {
+FO_DEVI void hot_load(const DevLeaf& L, const int gdt, const uint32_t i0, Raw<OPT, PDT, ECC_BITS, STATE>& r) {
   if constexpr (PDT == FO_F32) {
     r.p0 = __ldcs((const uint4*)((const float*)L.param + i0));
     r.p1 = __ldcs((const uint4*)((const float*)L.param + i0) + 1);
@@ -522,7 +522,7 @@ FO_DEVI bool hot_unpack(const Raw<OPT, PDT, ECC_BITS, STATE>& r, const int gdt, 
 FO_DEVI float sign_of(float x);
 
 template <int OPT, int PDT, int ECC_BITS, int STATE>
-__device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const unsigned long long base,
+__device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base,
                                         const float one, const float* lut_m, const float* lut_v, const Peers& peers);
 
 // Second half of a hot chunk: update, split, requantize, store.  Each stage runs its packed
@@ -534,7 +534,7 @@ __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const in
 // untouched rows, padding, zero gradients) redoes that stage with IEEE operations, then stores.
 // The stored bits are those of the IEEE path in every case.
 template <bool REPAIR, int OPT, int PDT, int ECC_BITS, int STATE>
-FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const unsigned long long base, const float one,
+FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base, const float one,
                         bool rare, Unpacked& u, const float* lut_m, const float* lut_v, const Peers& peers) {
   using namespace fast2;
   const float2 one2 = sp(one);
@@ -542,9 +542,11 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uns
   float2 (&theta)[4] = u.theta;
   float2 (&m)[4] = u.m;
   float2 (&v)[4] = u.v;
-  float2 root[4];
-  const unsigned long long i0 = base + (unsigned long long)threadIdx.x * kPiece;
-  const unsigned long long gi = i0 >> 5;
+  float2 nroot[4];  // Adam: -sqrt(second moment)
+  // 32-bit element offsets (one multiply-add per address): the host hands this kernel leaves of
+  // at most 2^31 elements, splitting longer ones
+  const uint32_t i0 = base + threadIdx.x * kPiece;
+  const uint32_t gi = i0 >> 5;
 
   // ---- update --------------------------------------------------------------------------------------
   const bool decoupled = (h.flags & FO_FLAG_DECOUPLED_WD) != 0;
@@ -555,41 +557,51 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uns
 #pragma unroll
       for (int k = 0; k < 4; ++k) g[k] = sum2(mul2(sp(h.wd), theta[k]), g[k], one2);
     }
+    // The second moment and its square root are carried negated (nv = -v, nroot = -sqrt(v)):
+    // the signs then fall where the packed residual corrections need them (see fo_math.cuh).
+    float2 nv[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       m[k] = sum2(mul2(sp(h.b1), m[k]), mul2(sp(h.omb1), g[k]), one2);
-      v[k] = sum2(mul2(sp(h.b2), v[k]), mul2(sp(h.omb2), mul2(g[k], g[k])), one2);
+      nv[k] = sum2(mul2(sp(-h.b2), v[k]), mul2(sp(-h.omb2), mul2(g[k], g[k])), one2);
+    }
+    if constexpr (STATE == FO_STATE_FULL) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[k] = mul2(nv[k], sp(-1.0f));  // stored as it is
     }
     if (decoupled) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) theta[k] = mul2(theta[k], sp(h.decay));
     }
-    const float2 nsq = sp(-h.sqrt_bc2), rsq = sp(h.rcp_sqrt_bc2), eps = sp(h.eps), nlr = sp(-h.lr_bc1);
+    const float2 sq = sp(h.sqrt_bc2), nrsq = sp(-h.rcp_sqrt_bc2), eps = sp(h.eps), lrb1 = sp(h.lr_bc1);
     float2 tn[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      root[k] = sqrt_core2(v[k]);
-      const float2 den = add2(div_by_rcp2(root[k], nsq, rsq), eps);
-      tn[k] = sum2(div2(mul2(nlr, m[k]), den), theta[k], one2);  // theta - (lr/bc1 * m) / den
+      nroot[k] = neg_sqrt_core2(nv[k]);
+      const float2 den = add2(div_negnum_by_rcp2(nroot[k], sq, nrsq), eps);
+      tn[k] = sum2(neg_div2(mul2(lrb1, m[k]), den), theta[k], one2);  // theta - (lr/bc1 * m) / den
     }
     // Ranges in which the packed square root and division are exact: second moment >= 1e-30 with
     // sqrt <= 2^30 (so the denominator lies in [eps, 2^47]) and numerator magnitudes in [2^-70, 2^60].
     am_lane = maxabs8(m);
+    av_lane = -min8(nroot);
     const float lrb = fabsf(h.lr_bc1);
-    if (!(min8(v) >= 1.0e-30f) || !(max8(v) <= 1.0e18f) || !(fmul(minabs8(m), lrb) >= 8.4703295e-22f) ||
+    if (!(max8(nv) <= -1.0e-30f) || !(av_lane <= 1.0737418e9f) || !(fmul(minabs8(m), lrb) >= 8.4703295e-22f) ||
         !(fmul(am_lane, lrb) <= 1.1529215e18f)) {
       rare = true;
       if constexpr (REPAIR) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          tn[k].x = repair_adam(v[k].x, m[k].x, theta[k].x, h.lr_bc1, h.sqrt_bc2, h.eps, root[k].x);
-          tn[k].y = repair_adam(v[k].y, m[k].y, theta[k].y, h.lr_bc1, h.sqrt_bc2, h.eps, root[k].y);
+          float rx, ry;
+          tn[k].x = repair_adam(-nv[k].x, m[k].x, theta[k].x, h.lr_bc1, h.sqrt_bc2, h.eps, rx);
+          tn[k].y = repair_adam(-nv[k].y, m[k].y, theta[k].y, h.lr_bc1, h.sqrt_bc2, h.eps, ry);
+          nroot[k] = mk(-rx, -ry);
         }
+        av_lane = -min8(nroot);
       }
     }
 #pragma unroll
     for (int k = 0; k < 4; ++k) theta[k] = tn[k];
-    av_lane = max8(root);
   } else if constexpr (OPT == FO_OPT_LION) {
     // flashoptim_jax/momentum_kernel.py:77-79 or flashoptim_jax/lion.py:50-52
     float2 upd[4];
@@ -699,17 +711,17 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uns
     mq.y = pack_bytes(q[4], q[5], q[6], q[7]);
     if constexpr (OPT == FO_OPT_ADAM) {
       av = group_max(av_lane);
-      const float2 nav = sp(-av), rv2 = sp(fast::rcp_rn(av));
+      const float2 av2 = sp(av), nrv2 = sp(-fast::rcp_rn(av));
 #pragma unroll
-      for (int k = 0; k < 4; ++k) quant_v_bits2(root[k], nav, rv2, one2, q[2 * k], q[2 * k + 1]);
+      for (int k = 0; k < 4; ++k) quant_v_bits2(nroot[k], av2, nrv2, one2, q[2 * k], q[2 * k + 1]);
       if (!(av >= 1.0e-12f && av <= 1.0e30f)) {
         rare = true;
         if constexpr (REPAIR) {
           const float safe = ieee::safe_scale(av, floor_mode);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            q[2 * k] = repair_code_v(root[k].x, safe);
-            q[2 * k + 1] = repair_code_v(root[k].y, safe);
+            q[2 * k] = repair_code_v(-nroot[k].x, safe);
+            q[2 * k + 1] = repair_code_v(-nroot[k].y, safe);
           }
         }
       }
@@ -724,6 +736,8 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uns
       warm_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, one, lut_m, lut_v, peers);
       return;
     }
+  } else {
+    (void)rare;
   }
   // ---- stores ---------------------------------------------------------------------------------------------
   if constexpr (PDT == FO_F32) {
@@ -762,10 +776,10 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uns
 // packed arithmetic from a fresh load, with per-lane IEEE repairs.  About twice the cost of a
 // first pass for that warp, against about seven times for the scalar IEEE path.
 template <int OPT, int PDT, int ECC_BITS, int STATE>
-__device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const unsigned long long base,
+__device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base,
                                         const float one, const float* lut_m, const float* lut_v, const Peers& peers) {
   Raw<OPT, PDT, ECC_BITS, STATE> raw;
-  hot_load<OPT, PDT, ECC_BITS, STATE>(L, gdt, base + (unsigned long long)threadIdx.x * kPiece, raw);
+  hot_load<OPT, PDT, ECC_BITS, STATE>(L, gdt, base + threadIdx.x * kPiece, raw);
   Unpacked u;
   hot_unpack<true, OPT, PDT, ECC_BITS, STATE>(raw, gdt, lut_m, lut_v, one, u);
   hot_finish<true, OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, one, false, u, lut_m, lut_v, peers);
@@ -785,7 +799,7 @@ FO_DEVI void build_luts(float* lut_m, float* lut_v) {
 struct ChunkRef {
   int leaf;
   bool hot;
-  unsigned long long base;
+  uint32_t base;  // leaves of this kernel hold at most 2^31 elements
 };
 
 template <int OPT>
@@ -803,8 +817,8 @@ FO_DEVI ChunkRef locate(const StepParams& p, uint32_t c, int l_hint) {
   int l = l_hint;
   while (c >= p.first_block[l + 1]) ++l;
   r.leaf = l;
-  r.base = (unsigned long long)(c - p.first_block[l]) * kChunk;
-  r.hot = leaf_is_hot<OPT>(p, l) && r.base + kChunk <= p.leaf[l].n;
+  r.base = (c - p.first_block[l]) * (uint32_t)kChunk;
+  r.hot = leaf_is_hot<OPT>(p, l) && r.base + (uint32_t)kChunk <= (uint32_t)p.leaf[l].n;
   return r;
 }
 
@@ -815,7 +829,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
   const uint32_t total = p.first_block[p.n_leaves];
   uint32_t c = blockIdx.x;
   if (c >= total) return;
-  const unsigned long long toff = (unsigned long long)threadIdx.x * kPiece;
+  const uint32_t toff = threadIdx.x * kPiece;
   ChunkRef cur = locate<OPT>(p, c, 0);
   int l_loaded = -1;
   Hyp h;
