@@ -794,14 +794,6 @@ FO_DEVI void build_luts(float* lut_m, float* lut_v) {
   __syncthreads();
 }
 
-// which chunk a block works on: the leaf it belongs to, its first element, and whether the
-// hot path may take it
-struct ChunkRef {
-  int leaf;
-  bool hot;
-  uint32_t base;  // leaves of this kernel hold at most 2^31 elements
-};
-
 template <int OPT>
 FO_DEVI bool leaf_is_hot(const StepParams& p, int l) {
 #ifdef FO_NAIVE_MATH
@@ -811,62 +803,53 @@ FO_DEVI bool leaf_is_hot(const StepParams& p, int l) {
 #endif
 }
 
-template <int OPT>
-FO_DEVI ChunkRef locate(const StepParams& p, uint32_t c, int l_hint) {
-  ChunkRef r;
-  int l = l_hint;
-  while (c >= p.first_block[l + 1]) ++l;
-  r.leaf = l;
-  r.base = (c - p.first_block[l]) * (uint32_t)kChunk;
-  r.hot = leaf_is_hot<OPT>(p, l) && r.base + (uint32_t)kChunk <= (uint32_t)p.leaf[l].n;
-  return r;
-}
-
+// Persistent grid.  The chunks of all leaves form one sequence (first_block[] gives each leaf's
+// first position in it); block b takes the contiguous span [total*b/grid, total*(b+1)/grid) and
+// walks it leaf by leaf.  Inside a leaf the whole aligned chunks form one run that the
+// straight-line path takes with nothing per chunk but a counter and the prefetch of the next
+// chunk; what is left (a ragged last chunk, unaligned leaves, hyper-parameter sets outside the
+// shortcuts' range) goes to the scalar IEEE path.
 template <int OPT, int PDT, int ECC_BITS, int STATE>
 __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const __grid_constant__ StepParams p) {
   __shared__ float lut_m[256], lut_v[256];
   if constexpr (STATE == FO_STATE_QUANT) build_luts(lut_m, lut_v);
   const uint32_t total = p.first_block[p.n_leaves];
-  uint32_t c = blockIdx.x;
-  if (c >= total) return;
+  const uint32_t c0 = (uint32_t)((unsigned long long)total * blockIdx.x / gridDim.x);
+  const uint32_t c1 = (uint32_t)((unsigned long long)total * (blockIdx.x + 1) / gridDim.x);
+  if (c0 >= c1) return;
   const uint32_t toff = threadIdx.x * kPiece;
-  ChunkRef cur = locate<OPT>(p, c, 0);
-  int l_loaded = -1;
-  Hyp h;
-  bool hyper_ok = true;  // Adam: the hyper set allows the reciprocal shortcut in the denominator
-  Raw<OPT, PDT, ECC_BITS, STATE> raw;
-  bool loaded = false;
-  if (cur.hot) {
-    hot_load<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], p.grad_dtype, cur.base + toff, raw);
-    loaded = true;
+  int l = 0, hi = p.n_leaves;  // the leaf that holds chunk c0
+  while (hi - l > 1) {
+    const int mid = (l + hi) >> 1;
+    if (p.first_block[mid] <= c0) l = mid; else hi = mid;
   }
-  while (true) {
-    if (cur.leaf != l_loaded) {
-      h = load_hyper<OPT>(p.hyper[p.hyper_of[cur.leaf]]);
-      l_loaded = cur.leaf;
-      // the CPU-path parameter hand-back (FO_FLAG_LP_DELTA) needs the old stored value to the end: IEEE path only
-      hyper_ok = (h.flags & FO_FLAG_LP_DELTA) == 0;
-      if constexpr (OPT == FO_OPT_ADAM) hyper_ok = hyper_ok && (h.flags & kFlagTameAdam) != 0;
+  Raw<OPT, PDT, ECC_BITS, STATE> raw;
+  for (uint32_t c = c0; c < c1; ++l) {
+    const uint32_t first = p.first_block[l], next = p.first_block[l + 1];
+    const uint32_t lo = c - first;                         // chunk indices inside the leaf
+    const uint32_t end = (c1 < next ? c1 : next) - first;
+    c = first + end;
+    const DevLeaf& L = p.leaf[l];
+    const Hyp h = load_hyper<OPT>(p.hyper[p.hyper_of[l]]);
+    // the CPU-path parameter hand-back (FO_FLAG_LP_DELTA) needs the old stored value to the end: IEEE path only
+    bool hyper_ok = (h.flags & FO_FLAG_LP_DELTA) == 0;
+    if constexpr (OPT == FO_OPT_ADAM) hyper_ok = hyper_ok && (h.flags & kFlagTameAdam) != 0;  // the reciprocal shortcut in the denominator
+    uint32_t hot_end = (leaf_is_hot<OPT>(p, l) && hyper_ok) ? (uint32_t)(L.n / kChunk) : 0u;  // whole chunks
+    if (hot_end > end) hot_end = end;
+    uint32_t ch = lo;
+    if (ch < hot_end) {
+      uint32_t base = ch * (uint32_t)kChunk;
+      hot_load<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, base + toff, raw);
+      for (; ch < hot_end; ++ch, base += kChunk) {
+        Unpacked u;
+        const bool rare = hot_unpack<false, OPT, PDT, ECC_BITS, STATE>(raw, p.grad_dtype, lut_m, lut_v, p.one, u);
+        // the next chunk's loads fly while this one is computed
+        if (ch + 1 < hot_end) hot_load<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, base + kChunk + toff, raw);
+        hot_finish<false, OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, base, p.one, rare, u, lut_m, lut_v, p.peers);
+      }
     }
-    const uint32_t cn = c + gridDim.x;
-    const bool more = cn < total;
-    ChunkRef nxt = cur;
-    if (more) nxt = locate<OPT>(p, cn, cur.leaf);
-    if (cur.hot && hyper_ok) {
-      if (!loaded) hot_load<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], p.grad_dtype, cur.base + toff, raw);
-      Unpacked u;
-      const bool rare = hot_unpack<false, OPT, PDT, ECC_BITS, STATE>(raw, p.grad_dtype, lut_m, lut_v, p.one, u);
-      // the next chunk's loads fly while this one is computed
-      loaded = more && nxt.hot;
-      if (loaded) hot_load<OPT, PDT, ECC_BITS, STATE>(p.leaf[nxt.leaf], p.grad_dtype, nxt.base + toff, raw);
-      hot_finish<false, OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], h, p.grad_dtype, cur.base, p.one, rare, u, lut_m, lut_v, p.peers);
-    } else {
-      cold_chunk<OPT, PDT, ECC_BITS, STATE>(p.leaf[cur.leaf], h, p.grad_dtype, cur.base, lut_m, lut_v, p.peers);
-      loaded = false;
-    }
-    if (!more) break;
-    c = cn;
-    cur = nxt;
+    for (; ch < end; ++ch)
+      cold_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, (unsigned long long)ch * kChunk, lut_m, lut_v, p.peers);
   }
 }
 
