@@ -428,19 +428,35 @@ FO_DEVI f2 reconstruct_ordinary2(f2 lpf, f2 ef, f2 one) {
   f2 sc = mk(__uint_as_float(exp_field<PDT>(lpf.x)), __uint_as_float(exp_field<PDT>(lpf.y)));
   return sum2(mul2(fr, sc), lpf, one);
 }
-// ECC of theta given lpf = RN_lp(theta) as fp32, ordinary values
+// 2^(1 - exponent of lpf) as float bits: the inverted exponent field (one logic operation)
+template <int PDT>
+FO_DEVI uint32_t inv_exp_field(float lpf) {
+  uint32_t ib = ~__float_as_uint(lpf) & 0x7F800000u;
+  if constexpr (PDT == FO_F16) ib = min(ib, 142u << 23);  // zero / subnormal halves use the min normal exponent
+  return ib;
+}
+// ECC of theta given lpf = RN_lp(theta) as fp32, for kMin <= |lpf| <= 1e38 (see fast::Ordinary):
+// err * 2^-log_half_ulp * MAX, |.| <= MAX without clipping because |err| is at most half an ULP of lpf
 template <int PDT, int ECC_BITS>
 FO_DEVI void ecc_ordinary2(f2 theta, f2 lpf, int& e0, int& e1) {
-  // MAX * 2^-log_half_ulp as a float: exponent arithmetic on the bits of MAX
-  constexpr uint32_t kMaxBits = ECC_BITS == 8 ? 0x42FE0000u : 0x46FFFE00u;  // 127.0f, 32767.0f
-  constexpr uint32_t kBase = kMaxBits + ((PDT == FO_BF16 ? 262u - 127u : 265u - 127u) << 23);
+  constexpr float kC = Ecc<ECC_BITS>::MAX * (PDT == FO_BF16 ? 128.0f : 1024.0f);  // MAX * 2^MANT, exact
   f2 err = fma2(lpf, sp(-1.0f), theta);
-  f2 sc = mk(__uint_as_float(kBase - exp_field<PDT>(lpf.x)), __uint_as_float(kBase - exp_field<PDT>(lpf.y)));
-  f2 s = mul2(err, sc);  // clip(err * 2^-ls, -1, 1) * MAX == clip(err * 2^-ls * MAX, -MAX, MAX)
-  f2 a = mk(fminf(fabsf(s.x), Ecc<ECC_BITS>::MAX), fminf(fabsf(s.y), Ecc<ECC_BITS>::MAX));
-  f2 y = add2(a, sp(0.5f));
-  e0 = __float2int_rz(copysignf(y.x, s.x));
-  e1 = __float2int_rz(copysignf(y.y, s.y));
+  f2 sc = mk(__uint_as_float(inv_exp_field<PDT>(lpf.x)), __uint_as_float(inv_exp_field<PDT>(lpf.y)));
+  f2 s = mul2(mul2(err, sc), sp(kC));  // the first product is exact (a power of two, no underflow: err is a multiple of theta's ULP)
+  f2 y = add2(s, mk(copysignf(0.5f, s.x), copysignf(0.5f, s.y)));  // round half away from zero ...
+  e0 = __float2int_rz(y.x);                                        // ... by truncation
+  e1 = __float2int_rz(y.y);
+}
+
+// RN(c/255) for the codes c in bytes b and b+1 of w (flashoptim_jax/quantization.py:74), without a
+// table: the byte goes into the mantissa of 2^23, which is then subtracted; c*hi + RN(c*lo) with
+// hi + lo = 1/255 to 2^-48 equals RN(c/255) for all 256 codes (compared with the IEEE division
+// by the self-test).
+FO_DEVI f2 codes_over_255(uint32_t w, int b) {
+  f2 cf = add2(mk(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | (uint32_t)b)),
+                  __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | (uint32_t)(b + 1)))),
+               sp(-8388608.0f));
+  return fma2(cf, sp(__uint_as_float(0x3B808081u)), mul2(cf, sp(__uint_as_float(0xAF7EFEFFu))));
 }
 
 // bits whose low byte is floor(127 * 2n/(1+|n|) + 0.5), |n| <= 1

@@ -212,6 +212,12 @@ __global__ void selftest_code_tables(unsigned long long* out) {
     if (i < 256) {
       int e8 = i - 128;
       bad += !same_float(fast::ecc_fraction<8>(e8), fdiv((float)e8, 127.0f));
+      // second-moment codes in every byte position of a word, next to an unrelated neighbour
+      const uint32_t j = (uint32_t)(255 - i);
+      const float2 lo = fast2::codes_over_255((uint32_t)i | (j << 8) | 0xA5000000u, 0);
+      const float2 hi = fast2::codes_over_255(0x5Au | (j << 16) | ((uint32_t)i << 24), 2);
+      bad += !same_float(lo.x, ieee::deq_v_norm(i)) || !same_float(lo.y, ieee::deq_v_norm((int)j));
+      bad += !same_float(hi.x, ieee::deq_v_norm((int)j)) || !same_float(hi.y, ieee::deq_v_norm(i));
     }
   }
   tally(bad, out);

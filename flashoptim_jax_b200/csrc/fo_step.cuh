@@ -40,9 +40,16 @@ namespace fo {
 #ifndef FO_MIN_BLOCKS_MOMENTUM
 #define FO_MIN_BLOCKS_MOMENTUM 3
 #endif
+#ifndef FO_MAX_STAGES
+#define FO_MAX_STAGES 3
+#endif
+#ifndef FO_LUT_COPIES
+#define FO_LUT_COPIES 8
+#endif
 constexpr int kThreads = FO_THREADS;
 constexpr int min_blocks(int opt) { return opt == FO_OPT_ADAM ? FO_MIN_BLOCKS_ADAM : FO_MIN_BLOCKS_MOMENTUM; }
 constexpr int kPiece = 8;
+constexpr int kLutCopies = FO_LUT_COPIES;                 // copies of the momentum dequantization table in shared memory
 constexpr int kChunk = kThreads * kPiece;      // elements per chunk
 constexpr int kMaxLeaves = 320;                // leaves per launch (kernel-parameter table)
 constexpr int kGenericTile = 1024;             // slots per block of the any-group-size kernel
@@ -91,6 +98,7 @@ struct StepParams {
   int32_t grad_dtype;
   int32_t group_size;
   float one;  // 1.0f the compiler cannot see through (see fast2::sum2)
+  int32_t stages;  // shared-memory stages of the copy pipeline (2..kMaxStages), set by the launcher
   Peers peers;
 };
 
@@ -409,6 +417,110 @@ FO_DEVI void hot_load(const DevLeaf& L, const int gdt, const uint32_t i0, Raw<OP
   }
 }
 
+// ---- shared-memory staging of the streams (asynchronous copies) ---------------------------------
+// Every thread copies its own eight elements of every stream of a later chunk into a slot of
+// shared memory that only it reads back, so the pipeline needs no barrier: the thread waits for
+// its own copy groups.  Several chunks are in flight per thread at no cost in registers.
+// A 32-byte stream (fp32) is kept as two planes of 16 bytes per thread, so that the 128-bit
+// reads of a warp fall on consecutive banks.
+template <int OPT, int PDT, int ECC_BITS, int STATE>
+struct Stage {
+  static constexpr int kParam = PDT == FO_F32 ? 32 : 16;  // bytes per thread and stage
+  static constexpr int kEcc = ECC_BITS == 16 ? 16 : (ECC_BITS == 8 ? 8 : 0);
+  static constexpr int kMu = STATE == FO_STATE_QUANT ? 8 : (STATE == FO_STATE_FULL ? 32 : 0);
+  static constexpr int kNu = OPT == FO_OPT_ADAM ? kMu : 0;
+  static constexpr int kOffEcc = kParam * kThreads;       // byte offsets of the streams inside a stage
+  static constexpr int kOffMu = kOffEcc + kEcc * kThreads;
+  static constexpr int kOffNu = kOffMu + kMu * kThreads;
+  static constexpr int kOffGrad = kOffNu + kNu * kThreads;
+  __host__ __device__ static constexpr int bytes(int gdt) { return kOffGrad + (gdt == FO_F32 ? 32 : 16) * kThreads; }
+};
+constexpr int kMaxStages = FO_MAX_STAGES;
+FO_DEVI void copy_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+// for the two halves of a 32-byte piece: each copy uses half of every 32-byte sector it touches,
+// so the line is kept in L1 for the other half
+FO_DEVI void copy_async16_l1(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+FO_DEVI void copy_async8(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+FO_DEVI void copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+FO_DEVI void copy_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+FO_DEVI uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory");
+  return v;
+}
+FO_DEVI uint2 lds64(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a) : "memory");
+  return v;
+}
+
+// start the copies of this thread's piece at element i0 of every stream into the stage at
+// shared address st (the group scales are not staged: they are two bytes per 32 elements)
+template <int OPT, int PDT, int ECC_BITS, int STATE>
+FO_DEVI void stage_fill(const DevLeaf& L, const int gdt, const uint32_t i0, const uint32_t st) {
+  using S = Stage<OPT, PDT, ECC_BITS, STATE>;
+  const uint32_t t16 = threadIdx.x * 16u, t8 = threadIdx.x * 8u;
+  if constexpr (PDT == FO_F32) {
+    copy_async16_l1(st + t16, (const float*)L.param + i0);
+    copy_async16_l1(st + 16u * kThreads + t16, (const float*)L.param + i0 + 4);
+  } else {
+    copy_async16(st + t16, (const unsigned short*)L.param + i0);
+  }
+  if constexpr (ECC_BITS == 16) copy_async16(st + S::kOffEcc + t16, (const short*)L.ecc + i0);
+  if constexpr (ECC_BITS == 8) copy_async8(st + S::kOffEcc + t8, (const signed char*)L.ecc + i0);
+  if constexpr (STATE == FO_STATE_QUANT) {
+    copy_async8(st + S::kOffMu + t8, (const unsigned char*)L.mu + i0);
+    if constexpr (OPT == FO_OPT_ADAM) copy_async8(st + S::kOffNu + t8, (const unsigned char*)L.nu + i0);
+  } else if constexpr (STATE == FO_STATE_FULL) {
+    copy_async16_l1(st + S::kOffMu + t16, (const float*)L.mu + i0);
+    copy_async16_l1(st + S::kOffMu + 16u * kThreads + t16, (const float*)L.mu + i0 + 4);
+    if constexpr (OPT == FO_OPT_ADAM) {
+      copy_async16_l1(st + S::kOffNu + t16, (const float*)L.nu + i0);
+      copy_async16_l1(st + S::kOffNu + 16u * kThreads + t16, (const float*)L.nu + i0 + 4);
+    }
+  }
+  if (gdt == FO_F32) {
+    copy_async16_l1(st + S::kOffGrad + t16, (const float*)L.grad + i0);
+    copy_async16_l1(st + S::kOffGrad + 16u * kThreads + t16, (const float*)L.grad + i0 + 4);
+  } else {
+    copy_async16(st + S::kOffGrad + t16, (const unsigned short*)L.grad + i0);
+  }
+}
+
+// read this thread's piece back from a stage whose copies have completed
+template <int OPT, int PDT, int ECC_BITS, int STATE>
+FO_DEVI void stage_read(const int gdt, const uint32_t st, Raw<OPT, PDT, ECC_BITS, STATE>& r) {
+  using S = Stage<OPT, PDT, ECC_BITS, STATE>;
+  const uint32_t t16 = threadIdx.x * 16u, t8 = threadIdx.x * 8u;
+  r.p0 = lds128(st + t16);
+  if constexpr (PDT == FO_F32) r.p1 = lds128(st + 16u * kThreads + t16);
+  if constexpr (ECC_BITS == 16) r.e = lds128(st + S::kOffEcc + t16);
+  if constexpr (ECC_BITS == 8) {
+    const uint2 t = lds64(st + S::kOffEcc + t8);
+    r.e.x = t.x; r.e.y = t.y;
+  }
+  if constexpr (STATE == FO_STATE_QUANT) {
+    r.mq = lds64(st + S::kOffMu + t8);
+    if constexpr (OPT == FO_OPT_ADAM) r.vq = lds64(st + S::kOffNu + t8);
+  } else if constexpr (STATE == FO_STATE_FULL) {
+    r.m0 = lds128(st + S::kOffMu + t16);
+    r.m1 = lds128(st + S::kOffMu + 16u * kThreads + t16);
+    if constexpr (OPT == FO_OPT_ADAM) {
+      r.v0 = lds128(st + S::kOffNu + t16);
+      r.v1 = lds128(st + S::kOffNu + 16u * kThreads + t16);
+    }
+  }
+  r.g0 = lds128(st + S::kOffGrad + t16);
+  if (gdt == FO_F32) r.g1 = lds128(st + S::kOffGrad + 16u * kThreads + t16);
+}
+
 // what survives of a chunk's loads once they are unpacked: fp32 pairs ready for the update
 // (pair k holds elements 2k and 2k+1 of the thread's piece)
 struct Unpacked {
@@ -449,8 +561,7 @@ FO_DEVI uint32_t byte_of(uint32_t w, int k) { return __byte_perm(w, 0u, 0x4440u 
 // range (the results are then not to be stored).  REPAIR = true: the affected lane redoes the stage
 // with IEEE operations and the results are always good.
 template <bool REPAIR, int OPT, int PDT, int ECC_BITS, int STATE>
-FO_DEVI bool hot_unpack(const Raw<OPT, PDT, ECC_BITS, STATE>& r, const int gdt, const float* lut_m, const float* lut_v,
-                        const float one, Unpacked& u) {
+FO_DEVI bool hot_unpack(const Raw<OPT, PDT, ECC_BITS, STATE>& r, const int gdt, const float* lut_mw, const float one, Unpacked& u) {
   using namespace fast2;
   const float2 one2 = sp(one);
   bool rare = false;
@@ -502,13 +613,14 @@ FO_DEVI bool hot_unpack(const Raw<OPT, PDT, ECC_BITS, STATE>& r, const int gdt, 
     const uint32_t mw[2] = {r.mq.x, r.mq.y};
 #pragma unroll
     for (int k = 0; k < 4; ++k)  // quantization.py:52-55
-      u.m[k] = mul2(mk(lut_m[byte_of(mw[k >> 1], 2 * (k & 1))], lut_m[byte_of(mw[k >> 1], 2 * (k & 1) + 1)]), msc);
+      u.m[k] = mul2(mk(lut_mw[byte_of(mw[k >> 1], 2 * (k & 1)) * kLutCopies], lut_mw[byte_of(mw[k >> 1], 2 * (k & 1) + 1) * kLutCopies]), msc);
     if constexpr (OPT == FO_OPT_ADAM) {
       const float2 vsc = sp(__half2float(r.vsc));
       const uint32_t vw[2] = {r.vq.x, r.vq.y};
 #pragma unroll
       for (int k = 0; k < 4; ++k) {  // quantization.py:74-77
-        const float2 s = mul2(mk(lut_v[byte_of(vw[k >> 1], 2 * (k & 1))], lut_v[byte_of(vw[k >> 1], 2 * (k & 1) + 1)]), vsc);
+        const float2 nrm = codes_over_255(vw[k >> 1], 2 * (k & 1));
+        const float2 s = mul2(nrm, vsc);
         u.v[k] = mul2(s, s);
       }
     }
@@ -523,7 +635,7 @@ FO_DEVI float sign_of(float x);
 
 template <int OPT, int PDT, int ECC_BITS, int STATE>
 __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base,
-                                        const float one, const float* lut_m, const float* lut_v, const Peers& peers);
+                                        const float one, const float* lut_mw, const Peers& peers);
 
 // Second half of a hot chunk: update, split, requantize, store.  Each stage runs its packed
 // shortcut unconditionally.
@@ -535,7 +647,7 @@ __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const in
 // The stored bits are those of the IEEE path in every case.
 template <bool REPAIR, int OPT, int PDT, int ECC_BITS, int STATE>
 FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base, const float one,
-                        bool rare, Unpacked& u, const float* lut_m, const float* lut_v, const Peers& peers) {
+                        bool rare, Unpacked& u, const float* lut_mw, const Peers& peers) {
   using namespace fast2;
   const float2 one2 = sp(one);
   float2 (&g)[4] = u.g;
@@ -664,8 +776,12 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
       int ne[8];
 #pragma unroll
       for (int k = 0; k < 4; ++k) ecc_ordinary2<PDT, ECC_BITS>(theta[k], new_lp[k], ne[2 * k], ne[2 * k + 1]);
-      if constexpr (PDT == FO_BF16) {
-        if (!(minabs8(new_lp) >= fast::Ordinary<PDT>::kMin)) {
+      {
+        // outside these the exponent-field shortcut does not hold (tiny bf16 values), or the
+        // update overflowed the 16-bit range and the reference clips the ECC
+        bool odd = !(maxabs8(new_lp) <= 1.0e38f);
+        if constexpr (PDT == FO_BF16) odd = odd || !(minabs8(new_lp) >= fast::Ordinary<PDT>::kMin);
+        if (odd) {
           rare = true;
           if constexpr (REPAIR) {
 #pragma unroll
@@ -733,7 +849,7 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
   // ---- first pass: one decision per warp -----------------------------------------------------------------
   if constexpr (!REPAIR) {
     if (__any_sync(0xFFFFFFFFu, rare)) {
-      warm_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, one, lut_m, lut_v, peers);
+      warm_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, one, lut_mw, peers);
       return;
     }
   } else {
@@ -777,12 +893,12 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
 // first pass for that warp, against about seven times for the scalar IEEE path.
 template <int OPT, int PDT, int ECC_BITS, int STATE>
 __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base,
-                                        const float one, const float* lut_m, const float* lut_v, const Peers& peers) {
+                                        const float one, const float* lut_mw, const Peers& peers) {
   Raw<OPT, PDT, ECC_BITS, STATE> raw;
   hot_load<OPT, PDT, ECC_BITS, STATE>(L, gdt, base + threadIdx.x * kPiece, raw);
   Unpacked u;
-  hot_unpack<true, OPT, PDT, ECC_BITS, STATE>(raw, gdt, lut_m, lut_v, one, u);
-  hot_finish<true, OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, one, false, u, lut_m, lut_v, peers);
+  hot_unpack<true, OPT, PDT, ECC_BITS, STATE>(raw, gdt, lut_mw, one, u);
+  hot_finish<true, OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, one, false, u, lut_mw, peers);
 }
 
 // exact dequantization tables, one entry per code byte (built once per block)
@@ -791,6 +907,13 @@ FO_DEVI void build_luts(float* lut_m, float* lut_v) {
     lut_m[b] = ieee::deq_m_norm((int)(signed char)b);
     lut_v[b] = ieee::deq_v_norm(b);
   }
+  __syncthreads();
+}
+// The momentum table once more in kLutCopies interleaved copies (entry of code b for lane l at
+// b*kLutCopies + l % kLutCopies): the straight-line path looks eight random codes up per
+// thread, and with a single copy a warp's 32 look-ups fall three deep on some bank.
+FO_DEVI void build_wide_lut(const float* lut_m, float* lut_mw) {
+  for (int i = threadIdx.x; i < 256 * kLutCopies; i += blockDim.x) lut_mw[i] = lut_m[i / kLutCopies];
   __syncthreads();
 }
 
@@ -804,52 +927,87 @@ FO_DEVI bool leaf_is_hot(const StepParams& p, int l) {
 }
 
 // Persistent grid.  The chunks of all leaves form one sequence (first_block[] gives each leaf's
-// first position in it); block b takes the contiguous span [total*b/grid, total*(b+1)/grid) and
-// walks it leaf by leaf.  Inside a leaf the whole aligned chunks form one run that the
-// straight-line path takes with nothing per chunk but a counter and the prefetch of the next
-// chunk; what is left (a ragged last chunk, unaligned leaves, hyper-parameter sets outside the
-// shortcuts' range) goes to the scalar IEEE path.
+// first position in it) and block b takes positions b, b + grid, b + 2*grid, ...: at any moment
+// the blocks work on neighbouring chunks, which keeps the DRAM pages they stream from few.
+// Every block walks the leaves in order.  Inside a leaf its whole aligned chunks are taken by
+// the straight-line path with nothing per chunk but a counter and the prefetch of the block's
+// next chunk; what is left (a ragged last chunk, unaligned leaves, hyper-parameter sets outside
+// the shortcuts' range) goes to the scalar IEEE path.
 template <int OPT, int PDT, int ECC_BITS, int STATE>
 __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const __grid_constant__ StepParams p) {
   __shared__ float lut_m[256], lut_v[256];
-  if constexpr (STATE == FO_STATE_QUANT) build_luts(lut_m, lut_v);
-  const uint32_t total = p.first_block[p.n_leaves];
-  const uint32_t c0 = (uint32_t)((unsigned long long)total * blockIdx.x / gridDim.x);
-  const uint32_t c1 = (uint32_t)((unsigned long long)total * (blockIdx.x + 1) / gridDim.x);
-  if (c0 >= c1) return;
-  const uint32_t toff = threadIdx.x * kPiece;
-  int l = 0, hi = p.n_leaves;  // the leaf that holds chunk c0
-  while (hi - l > 1) {
-    const int mid = (l + hi) >> 1;
-    if (p.first_block[mid] <= c0) l = mid; else hi = mid;
+  __shared__ float lut_m_wide[STATE == FO_STATE_QUANT ? 256 * kLutCopies : 1];
+  if constexpr (STATE == FO_STATE_QUANT) {
+    build_luts(lut_m, lut_v);
+    build_wide_lut(lut_m, lut_m_wide);
   }
-  Raw<OPT, PDT, ECC_BITS, STATE> raw;
-  for (uint32_t c = c0; c < c1; ++l) {
+  const float* lut_mw = lut_m_wide + (STATE == FO_STATE_QUANT ? (threadIdx.x & (kLutCopies - 1)) : 0);
+  extern __shared__ __align__(16) unsigned char stage_mem[];  // p.stages stages of Stage::bytes(grad dtype)
+  using S = Stage<OPT, PDT, ECC_BITS, STATE>;
+  const uint32_t stage_bytes = (uint32_t)S::bytes(p.grad_dtype);
+  const uint32_t stage0 = (uint32_t)__cvta_generic_to_shared(stage_mem);
+  const uint32_t stage_end = stage0 + (uint32_t)p.stages * stage_bytes;
+  const uint32_t toff = threadIdx.x * kPiece;
+  const uint32_t grid = gridDim.x;
+  uint32_t c = blockIdx.x;  // this block's next position in the sequence
+  for (int l = 0; l < p.n_leaves; ++l) {
     const uint32_t first = p.first_block[l], next = p.first_block[l + 1];
-    const uint32_t lo = c - first;                         // chunk indices inside the leaf
-    const uint32_t end = (c1 < next ? c1 : next) - first;
-    c = first + end;
+    if (c >= next) continue;
+    const uint32_t end = next - first;  // chunks in this leaf
+    uint32_t ch = c - first;            // this block's first chunk inside the leaf
     const DevLeaf& L = p.leaf[l];
     const Hyp h = load_hyper<OPT>(p.hyper[p.hyper_of[l]]);
     // the CPU-path parameter hand-back (FO_FLAG_LP_DELTA) needs the old stored value to the end: IEEE path only
     bool hyper_ok = (h.flags & FO_FLAG_LP_DELTA) == 0;
     if constexpr (OPT == FO_OPT_ADAM) hyper_ok = hyper_ok && (h.flags & kFlagTameAdam) != 0;  // the reciprocal shortcut in the denominator
-    uint32_t hot_end = (leaf_is_hot<OPT>(p, l) && hyper_ok) ? (uint32_t)(L.n / kChunk) : 0u;  // whole chunks
-    if (hot_end > end) hot_end = end;
-    uint32_t ch = lo;
+    const uint32_t hot_end = (leaf_is_hot<OPT>(p, l) && hyper_ok) ? (uint32_t)(L.n / kChunk) : 0u;  // whole chunks
     if (ch < hot_end) {
+      const uint32_t stride = grid * (uint32_t)kChunk;
       uint32_t base = ch * (uint32_t)kChunk;
-      hot_load<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, base + toff, raw);
-      for (; ch < hot_end; ++ch, base += kChunk) {
+      // Copy pipeline: one group per chunk (empty past the end of the run, so that the count of
+      // groups still pending always tells which chunk has landed).  The stage filled in an
+      // iteration is the one read in the iteration before, whose values have been consumed.
+      uint32_t fill_ch = ch, fill_base = base, wr = stage0;
+      for (int k = 1; k < p.stages; ++k) {
+        if (fill_ch < hot_end) stage_fill<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, fill_base + toff, wr);
+        copy_commit();
+        fill_ch += grid; fill_base += stride; wr += stage_bytes;
+      }
+      uint32_t rd = stage0;
+      // the group scales go through registers, one chunk ahead
+      __half msc = __float2half(0.0f), vsc = msc;
+      if constexpr (STATE == FO_STATE_QUANT) {
+        msc = ((const __half*)L.mu_scales)[(base + toff) >> 5];
+        if constexpr (OPT == FO_OPT_ADAM) vsc = ((const __half*)L.nu_scales)[(base + toff) >> 5];
+      }
+      for (; ch < hot_end; ch += grid, base += stride) {
+        if (fill_ch < hot_end) stage_fill<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, fill_base + toff, wr);
+        copy_commit();
+        fill_ch += grid; fill_base += stride;
+        wr += stage_bytes;
+        if (wr == stage_end) wr = stage0;
+        if (p.stages == 4) copy_wait<3>();
+        else if (p.stages == 3) copy_wait<2>();
+        else copy_wait<1>();
+        Raw<OPT, PDT, ECC_BITS, STATE> raw;
+        stage_read<OPT, PDT, ECC_BITS, STATE>(p.grad_dtype, rd, raw);
+        rd += stage_bytes;
+        if (rd == stage_end) rd = stage0;
+        raw.msc = msc; raw.vsc = vsc;
+        if constexpr (STATE == FO_STATE_QUANT) {
+          if (ch + grid < hot_end) {
+            msc = ((const __half*)L.mu_scales)[(base + stride + toff) >> 5];
+            if constexpr (OPT == FO_OPT_ADAM) vsc = ((const __half*)L.nu_scales)[(base + stride + toff) >> 5];
+          }
+        }
         Unpacked u;
-        const bool rare = hot_unpack<false, OPT, PDT, ECC_BITS, STATE>(raw, p.grad_dtype, lut_m, lut_v, p.one, u);
-        // the next chunk's loads fly while this one is computed
-        if (ch + 1 < hot_end) hot_load<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, base + kChunk + toff, raw);
-        hot_finish<false, OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, base, p.one, rare, u, lut_m, lut_v, p.peers);
+        const bool rare = hot_unpack<false, OPT, PDT, ECC_BITS, STATE>(raw, p.grad_dtype, lut_mw, p.one, u);
+        hot_finish<false, OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, base, p.one, rare, u, lut_mw, p.peers);
       }
     }
-    for (; ch < end; ++ch)
+    for (; ch < end; ch += grid)
       cold_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, (unsigned long long)ch * kChunk, lut_m, lut_v, p.peers);
+    c = first + ch;
   }
 }
 
@@ -952,11 +1110,42 @@ struct LaunchInfo {
 };
 using LaunchFn = cudaError_t (*)(const StepParams&, const LaunchInfo&, cudaStream_t);
 
+// Shared memory of one SM that blocks may use, and what each block loses to the system.
+constexpr int kSmemPerSm = 227 * 1024, kSmemReservedPerBlock = 1024;
+
 template <int OPT, int PDT, int ECC_BITS, int STATE>
-cudaError_t launch_step(const StepParams& p, const LaunchInfo& info, cudaStream_t s) {
+cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStream_t s) {
+  auto kernel = step_kernel<OPT, PDT, ECC_BITS, STATE>;
+  static int static_smem = -1;  // the same on every device
+  if (static_smem < 0) {
+    cudaFuncAttributes attr;
+    cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
+    if (e != cudaSuccess) return e;
+    static_smem = (int)attr.sharedSizeBytes;
+  }
+  // as many stages as fit beside the tables with min_blocks(OPT) blocks on an SM
+  const int per_stage = Stage<OPT, PDT, ECC_BITS, STATE>::bytes(p_in.grad_dtype);
+  const int budget = kSmemPerSm / min_blocks(OPT) - kSmemReservedPerBlock - static_smem;
+  int stages = budget / per_stage;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return cudaErrorInvalidConfiguration;
+  const int dynamic_smem = stages * per_stage;
+  static bool opted_in[64] = {false};  // per device ordinal: the opt-in above 48 KB belongs to the device's copy of the function
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64 || !opted_in[dev]) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPerSm / min_blocks(OPT) - kSmemReservedPerBlock - static_smem);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) opted_in[dev] = true;
+  }
+  StepParams p = p_in;
+  p.stages = stages;
   unsigned int grid = (unsigned int)info.sm_count * min_blocks(OPT);
   if (grid > info.total_chunks) grid = info.total_chunks;
-  step_kernel<OPT, PDT, ECC_BITS, STATE><<<grid, kThreads, 0, s>>>(p);
+  kernel<<<grid, kThreads, dynamic_smem, s>>>(p);
   return cudaGetLastError();
 }
 template <int OPT, int PDT, int ECC_BITS>
