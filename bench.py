@@ -200,7 +200,7 @@ def run_ours(args):
     kernel_ms = {}  # per (param dtype code) -> list of launch durations
     pending = []
 
-    def timed_launch(opt, work, peers=None):
+    def timed_launch(opt, work, peers=None, grad_peers=None):
         by_bucket = {}
         for w in work:
             by_bucket.setdefault(w.bucket, []).append(w)
@@ -208,19 +208,20 @@ def run_ours(args):
         for bucket, items in by_bucket.items():
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            calls += eng.launch(opt, items, peers)
+            calls += eng.launch(opt, items, peers, grad_peers)
             e1.record()
             pending.append((bucket[1], sum(w.param.numel() for w in items), e0, e1))
         return calls
 
     launches = [0]
 
-    def counting_launch(opt, work, peers=None):
-        n = timed_launch(opt, work, peers)
+    def counting_launch(opt, work, peers=None, grad_peers=None):
+        n = timed_launch(opt, work, peers, grad_peers)
         launches[0] += n
         return n
 
-    zero = Zero1Optimizer("adamw", params, step_fn=counting_launch, fused_allgather=(world > 1 and not args.nccl_allgather), **HPARAMS)
+    zero = Zero1Optimizer("adamw", params, step_fn=counting_launch, fused_allgather=(world > 1 and not args.nccl_allgather),
+                          fused_reduce_scatter=(world > 1 and not args.nccl_reduce_scatter), **HPARAMS)
     del params
     torch.cuda.empty_cache()
     ggen = torch.Generator(device=device)
@@ -348,6 +349,7 @@ def finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline
             "data": "synthetic",
             "config": {"workload": args.workload, "leaves": len(shapes), "params": total_params, "optimizer": "flash_adamw",
                        **HPARAMS, "grad_dtype": "bf16", "parallelism": "single" if world == 1 else f"zero1x{world}",
+                       "reduce_scatter": None if world == 1 else ("nccl" if args.nccl_reduce_scatter else "fused into the step kernel (peer loads)"),
                        "allgather": None if world == 1 else ("nccl" if args.nccl_allgather else "fused into the step kernel (peer stores)"),
                        "l2": "working set per step (>= 14 B/param) exceeds the 126 MB L2, no flush needed"},
             "roofline": roofline, "cpu_baseline": base, "e2e": e2e, "gpu_launches": n_launch, "clocks": clocks,
@@ -368,6 +370,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (used for ncu captures)")
     ap.add_argument("--nccl-allgather", action="store_true", help="N > 1: NCCL all-gather after the step instead of peer stores inside it")
+    ap.add_argument("--nccl-reduce-scatter", action="store_true", help="N > 1: NCCL reduce-scatter before the step instead of peer loads inside it")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

@@ -79,12 +79,19 @@ def _ptr(t: Optional[torch.Tensor]) -> int:
     return 0 if t is None else t.data_ptr()
 
 
-def launch(opt: int, work: List[LeafWork], peer_param_offsets: Optional[List[int]] = None) -> int:
+def launch(opt: int, work: List[LeafWork], peer_param_offsets: Optional[List[int]] = None,
+           peer_grad_offsets: Optional[List[int]] = None) -> int:
     """Issue one fo_step per bucket (per <=16 hyper sets); returns the number of calls.
 
     peer_param_offsets: byte distances from every param address to the same element of each peer
-    GPU's replica; when given, the kernel also stores the updated parameters there."""
+    GPU's replica; when given, the kernel also stores the updated parameters there.
+    peer_grad_offsets: byte distances from every grad address to the same element of each peer GPU's
+    gradient buffer; when given, the kernel averages the gradients over the ranks as it reads them."""
     peers = np.asarray(peer_param_offsets or [], dtype=np.int64)
+    grad_peers = np.asarray(peer_grad_offsets or [], dtype=np.int64)
+    if len(peers) and len(grad_peers) and len(peers) != len(grad_peers):
+        raise ValueError("peer_param_offsets and peer_grad_offsets must name the same peers")
+    n_peers = max(len(peers), len(grad_peers))
     buckets: Dict[Tuple[Any, ...], List[LeafWork]] = {}
     for w in work:
         buckets.setdefault(w.bucket, []).append(w)
@@ -117,7 +124,8 @@ def launch(opt: int, work: List[LeafWork], peer_param_offsets: Optional[List[int
                 struct_size=ctypes.sizeof(_lib.FoStepDesc), opt=opt, param_dtype=pdt, grad_dtype=gdt, ecc_bits=ecc_bits,
                 state=state, group_size=group_size, n_leaves=len(pending), n_hypers=len(hyper_index),
                 leaves=leaves.ctypes.data, hypers=hypers.ctypes.data,
-                n_peers=len(peers), peer_param_offsets=peers.ctypes.data if len(peers) else None,
+                n_peers=n_peers, peer_param_offsets=peers.ctypes.data if len(peers) else None,
+                peer_grad_offsets=grad_peers.ctypes.data if len(grad_peers) else None,
             )
             device = torch.device("cuda", dev_index)
             with torch.cuda.device(device):

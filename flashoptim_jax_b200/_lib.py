@@ -60,6 +60,7 @@ class FoStepDesc(ctypes.Structure):
         ("n_leaves", ctypes.c_uint32), ("n_hypers", ctypes.c_uint32),
         ("leaves", ctypes.c_void_p), ("hypers", ctypes.c_void_p),
         ("n_peers", ctypes.c_uint32), ("reserved", ctypes.c_uint32), ("peer_param_offsets", ctypes.c_void_p),
+        ("peer_grad_offsets", ctypes.c_void_p),
     ]
 
 

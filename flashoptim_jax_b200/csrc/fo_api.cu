@@ -96,7 +96,8 @@ extern "C" int fo_step(const FoStepDesc* d, void* cuda_stream) {
     generic = d->group_size != 32;
   }
   if (d->n_peers > (uint32_t)kMaxPeers) return fail(FO_ERR_TOO_LARGE, "fo_step: %u peers, at most %d", d->n_peers, kMaxPeers);
-  if (d->n_peers > 0 && d->peer_param_offsets == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_step: n_peers without peer_param_offsets");
+  if (d->n_peers > 0 && d->peer_param_offsets == nullptr && d->peer_grad_offsets == nullptr)
+    return fail(FO_ERR_INVALID_ARG, "fo_step: n_peers without peer_param_offsets or peer_grad_offsets");
   if (d->n_peers > 0 && generic) return fail(FO_ERR_UNSUPPORTED, "fo_step: peer replicas need group_size 32");
   LaunchFn launch = find_launcher(d->opt, d->param_dtype, d->ecc_bits, d->state, generic);
   if (launch == nullptr) return fail(FO_ERR_UNSUPPORTED, "fo_step: no kernel for this combination");
@@ -129,8 +130,18 @@ extern "C" int fo_step(const FoStepDesc* d, void* cuda_stream) {
   p.grad_dtype = d->grad_dtype;
   p.group_size = d->state == FO_STATE_QUANT ? d->group_size : 32;
   p.one = 1.0f;
-  p.peers.n = (int)d->n_peers;
-  for (uint32_t r = 0; r < d->n_peers; ++r) p.peers.delta[r] = (long long)d->peer_param_offsets[r];
+  if (d->peer_param_offsets != nullptr) {
+    p.peers.n = (int)d->n_peers;
+    for (uint32_t r = 0; r < d->n_peers; ++r) p.peers.delta[r] = (long long)d->peer_param_offsets[r];
+  }
+  if (d->peer_grad_offsets != nullptr && d->n_peers > 0) {
+    const uint32_t ranks = d->n_peers + 1;
+    p.peers.ng = (int)d->n_peers;
+    for (uint32_t r = 0; r < d->n_peers; ++r) p.peers.gdelta[r] = (long long)d->peer_grad_offsets[r];
+    p.peers.neg_ranks = -(float)ranks;
+    p.peers.rcp_ranks = 1.0f / (float)ranks;  // correctly rounded (IEEE division on the host)
+    p.peers.ranks_pow2 = (ranks & (ranks - 1)) == 0;
+  }
 
   int count = 0;
   unsigned long long blocks = 0;

@@ -78,10 +78,19 @@ struct DevHyper {
 // updated parameter vector is also stored `delta[r]` bytes away from its local address, i.e. at the
 // same element of peer r's replica.  Plain stores through peer-mapped memory; no waiting on peers.
 constexpr int kMaxPeers = 7;
+// Reduce-scatter folded into the step: the gradient of an element is the mean over this rank's
+// value and the values `gdelta[r]` bytes away (the same element of peer r's gradient buffer):
+// fp32 sum in the order own, peer 0, peer 1, ..., divided by the number of ranks, rounded once to
+// the gradient dtype.  Plain loads through peer-mapped memory.
 struct Peers {
-  int n;
-  int pad;
+  int n;              // replicas that receive the parameter stores
+  int ng;             // peers whose gradients are read
   long long delta[kMaxPeers];
+  long long gdelta[kMaxPeers];
+  float neg_ranks;    // -(ng + 1)
+  float rcp_ranks;    // RN(1 / (ng + 1))
+  int ranks_pow2;     // the division by the rank count is exact for every input
+  int pad;
 };
 template <typename T>
 FO_DEVI void store_to_peers(const Peers& peers, T* local, const T& v) {
@@ -208,6 +217,19 @@ FO_DEVI float load_grad(const void* grad, int gdt, unsigned long long i) {
   if (gdt == FO_BF16) return Lp<FO_BF16>::to_f32(((const unsigned short*)grad)[i]);
   return Lp<FO_F16>::to_f32(((const unsigned short*)grad)[i]);
 }
+// fp32 value rounded to the gradient dtype and back
+FO_DEVI float round_to_grad_dtype(float x, int gdt) {
+  if (gdt == FO_BF16) return __bfloat162float(__float2bfloat16_rn(x));
+  if (gdt == FO_F16) return __half2float(__float2half_rn(x));
+  return x;
+}
+// the gradient of element i: the local value, or the mean over the ranks (see Peers)
+FO_DEVI float load_grad_mean(const void* grad, int gdt, unsigned long long i, const Peers& peers) {
+  float g = load_grad(grad, gdt, i);
+  if (peers.ng == 0) return g;
+  for (int r = 0; r < peers.ng; ++r) g = fadd(g, load_grad((const char*)grad + peers.gdelta[r], gdt, i));
+  return round_to_grad_dtype(fdiv(g, -peers.neg_ranks), gdt);
+}
 
 // One chunk, any alignment, any length: thread t owns elements base + 8t .. base + 8t + 7,
 // out-of-range elements count as zeros (flashoptim_jax/quantization.py:20-26).
@@ -231,7 +253,7 @@ __device__ __noinline__ void cold_chunk(const DevLeaf& L, const Hyp& h, int gdt,
     const unsigned long long i = i0 + j;
     m[j] = 0.0f; root[j] = 0.0f;
     if (i < n) {
-      const float g = load_grad(L.grad, gdt, i);
+      const float g = load_grad_mean(L.grad, gdt, i, peers);
       float theta, old_f32 = 0.0f;
       uint32_t pb = 0;
       if constexpr (PDT == FO_F32) {
@@ -433,7 +455,9 @@ struct Stage {
   static constexpr int kOffMu = kOffEcc + kEcc * kThreads;
   static constexpr int kOffNu = kOffMu + kMu * kThreads;
   static constexpr int kOffGrad = kOffNu + kNu * kThreads;
-  __host__ __device__ static constexpr int bytes(int gdt) { return kOffGrad + (gdt == FO_F32 ? 32 : 16) * kThreads; }
+  // the gradient comes last: this rank's piece, then one piece per peer whose gradients are averaged in
+  __host__ __device__ static constexpr int grad_bytes(int gdt) { return (gdt == FO_F32 ? 32 : 16) * kThreads; }
+  __host__ __device__ static constexpr int bytes(int gdt, int grad_peers) { return kOffGrad + grad_bytes(gdt) * (1 + grad_peers); }
 };
 constexpr int kMaxStages = FO_MAX_STAGES;
 FO_DEVI void copy_async16(uint32_t dst, const void* src) {
@@ -464,7 +488,7 @@ FO_DEVI uint2 lds64(uint32_t a) {
 // start the copies of this thread's piece at element i0 of every stream into the stage at
 // shared address st (the group scales are not staged: they are two bytes per 32 elements)
 template <int OPT, int PDT, int ECC_BITS, int STATE>
-FO_DEVI void stage_fill(const DevLeaf& L, const int gdt, const uint32_t i0, const uint32_t st) {
+FO_DEVI void stage_fill(const DevLeaf& L, const int gdt, const uint32_t i0, const uint32_t st, const Peers& peers) {
   using S = Stage<OPT, PDT, ECC_BITS, STATE>;
   const uint32_t t16 = threadIdx.x * 16u, t8 = threadIdx.x * 8u;
   if constexpr (PDT == FO_F32) {
@@ -486,11 +510,16 @@ FO_DEVI void stage_fill(const DevLeaf& L, const int gdt, const uint32_t i0, cons
       copy_async16_l1(st + S::kOffNu + 16u * kThreads + t16, (const float*)L.nu + i0 + 4);
     }
   }
-  if (gdt == FO_F32) {
-    copy_async16_l1(st + S::kOffGrad + t16, (const float*)L.grad + i0);
-    copy_async16_l1(st + S::kOffGrad + 16u * kThreads + t16, (const float*)L.grad + i0 + 4);
-  } else {
-    copy_async16(st + S::kOffGrad + t16, (const unsigned short*)L.grad + i0);
+  uint32_t gs = st + S::kOffGrad;
+  for (int r = -1; r < peers.ng; ++r) {  // own gradient, then the peers'
+    const char* g = (const char*)L.grad + (r < 0 ? 0ll : peers.gdelta[r]);
+    if (gdt == FO_F32) {
+      copy_async16_l1(gs + t16, (const float*)g + i0);
+      copy_async16_l1(gs + 16u * kThreads + t16, (const float*)g + i0 + 4);
+    } else {
+      copy_async16(gs + t16, (const unsigned short*)g + i0);
+    }
+    gs += (uint32_t)S::grad_bytes(gdt);
   }
 }
 
@@ -627,6 +656,51 @@ FO_DEVI bool hot_unpack(const Raw<OPT, PDT, ECC_BITS, STATE>& r, const int gdt, 
   } else if constexpr (STATE == FO_STATE_FULL) {
     pairs_of(r.m0, r.m1, u.m);
     if constexpr (OPT == FO_OPT_ADAM) pairs_of(r.v0, r.v1, u.v);
+  }
+  return rare;
+}
+
+FO_DEVI void grad_pairs(const uint4& w0, const uint4& w1, const int gdt, float2 (&o)[4]) {
+  if (gdt == FO_F32) pairs_of(w0, w1, o);
+  else if (gdt == FO_BF16) pairs_of16<FO_BF16>(w0, o);
+  else pairs_of16<FO_F16>(w0, o);
+}
+
+// Reduce-scatter folded into the step (see Peers): g holds this rank's gradients on entry and the
+// mean over the ranks, rounded to the gradient dtype, on return.  fetch(r, w0, w1) delivers the
+// words of peer r's piece.  Same contract for REPAIR as hot_unpack.
+template <bool REPAIR, typename Fetch>
+FO_DEVI bool merge_peer_grads(float2 (&g)[4], const int gdt, const Peers& peers, Fetch fetch) {
+  using namespace fast2;
+  bool rare = false;
+  for (int r = 0; r < peers.ng; ++r) {
+    uint4 w0, w1 = make_uint4(0u, 0u, 0u, 0u);
+    fetch(r, w0, w1);
+    float2 pg[4];
+    grad_pairs(w0, w1, gdt, pg);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) g[k] = add2(g[k], pg[k]);
+  }
+  float2 mean[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) mean[k] = div_by_rcp2(g[k], sp(peers.neg_ranks), sp(peers.rcp_ranks));
+  // a rank count that is not a power of two: the residual of the reciprocal division underflows for tiny sums
+  if (!peers.ranks_pow2 && !(minabs8(g) >= 7.8886091e-31f)) {
+    rare = true;
+    if constexpr (REPAIR) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) mean[k] = mk(fdiv(g[k].x, -peers.neg_ranks), fdiv(g[k].y, -peers.neg_ranks));
+    }
+  }
+  if (gdt == FO_BF16) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) unpack2<FO_BF16>(pack2<FO_BF16>(mean[k].x, mean[k].y), g[k].x, g[k].y);
+  } else if (gdt == FO_F16) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) unpack2<FO_F16>(pack2<FO_F16>(mean[k].x, mean[k].y), g[k].x, g[k].y);
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) g[k] = mean[k];
   }
   return rare;
 }
@@ -898,6 +972,18 @@ __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const in
   hot_load<OPT, PDT, ECC_BITS, STATE>(L, gdt, base + threadIdx.x * kPiece, raw);
   Unpacked u;
   hot_unpack<true, OPT, PDT, ECC_BITS, STATE>(raw, gdt, lut_mw, one, u);
+  if (peers.ng > 0) {
+    const uint32_t i0 = base + threadIdx.x * kPiece;
+    merge_peer_grads<true>(u.g, gdt, peers, [&](int r, uint4& w0, uint4& w1) {
+      const char* g = (const char*)L.grad + peers.gdelta[r];
+      if (gdt == FO_F32) {
+        w0 = __ldcs((const uint4*)((const float*)g + i0));
+        w1 = __ldcs((const uint4*)((const float*)g + i0) + 1);
+      } else {
+        w0 = __ldcs((const uint4*)((const unsigned short*)g + i0));
+      }
+    });
+  }
   hot_finish<true, OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, one, false, u, lut_mw, peers);
 }
 
@@ -944,7 +1030,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
   const float* lut_mw = lut_m_wide + (STATE == FO_STATE_QUANT ? (threadIdx.x & (kLutCopies - 1)) : 0);
   extern __shared__ __align__(16) unsigned char stage_mem[];  // p.stages stages of Stage::bytes(grad dtype)
   using S = Stage<OPT, PDT, ECC_BITS, STATE>;
-  const uint32_t stage_bytes = (uint32_t)S::bytes(p.grad_dtype);
+  const uint32_t stage_bytes = (uint32_t)S::bytes(p.grad_dtype, p.peers.ng);
   const uint32_t stage0 = (uint32_t)__cvta_generic_to_shared(stage_mem);
   const uint32_t stage_end = stage0 + (uint32_t)p.stages * stage_bytes;
   const uint32_t toff = threadIdx.x * kPiece;
@@ -969,7 +1055,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
       // iteration is the one read in the iteration before, whose values have been consumed.
       uint32_t fill_ch = ch, fill_base = base, wr = stage0;
       for (int k = 1; k < p.stages; ++k) {
-        if (fill_ch < hot_end) stage_fill<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, fill_base + toff, wr);
+        if (fill_ch < hot_end) stage_fill<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, fill_base + toff, wr, p.peers);
         copy_commit();
         fill_ch += grid; fill_base += stride; wr += stage_bytes;
       }
@@ -981,7 +1067,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
         if constexpr (OPT == FO_OPT_ADAM) vsc = ((const __half*)L.nu_scales)[(base + toff) >> 5];
       }
       for (; ch < hot_end; ch += grid, base += stride) {
-        if (fill_ch < hot_end) stage_fill<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, fill_base + toff, wr);
+        if (fill_ch < hot_end) stage_fill<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, fill_base + toff, wr, p.peers);
         copy_commit();
         fill_ch += grid; fill_base += stride;
         wr += stage_bytes;
@@ -991,6 +1077,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
         else copy_wait<1>();
         Raw<OPT, PDT, ECC_BITS, STATE> raw;
         stage_read<OPT, PDT, ECC_BITS, STATE>(p.grad_dtype, rd, raw);
+        const uint32_t peer_grads = rd + S::kOffGrad + (uint32_t)S::grad_bytes(p.grad_dtype);
         rd += stage_bytes;
         if (rd == stage_end) rd = stage0;
         raw.msc = msc; raw.vsc = vsc;
@@ -1001,7 +1088,15 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
           }
         }
         Unpacked u;
-        const bool rare = hot_unpack<false, OPT, PDT, ECC_BITS, STATE>(raw, p.grad_dtype, lut_mw, p.one, u);
+        bool rare = hot_unpack<false, OPT, PDT, ECC_BITS, STATE>(raw, p.grad_dtype, lut_mw, p.one, u);
+        if (p.peers.ng > 0) {
+          const bool odd = merge_peer_grads<false>(u.g, p.grad_dtype, p.peers, [&](int r, uint4& w0, uint4& w1) {
+            const uint32_t at = peer_grads + (uint32_t)r * (uint32_t)S::grad_bytes(p.grad_dtype) + threadIdx.x * 16u;
+            w0 = lds128(at);
+            if (p.grad_dtype == FO_F32) w1 = lds128(at + 16u * kThreads);
+          });
+          rare = rare || odd;
+        }
         hot_finish<false, OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, base, p.one, rare, u, lut_mw, p.peers);
       }
     }
@@ -1123,10 +1218,15 @@ cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStre
     if (e != cudaSuccess) return e;
     static_smem = (int)attr.sharedSizeBytes;
   }
-  // as many stages as fit beside the tables with min_blocks(OPT) blocks on an SM
-  const int per_stage = Stage<OPT, PDT, ECC_BITS, STATE>::bytes(p_in.grad_dtype);
-  const int budget = kSmemPerSm / min_blocks(OPT) - kSmemReservedPerBlock - static_smem;
-  int stages = budget / per_stage;
+  // as many stages as fit beside the tables with min_blocks(OPT) blocks on an SM; when the peers'
+  // gradient pieces make a stage too large for two of them, with one block on an SM
+  const int per_stage = Stage<OPT, PDT, ECC_BITS, STATE>::bytes(p_in.grad_dtype, p_in.peers.ng);
+  int blocks_per_sm = min_blocks(OPT);
+  int stages = (kSmemPerSm / blocks_per_sm - kSmemReservedPerBlock - static_smem) / per_stage;
+  if (stages < 2) {
+    blocks_per_sm = 1;
+    stages = (kSmemPerSm - kSmemReservedPerBlock - static_smem) / per_stage;
+  }
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return cudaErrorInvalidConfiguration;
   const int dynamic_smem = stages * per_stage;
@@ -1135,7 +1235,7 @@ cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStre
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64 || !opted_in[dev]) {
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPerSm / min_blocks(OPT) - kSmemReservedPerBlock - static_smem);
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPerSm - kSmemReservedPerBlock - static_smem);
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
@@ -1143,7 +1243,7 @@ cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStre
   }
   StepParams p = p_in;
   p.stages = stages;
-  unsigned int grid = (unsigned int)info.sm_count * min_blocks(OPT);
+  unsigned int grid = (unsigned int)info.sm_count * blocks_per_sm;
   if (grid > info.total_chunks) grid = info.total_chunks;
   kernel<<<grid, kThreads, dynamic_smem, s>>>(p);
   return cudaGetLastError();

@@ -159,10 +159,17 @@ class Zero1Optimizer:
                 symmetric (peer-mapped) memory and the kernel stores every updated parameter vector into
                 all peers' replicas over NVLink as it produces it; a one-element all-reduce afterwards
                 orders the peers' reads.  NCCL / CUDA ranks on one node only.
+    fused_reduce_scatter
+                fold the reduce-scatter into the step kernel: the flat gradient buffers are symmetric
+                memory too, and the kernel reads its slice of every rank's gradients over NVLink and
+                averages them (fp32 sum in rank order starting with its own, one rounding to the
+                gradient dtype) as it goes; a one-element all-reduce before the launch makes sure that
+                every rank's gradients are complete.  Same restrictions.
     """
 
     def __init__(self, optimizer: str, params: Any, *, group=None, step_fn: Optional[StepFn] = None,
-                 n_slices: Optional[int] = None, fused_allgather: bool = False, **hparams):
+                 n_slices: Optional[int] = None, fused_allgather: bool = False, fused_reduce_scatter: bool = False,
+                 **hparams):
         self.kind = optimizer
         if optimizer not in ("adamw", "adam", "lion", "sgd", "sgdw"):
             raise ValueError(f"unknown optimizer {optimizer!r}")
@@ -199,12 +206,17 @@ class Zero1Optimizer:
         device = leaves[0].device if leaves else torch.device("cpu")
         self.device = device
         self.fused_allgather = bool(fused_allgather) and self.world_size > 1
-        if self.fused_allgather:
+        self.fused_reduce_scatter = bool(fused_reduce_scatter) and self.world_size > 1
+        if self.fused_allgather or self.fused_reduce_scatter:
             if device.type != "cuda" or dist.get_backend(group) != "nccl":
-                raise ValueError("fused_allgather needs CUDA tensors and an NCCL process group")
+                raise ValueError("fused collectives need CUDA tensors and an NCCL process group")
             if self.world_size - 1 > _lib.FO_MAX_PEERS:
-                raise ValueError(f"fused_allgather supports at most {_lib.FO_MAX_PEERS + 1} ranks")
+                raise ValueError(f"fused collectives support at most {_lib.FO_MAX_PEERS + 1} ranks")
+            if n_slices not in (None, 1):
+                raise ValueError("fused collectives work on whole buckets: n_slices must be 1")
+            n_slices = 1
         self.peer_offsets: List[List[int]] = []
+        self.peer_grad_offsets: List[List[int]] = []
         self.buckets: List[BucketLayout] = []
         self.flat_params: List[torch.Tensor] = []
         self.flat_grads: List[torch.Tensor] = []
@@ -216,8 +228,8 @@ class Zero1Optimizer:
         grad_views: List[Optional[torch.Tensor]] = [None] * len(leaves)
         for dtype, ids in by_dtype.items():
             layout = plan_bucket(dtype, ids, [leaves[i].numel() for i in ids], self.world_size, n_slices)
-            flat_p = self._alloc_params(layout.total, dtype)
-            flat_g = torch.zeros(layout.total, dtype=dtype, device=device)
+            flat_p = self._alloc_flat(layout.total, dtype, self.fused_allgather, self.peer_offsets)
+            flat_g = self._alloc_flat(layout.total, dtype, self.fused_reduce_scatter, self.peer_grad_offsets)
             for i, start in zip(ids, layout.starts):
                 n = leaves[i].numel()
                 flat_p[start:start + n].copy_(leaves[i].reshape(-1))
@@ -227,10 +239,12 @@ class Zero1Optimizer:
             self.flat_params.append(flat_p)
             self.flat_grads.append(flat_g)
             # one rank owns everything: the "scattered" gradient is the flat buffer itself
-            self.grad_shards.append(flat_g if self.world_size == 1 else torch.zeros(layout.shard, dtype=dtype, device=device))
+            # (nor is there a scattered copy when the kernel reads the peers' gradients itself)
+            own_shard = self.world_size > 1 and not self.fused_reduce_scatter
+            self.grad_shards.append(torch.zeros(layout.shard, dtype=dtype, device=device) if own_shard else flat_g)
         self.params = self.treedef.unflatten(param_views)
         self.grads = self.treedef.unflatten(grad_views)
-        if self.fused_allgather:
+        if self.fused_allgather or self.fused_reduce_scatter:
             self._token = torch.zeros(1, dtype=torch.float32, device=device)
             dist.all_reduce(self._token, group=self.group)  # every rank has filled its replica before anyone writes into it
         # state of the segments this rank owns, keyed by (bucket, segment index)
@@ -241,10 +255,11 @@ class Zero1Optimizer:
 
     # ---- construction helpers ---------------------------------------------------------------------
 
-    def _alloc_params(self, n: int, dtype: torch.dtype) -> torch.Tensor:
-        """Flat parameter buffer; with fused_allgather a symmetric allocation whose peer mappings give the
-        byte offsets from this rank's replica to every other rank's."""
-        if not self.fused_allgather:
+    def _alloc_flat(self, n: int, dtype: torch.dtype, symmetric: bool, offsets: List[List[int]]) -> torch.Tensor:
+        """Flat buffer of a bucket; when a fused collective works on it, a symmetric allocation whose peer
+        mappings give the byte offsets from this rank's buffer to every other rank's (appended to `offsets`,
+        peers in rank order)."""
+        if not symmetric:
             return torch.zeros(n, dtype=dtype, device=self.device)
         import torch.distributed._symmetric_memory as symm_mem
 
@@ -253,7 +268,7 @@ class Zero1Optimizer:
         pg = self.group if self.group is not None else dist.group.WORLD
         handle = symm_mem.rendezvous(buf, pg.group_name)
         ptrs = list(handle.buffer_ptrs)
-        self.peer_offsets.append([int(ptrs[r]) - int(ptrs[self.rank]) for r in range(self.world_size) if r != self.rank])
+        offsets.append([int(ptrs[r]) - int(ptrs[self.rank]) for r in range(self.world_size) if r != self.rank])
         self._symm_handles = getattr(self, "_symm_handles", []) + [handle]
         return buf
 
@@ -326,6 +341,7 @@ class Zero1Optimizer:
         dev_index = self.device.index if self.device.type == "cuda" else -1
         for b, layout in enumerate(self.buckets):
             flat_p, g_shard = self.flat_params[b], self.grad_shards[b]
+            own_shard = g_shard is not self.flat_grads[b]  # else gradients are addressed like parameters
             for s, seg in enumerate(layout.segments[self.rank]):
                 config = self.configs[seg.leaf]
                 lr = utils._resolve_learning_rate(config["learning_rate"], count_before)
@@ -341,7 +357,7 @@ class Zero1Optimizer:
                 bucket = (dev_index, DTYPE_CODE[layout.dtype], DTYPE_CODE[layout.dtype], ecc_bits, state_kind, 32)
                 at = flat_position(layout, self.rank, seg.offset)
                 work.append(eng.LeafWork(
-                    bucket, g_shard[seg.offset:seg.offset + n], flat_p[at:at + n],
+                    bucket, g_shard[seg.offset:seg.offset + n] if own_shard else g_shard[at:at + n], flat_p[at:at + n],
                     st.ecc, st.mu, st.mu_scales, st.nu, st.nu_scales, self._hyper(config, lr, self.count + 1)))
                 meta.append((seg.leaf, b, seg.slice))
         self._static_work = [(w, leaf, b, sl) for w, (leaf, b, sl) in zip(work, meta)]
@@ -414,15 +430,23 @@ class Zero1Optimizer:
             self._step_pipelined()
             self.count += 1
             return self.params
-        self.reduce_scatter_grads()
-        if self.fused_allgather:
+        if self.fused_reduce_scatter:
+            dist.all_reduce(self._token, group=self.group)  # every rank's gradients are complete before any kernel reads them
+        else:
+            self.reduce_scatter_grads()
+        if self.fused_allgather or self.fused_reduce_scatter:
             work = self.local_work()
             for b in range(len(self.buckets)):
                 items = [w for w, (_, _, wb, _) in zip(work, self._static_work) if wb == b]
                 if items:
-                    self._step_fn(self.opt_code, items, self.peer_offsets[b])
+                    self._step_fn(self.opt_code, items, self.peer_offsets[b] if self.fused_allgather else None,
+                                  self.peer_grad_offsets[b] if self.fused_reduce_scatter else None)
             self.count += 1
-            dist.all_reduce(self._token, group=self.group)  # all ranks' kernels, hence all peer stores, are complete
+            if self.fused_allgather:
+                # all ranks' kernels are complete: their stores into this replica, their reads of these gradients
+                dist.all_reduce(self._token, group=self.group)
+            else:
+                self.all_gather_params()  # a collective, hence also the barrier that protects the gradients
             return self.params
         self._step_fn(self.opt_code, self.local_work())
         self.count += 1

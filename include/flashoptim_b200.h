@@ -24,7 +24,7 @@
 extern "C" {
 #endif
 
-#define FO_ABI_VERSION 2
+#define FO_ABI_VERSION 3
 
 /* status codes */
 #define FO_OK 0
@@ -128,7 +128,16 @@ typedef struct FoStepDesc {
    * of their replicas and makes the peers wait for this stream before they read again. */
   uint32_t n_peers;
   uint32_t reserved;
-  const int64_t* peer_param_offsets;
+  const int64_t* peer_param_offsets; /* NULL: parameters are stored locally only */
+  /* ZeRO-1 reduce-scatter folded into the step (same remark): the gradient of element i of a
+   * leaf is the mean over the ranks of the values at (grad address + peer_grad_offsets[r]),
+   * r < n_peers, and the local one: summed in fp32 in the order local, peer 0, peer 1, ...,
+   * divided by (n_peers + 1), rounded once to grad_dtype.  Each leaf's `grad` then points into this
+   * rank's copy of the full gradient array.  Plain loads; the caller makes sure every peer has
+   * finished writing its gradients before the launch and does not overwrite them before all
+   * ranks' kernels have completed.  NULL: the local gradient is used as it is.
+   * With n_peers > 0 at least one of the two offset tables must be given; group size 32 only. */
+  const int64_t* peer_grad_offsets;
 } FoStepDesc;
 #define FO_MAX_PEERS 7
 

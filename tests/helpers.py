@@ -105,7 +105,8 @@ def oracle_step(opt: int, grad: np.ndarray, leaf: LeafArrays, state: int, group_
 
 
 def abi_step(opt: int, grads: List, leaves: List[LeafArrays], state: int, group_size: int, hypers: List, hyper_of: List[int],
-             param_dtype: int, grad_dtype: int, ecc_bits: int, stream: int = 0, expect_ok: bool = True) -> int:
+             param_dtype: int, grad_dtype: int, ecc_bits: int, stream: int = 0, expect_ok: bool = True,
+             peer_param_offsets=None, peer_grad_offsets=None) -> int:
     """One fo_step call through the C ABI on torch device tensors (in place)."""
     from flashoptim_jax_b200 import _lib
 
@@ -127,6 +128,13 @@ def abi_step(opt: int, grads: List, leaves: List[LeafArrays], state: int, group_
     d = _lib.FoStepDesc(struct_size=ctypes.sizeof(_lib.FoStepDesc), opt=opt, param_dtype=param_dtype, grad_dtype=grad_dtype,
                         ecc_bits=ecc_bits, state=state, group_size=group_size, n_leaves=len(leaves), n_hypers=len(hypers),
                         leaves=ctypes.cast(L, ctypes.c_void_p), hypers=ctypes.cast(H, ctypes.c_void_p))
+    keep = []
+    for name, offs in (("peer_param_offsets", peer_param_offsets), ("peer_grad_offsets", peer_grad_offsets)):
+        if offs is not None:
+            arr = (ctypes.c_int64 * len(offs))(*[int(o) for o in offs])
+            keep.append(arr)
+            setattr(d, name, ctypes.cast(arr, ctypes.c_void_p))
+            d.n_peers = len(offs)
     rc = _lib.lib().fo_step(ctypes.byref(d), stream)
     if expect_ok:
         _lib.check(rc)

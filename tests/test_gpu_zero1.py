@@ -60,7 +60,7 @@ def test_one_rank_equals_plain_step():
             assert a.dtype == b.dtype and torch.equal(a.cpu(), b.cpu())
 
 
-def _worker(rank, world, port, out, fused=False):
+def _worker(rank, world, port, out, mode="nccl", own_grads=False):
     import torch
     import torch.distributed as dist
 
@@ -72,10 +72,12 @@ def _worker(rank, world, port, out, fused=False):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        # three slices exercise the pipelined NCCL path; fused: all-gather by peer stores inside the kernel
-        z = Zero1Optimizer("adamw", _params(dev), n_slices=1 if fused else 3, fused_allgather=fused, **HP)
+        # nccl: three slices exercise the pipelined NCCL path; fused_ag: all-gather by peer stores inside the
+        # kernel; fused: reduce-scatter by peer loads inside the kernel as well
+        z = Zero1Optimizer("adamw", _params(dev), n_slices=3 if mode == "nccl" else 1, fused_allgather=mode != "nccl",
+                           fused_reduce_scatter=mode == "fused", **HP)
         for t in range(3):
-            z.step(_grads(t, dev))
+            z.step(_grads(t + (100 * rank if own_grads else 0), dev))
         torch.cuda.synchronize()
         state = z.gather_state(dst=0)
         if rank == 0:
@@ -84,8 +86,14 @@ def _worker(rank, world, port, out, fused=False):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("fused", [False, True], ids=["nccl_allgather", "fused_allgather"])
-def test_two_nccl_ranks_equal_one_rank(tmp_path, fused):
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("mode", ["nccl", "fused_ag", "fused"])
+def test_two_nccl_ranks_equal_one_rank(tmp_path, mode):
     import torch
     import torch.multiprocessing as mp
 
@@ -100,11 +108,37 @@ def test_two_nccl_ranks_equal_one_rank(tmp_path, fused):
         single.step(_grads(t, dev))
     want_p = [p.cpu() for p in tree.tree_leaves(single.params)]
     want_s = [s.cpu() for s in tree.tree_leaves(single.gather_state())]
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        port = s.getsockname()[1]
     out = str(tmp_path / "r0.pt")
-    mp.spawn(_worker, args=(2, port, out, fused), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), out, mode), nprocs=2, join=True)
+    got = torch.load(out, weights_only=False)
+    for a, b in zip(got["params"], want_p):
+        assert torch.equal(a, b)
+    for a, b in zip(got["state"], want_s):
+        assert a.dtype == b.dtype and torch.equal(a, b)
+
+
+@pytest.mark.parametrize("mode", ["fused", "nccl"])
+def test_two_ranks_with_their_own_gradients_step_on_the_mean(tmp_path, mode):
+    """Different gradients on the two ranks: the result is the one-rank step on their mean (fp32 sum, halved,
+    rounded once to the gradient dtype) - by the kernel's own averaging, and by NCCL's for two ranks."""
+    import torch
+    import torch.multiprocessing as mp
+
+    from flashoptim_jax_b200 import tree
+    from flashoptim_jax_b200.zero1 import Zero1Optimizer
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    dev = torch.device("cuda", 0)
+    single = Zero1Optimizer("adamw", _params(dev), **HP)
+    for t in range(3):
+        g0, g1 = _grads(t, dev), _grads(t + 100, dev)
+        mean = tree.tree_map(lambda a, b: ((a.float() + b.float()) * 0.5).to(a.dtype), g0, g1)
+        single.step(mean)
+    want_p = [p.cpu() for p in tree.tree_leaves(single.params)]
+    want_s = [s.cpu() for s in tree.tree_leaves(single.gather_state())]
+    out = str(tmp_path / "r0.pt")
+    mp.spawn(_worker, args=(2, _free_port(), out, mode, True), nprocs=2, join=True)
     got = torch.load(out, weights_only=False)
     for a, b in zip(got["params"], want_p):
         assert torch.equal(a, b)

@@ -22,14 +22,14 @@ def test_library_loads_and_exports_every_declared_symbol():
     lib = _lib.lib()
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.fo_version() == 2
+    assert lib.fo_version() == 3
     assert lib.fo_status_string(0) == b"ok"
 
 
 def test_struct_sizes_match_the_header_layout():
     assert ctypes.sizeof(_lib.FoHyper) == 48
     assert ctypes.sizeof(_lib.FoLeaf) == 72
-    assert ctypes.sizeof(_lib.FoStepDesc) == 72
+    assert ctypes.sizeof(_lib.FoStepDesc) == 80
 
 
 def test_fo_step_rejects_bad_descriptors_without_touching_a_gpu():
