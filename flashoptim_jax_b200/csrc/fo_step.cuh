@@ -107,7 +107,7 @@ struct StepParams {
   int32_t grad_dtype;
   int32_t group_size;
   float one;  // 1.0f the compiler cannot see through (see fast2::sum2)
-  int32_t stages;  // shared-memory stages of the copy pipeline (2..kMaxStages), set by the launcher
+  int32_t stages;  // shared-memory stages of the copy pipeline (2..8), set by the launcher
   Peers peers;
 };
 
@@ -459,7 +459,11 @@ struct Stage {
   __host__ __device__ static constexpr int grad_bytes(int gdt) { return (gdt == FO_F32 ? 32 : 16) * kThreads; }
   __host__ __device__ static constexpr int bytes(int gdt, int grad_peers) { return kOffGrad + grad_bytes(gdt) * (1 + grad_peers); }
 };
-constexpr int kMaxStages = FO_MAX_STAGES;
+constexpr int kMaxStages = FO_MAX_STAGES;   // local streams: deeper brings nothing (measured 2 = 3 = 4)
+#ifndef FO_MAX_STAGES_PEERS
+#define FO_MAX_STAGES_PEERS 8
+#endif
+constexpr int kMaxStagesPeers = FO_MAX_STAGES_PEERS;  // gradients read from peers over NVLink: several times the latency to cover
 FO_DEVI void copy_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -1072,9 +1076,15 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
         fill_ch += grid; fill_base += stride;
         wr += stage_bytes;
         if (wr == stage_end) wr = stage0;
-        if (p.stages == 4) copy_wait<3>();
-        else if (p.stages == 3) copy_wait<2>();
-        else copy_wait<1>();
+        switch (p.stages) {  // all but the oldest group may still be pending
+          case 2: copy_wait<1>(); break;
+          case 3: copy_wait<2>(); break;
+          case 4: copy_wait<3>(); break;
+          case 5: copy_wait<4>(); break;
+          case 6: copy_wait<5>(); break;
+          case 7: copy_wait<6>(); break;
+          default: copy_wait<7>(); break;
+        }
         Raw<OPT, PDT, ECC_BITS, STATE> raw;
         stage_read<OPT, PDT, ECC_BITS, STATE>(p.grad_dtype, rd, raw);
         const uint32_t peer_grads = rd + S::kOffGrad + (uint32_t)S::grad_bytes(p.grad_dtype);
@@ -1227,7 +1237,8 @@ cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStre
     blocks_per_sm = 1;
     stages = (kSmemPerSm - kSmemReservedPerBlock - static_smem) / per_stage;
   }
-  if (stages > kMaxStages) stages = kMaxStages;
+  const int max_stages = p_in.peers.ng > 0 ? kMaxStagesPeers : kMaxStages;
+  if (stages > max_stages) stages = max_stages;
   if (stages < 2) return cudaErrorInvalidConfiguration;
   const int dynamic_smem = stages * per_stage;
   static bool opted_in[64] = {false};  // per device ordinal: the opt-in above 48 KB belongs to the device's copy of the function
