@@ -355,6 +355,16 @@ def finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline
             "roofline": roofline, "cpu_baseline": base, "e2e": e2e, "gpu_launches": n_launch, "clocks": clocks,
             "hbm_gbs_whole_step": total_params * BYTES_PER_PARAM_BF16_ECC16 / (ms_per_step * 1e-3) / 1e9,
         }
+        if world > 1:
+            # What must cross NVLink per GPU and direction in one ZeRO-1 step: (N-1)/N of the gradients in
+            # (reduce-scatter) and of the parameters out (all-gather), and the same amounts the other way
+            # for the peers.  770 GB/s: peer copy per direction measured on this pool.
+            grad_bytes = sum(g.numel() * g.element_size() for g in pytree.tree_leaves(zero.grads))
+            param_bytes = sum(q.numel() * q.element_size() for q in pytree.tree_leaves(zero.params))
+            per_direction = (grad_bytes + param_bytes) * (world - 1) / world
+            achieved = per_direction / (ms_per_step * 1e-3) / 1e9
+            line["nvlink"] = {"bytes_per_direction_per_gpu": per_direction, "achieved": achieved, "peak": 770.0, "unit": "GB/s",
+                              "frac": achieved / 770.0, "floor_ms": per_direction / 770e9 * 1e3}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
