@@ -4,8 +4,10 @@
     python bench.py --impl reference ...                     (the reference's CPU path, restated)
 
 One step = one pass of the fused update over the whole pytree.  With N > 1 the step is
-ZeRO-1: NCCL reduce-scatter(mean) of the bf16 gradients, the fused kernel on the rank's
-slice, NCCL all-gather of the updated parameters (launch with torchrun, one rank per GPU).
+ZeRO-1 (launch with torchrun, one rank per GPU): reduce-scatter(mean) of the bf16 gradients,
+the fused kernel on the rank's slice, all-gather of the updated parameters - both collectives
+inside the kernel over NVLink peer pointers by default, through NCCL with --nccl-reduce-scatter /
+--nccl-allgather.
 Inputs are synthetic (seeded normal draws with the configured shapes and scales).  Rank 0
 prints ONE JSON line.
 """
