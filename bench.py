@@ -223,7 +223,8 @@ def run_ours(args):
         return n
 
     zero = Zero1Optimizer("adamw", params, step_fn=counting_launch, fused_allgather=(world > 1 and not args.nccl_allgather),
-                          fused_reduce_scatter=(world > 1 and not args.nccl_reduce_scatter), **HPARAMS)
+                          fused_reduce_scatter=(world > 1 and not args.nccl_reduce_scatter and args.clip is None),
+                          max_grad_norm=args.clip, **HPARAMS)
     del params
     torch.cuda.empty_cache()
     ggen = torch.Generator(device=device)
@@ -258,6 +259,8 @@ def run_ours(args):
     clocks = sampler.stop()
     elapsed_ms = e0.elapsed_time(e1)
     n_launch = launches[0]
+    if args.clip is not None:
+        n_launch += 2 * len(zero.buckets) * args.steps  # fo_sq_norm: partial sums and their fixed-order total, per dtype
     for code, n_par, a, b in pending:
         kernel_ms.setdefault(code, []).append((n_par, a.elapsed_time(b)))
     if world > 1:
@@ -351,7 +354,8 @@ def finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline
             "data": "synthetic",
             "config": {"workload": args.workload, "leaves": len(shapes), "params": total_params, "optimizer": "flash_adamw",
                        **HPARAMS, "grad_dtype": "bf16", "parallelism": "single" if world == 1 else f"zero1x{world}",
-                       "reduce_scatter": None if world == 1 else ("nccl" if args.nccl_reduce_scatter else "fused into the step kernel (peer loads)"),
+                       "reduce_scatter": None if world == 1 else ("nccl" if (args.nccl_reduce_scatter or args.clip is not None) else "fused into the step kernel (peer loads)"),
+                       "clip_global_norm": args.clip,
                        "allgather": None if world == 1 else ("nccl" if args.nccl_allgather else "fused into the step kernel (peer stores)"),
                        "l2": "working set per step (>= 14 B/param) exceeds the 126 MB L2, no flush needed"},
             "roofline": roofline, "cpu_baseline": base, "e2e": e2e, "gpu_launches": n_launch, "clocks": clocks,
@@ -382,6 +386,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (used for ncu captures)")
     ap.add_argument("--nccl-allgather", action="store_true", help="N > 1: NCCL all-gather after the step instead of peer stores inside it")
+    ap.add_argument("--clip", type=float, default=None,
+                    help="clip the gradients at this global norm inside the step (adds the sum-of-squares sweep; off by default)")
     ap.add_argument("--nccl-reduce-scatter", action="store_true", help="N > 1: NCCL reduce-scatter before the step instead of peer loads inside it")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":

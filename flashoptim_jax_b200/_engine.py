@@ -9,7 +9,9 @@ fo_step() call that covers all its leaves in a single launch.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
+import threading
 from typing import Any, Dict, List, NamedTuple, Optional, Tuple
 
 import numpy as np
@@ -79,6 +81,61 @@ def _ptr(t: Optional[torch.Tensor]) -> int:
     return 0 if t is None else t.data_ptr()
 
 
+# ---- global-norm clipping folded into the step ---------------------------------------------------
+
+_clip = threading.local()
+
+
+@contextlib.contextmanager
+def grad_clip(sq_norm: torch.Tensor, max_norm: float):
+    """While active, every launch rescales its gradients as optax.clip_by_global_norm does
+    (examples/train_gpt2_pretrain.py:56-70): `sq_norm` is a one-element float64 device tensor with the
+    sum of squares of all gradients of the step (see sq_norm_of)."""
+    if sq_norm.dtype != torch.float64 or sq_norm.numel() != 1 or not sq_norm.is_cuda:
+        raise ValueError("sq_norm must be a one-element float64 CUDA tensor")
+    previous = getattr(_clip, "value", None)
+    _clip.value = (sq_norm, float(max_norm))
+    try:
+        yield
+    finally:
+        _clip.value = previous
+
+
+_workspaces: Dict[int, torch.Tensor] = {}
+
+
+def sq_norm_of(tensors: List[torch.Tensor], out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+    """Sum of squares of the given CUDA tensors (fp32 / bf16 / fp16, one device) into a one-element
+    float64 tensor, on the current stream, without a host round trip (fo_sq_norm, one call per dtype)."""
+    tensors = [t for t in tensors if t.numel() > 0]
+    if not tensors and out is None:
+        raise ValueError("sq_norm_of needs a tensor or an output to tell the device")
+    device = tensors[0].device if tensors else out.device
+    if out is None:
+        out = torch.zeros(1, dtype=torch.float64, device=device)
+    lib = _lib.lib()
+    ws = _workspaces.get(device.index)
+    if ws is None:
+        ws = _workspaces[device.index] = torch.empty(_lib.FO_SQ_NORM_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+    by_dtype: Dict[torch.dtype, List[torch.Tensor]] = {}
+    for t in tensors:
+        if t.dtype not in DTYPE_CODE:
+            raise ValueError(f"sq_norm_of: unsupported dtype {t.dtype}")
+        if t.device != device:
+            raise ValueError("sq_norm_of: tensors on several devices")
+        by_dtype.setdefault(t.dtype, []).append(t.contiguous())
+    first = True
+    with torch.cuda.device(device):
+        for dtype, ts in by_dtype.items() or [(torch.float32, [])]:
+            table = (_lib.FoArray * max(1, len(ts)))()
+            for i, t in enumerate(ts):
+                table[i].data, table[i].n = t.data_ptr(), t.numel()
+            _lib.check(lib.fo_sq_norm(table, len(ts), DTYPE_CODE[dtype], int(accumulate or not first), out.data_ptr(),
+                                      ws.data_ptr(), stream_ptr(device)))
+            first = False
+    return out
+
+
 def launch(opt: int, work: List[LeafWork], peer_param_offsets: Optional[List[int]] = None,
            peer_grad_offsets: Optional[List[int]] = None) -> int:
     """Issue one fo_step per bucket (per <=16 hyper sets); returns the number of calls.
@@ -127,6 +184,9 @@ def launch(opt: int, work: List[LeafWork], peer_param_offsets: Optional[List[int
                 n_peers=n_peers, peer_param_offsets=peers.ctypes.data if len(peers) else None,
                 peer_grad_offsets=grad_peers.ctypes.data if len(grad_peers) else None,
             )
+            clip = getattr(_clip, "value", None)
+            if clip is not None:
+                desc.grad_sq_norm, desc.max_grad_norm = clip[0].data_ptr(), clip[1]
             device = torch.device("cuda", dev_index)
             with torch.cuda.device(device):
                 _lib.check(lib.fo_step(ctypes.byref(desc), stream_ptr(device)))

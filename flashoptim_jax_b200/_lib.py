@@ -27,8 +27,9 @@ FO_SELFTEST_GROUP_DIV, FO_SELFTEST_CODE_TABLES, FO_SELFTEST_RCP, FO_SELFTEST_PAC
 EXPORTS = (
     "fo_step", "fo_quantize_momentum", "fo_dequantize_momentum", "fo_quantize_variance",
     "fo_dequantize_variance", "fo_split", "fo_reconstruct", "fo_selftest", "fo_selftest_static", "fo_version",
-    "fo_status_string", "fo_last_error",
+    "fo_status_string", "fo_last_error", "fo_sq_norm",
 )
+FO_SQ_NORM_WORKSPACE_BYTES = 16384
 
 
 class FoHyper(ctypes.Structure):
@@ -61,7 +62,12 @@ class FoStepDesc(ctypes.Structure):
         ("leaves", ctypes.c_void_p), ("hypers", ctypes.c_void_p),
         ("n_peers", ctypes.c_uint32), ("reserved", ctypes.c_uint32), ("peer_param_offsets", ctypes.c_void_p),
         ("peer_grad_offsets", ctypes.c_void_p),
+        ("grad_sq_norm", ctypes.c_void_p), ("max_grad_norm", ctypes.c_float), ("reserved2", ctypes.c_uint32),
     ]
+
+
+class FoArray(ctypes.Structure):
+    _fields_ = [("data", ctypes.c_void_p), ("n", ctypes.c_uint64)]
 
 
 class NativeLibraryError(RuntimeError):
@@ -104,6 +110,8 @@ def lib() -> ctypes.CDLL:
     cdll.fo_selftest.argtypes = [i32, ctypes.c_int64, ctypes.POINTER(ctypes.c_uint64), vp]
     cdll.fo_selftest_static.restype = ctypes.c_int
     cdll.fo_selftest_static.argtypes = [i32, ctypes.c_int64, ctypes.POINTER(ctypes.c_uint64), ctypes.c_uint32, vp]
+    cdll.fo_sq_norm.restype = ctypes.c_int
+    cdll.fo_sq_norm.argtypes = [ctypes.POINTER(FoArray), ctypes.c_uint32, i32, i32, vp, vp, vp]
     cdll.fo_version.restype = ctypes.c_int
     cdll.fo_version.argtypes = []
     cdll.fo_status_string.restype = ctypes.c_char_p

@@ -36,7 +36,7 @@ _KINDS = (("quant", 0), ("full", 1), ("generic", 3))
 
 
 def _units() -> List[Tuple[str, str, List[str]]]:
-    units = [(name, name + ".cu", []) for name in ("fo_api", "fo_codec", "fo_selftest")]
+    units = [(name, name + ".cu", []) for name in ("fo_api", "fo_codec", "fo_selftest", "fo_norm")]
     for oname, omacro in _OPTS:
         for kname, kind in _KINDS:
             units.append((f"fo_step_{oname}_{kname}", "fo_step_inst.cu",

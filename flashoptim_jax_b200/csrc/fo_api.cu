@@ -143,6 +143,9 @@ extern "C" int fo_step(const FoStepDesc* d, void* cuda_stream) {
     p.peers.ranks_pow2 = (ranks & (ranks - 1)) == 0;
   }
 
+  p.sq_norm = d->grad_sq_norm;
+  p.max_norm = d->max_grad_norm;
+
   int count = 0;
   unsigned long long blocks = 0;
   auto flush = [&]() -> int {

@@ -1,0 +1,132 @@
+// Sum of squares of a gradient pytree (the global norm of optax.clip_by_global_norm, which the
+// reference's GPT-2 recipe chains in front of the optimizer, examples/train_gpt2_pretrain.py:56-70).
+// A pure read sweep: 128-bit loads, squares exact in fp32, eight-element runs summed in fp32 and
+// added to a per-thread double; block and grid reductions in double in a fixed order.
+#include "fo_step.cuh"
+
+namespace fo {
+int fail(int code, const char* fmt, ...);
+
+constexpr int kNormMaxArrays = 160;   // per launch (kernel-parameter table)
+constexpr int kNormBlocksPerSm = 4;
+constexpr int kNormMaxBlocks = 2048;  // doubles in the workspace
+
+struct NormParams {
+  const void* data[kNormMaxArrays];
+  unsigned long long n[kNormMaxArrays];
+  uint32_t first_chunk[kNormMaxArrays + 1];
+  uint8_t aligned[kNormMaxArrays];
+  int32_t n_arrays;
+  int32_t dtype;
+};
+
+FO_DEVI float sq_run(const uint4& w0, const uint4& w1, int dt) {
+  float2 v[4];
+  grad_pairs(w0, w1, dt, v);
+  float s = 0.0f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) s = __fmaf_rn(v[k].y, v[k].y, __fmaf_rn(v[k].x, v[k].x, s));
+  return s;
+}
+
+__global__ void __launch_bounds__(kThreads) sq_norm_partial(const __grid_constant__ NormParams p, double* partials) {
+  __shared__ double warp_sums[kThreads / 32];
+  double acc = 0.0;
+  const uint32_t total = p.first_chunk[p.n_arrays];
+  int a = 0;
+  for (uint32_t c = blockIdx.x; c < total; c += gridDim.x) {
+    while (c >= p.first_chunk[a + 1]) ++a;
+    const unsigned long long i0 = (unsigned long long)(c - p.first_chunk[a]) * kChunk + (unsigned long long)threadIdx.x * kPiece;
+    const unsigned long long n = p.n[a];
+    if (i0 >= n) continue;
+    if (p.aligned[a] && i0 + kPiece <= n) {
+      uint4 w0, w1 = make_uint4(0u, 0u, 0u, 0u);
+      if (p.dtype == FO_F32) {
+        w0 = __ldcs((const uint4*)((const float*)p.data[a] + i0));
+        w1 = __ldcs((const uint4*)((const float*)p.data[a] + i0) + 1);
+      } else {
+        w0 = __ldcs((const uint4*)((const unsigned short*)p.data[a] + i0));
+      }
+      acc += (double)sq_run(w0, w1, p.dtype);
+    } else {
+      float s = 0.0f;
+      for (int j = 0; j < kPiece && i0 + j < n; ++j) {
+        const float g = load_grad(p.data[a], p.dtype, i0 + j);
+        s = __fmaf_rn(g, g, s);
+      }
+      acc += (double)s;
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double s = 0.0;
+    for (int w = 0; w < kThreads / 32; ++w) s += warp_sums[w];
+    partials[blockIdx.x] = s;
+  }
+}
+
+__global__ void sq_norm_final(const double* partials, int n, double* out, int accumulate) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  double s = accumulate ? *out : 0.0;
+  for (int i = 0; i < n; ++i) s += partials[i];
+  *out = s;
+}
+
+}  // namespace fo
+
+using namespace fo;
+
+extern "C" int fo_sq_norm(const FoArray* arrays, uint32_t n_arrays, int32_t dtype, int32_t accumulate, double* out,
+                          void* workspace, void* cuda_stream) {
+  static_assert(kNormMaxBlocks * sizeof(double) <= FO_SQ_NORM_WORKSPACE_BYTES, "workspace too small");
+  if (out == nullptr || workspace == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_sq_norm: null out / workspace");
+  if (dtype < FO_F32 || dtype > FO_F16) return fail(FO_ERR_INVALID_ARG, "fo_sq_norm: bad dtype %d", dtype);
+  if (n_arrays > 0 && arrays == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_sq_norm: null table");
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return fail(FO_ERR_CUDA, "fo_sq_norm: cannot query the current device");
+  double* partials = static_cast<double*>(workspace);
+  NormParams p;
+  memset(&p, 0, sizeof(p));
+  p.dtype = dtype;
+  int count = 0;
+  unsigned long long chunks = 0;
+  bool launched = false;
+  auto flush = [&]() -> int {
+    // an empty list still has to define *out
+    if (count == 0 && launched) return FO_OK;
+    p.n_arrays = count;
+    p.first_chunk[count] = (uint32_t)chunks;
+    unsigned int grid = (unsigned int)(sms * kNormBlocksPerSm);
+    if (grid > kNormMaxBlocks) grid = kNormMaxBlocks;
+    if (grid > chunks) grid = (unsigned int)chunks;
+    if (grid > 0) sq_norm_partial<<<grid, kThreads, 0, stream>>>(p, partials);
+    sq_norm_final<<<1, 32, 0, stream>>>(partials, (int)grid, out, launched ? 1 : accumulate);
+    launched = true;
+    count = 0;
+    chunks = 0;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(FO_ERR_CUDA, "fo_sq_norm: launch failed: %s", cudaGetErrorString(e));
+    return FO_OK;
+  };
+  for (uint32_t i = 0; i < n_arrays; ++i) {
+    if (arrays[i].n == 0) continue;
+    if (arrays[i].data == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_sq_norm: array %u: null data", i);
+    const unsigned long long nc = (arrays[i].n + kChunk - 1) / kChunk;
+    if (nc > 0x7FFFFFFFull) return fail(FO_ERR_TOO_LARGE, "fo_sq_norm: array %u with %llu elements exceeds one launch", i, (unsigned long long)arrays[i].n);
+    if (count == kNormMaxArrays || chunks + nc > 0x7FFFFFFFull) {
+      int rc = flush();
+      if (rc != FO_OK) return rc;
+    }
+    p.data[count] = arrays[i].data;
+    p.n[count] = arrays[i].n;
+    p.first_chunk[count] = (uint32_t)chunks;
+    p.aligned[count] = ((uintptr_t)arrays[i].data & 15u) == 0;
+    chunks += nc;
+    ++count;
+  }
+  return flush();
+}

@@ -109,6 +109,9 @@ struct StepParams {
   float one;  // 1.0f the compiler cannot see through (see fast2::sum2)
   int32_t stages;  // shared-memory stages of the copy pipeline (2..8), set by the launcher
   Peers peers;
+  const double* sq_norm;  // device: sum of squares of all gradients of the step (nullptr: no clipping)
+  float max_norm;
+  int32_t pad;
 };
 
 // true when the quotient sqrt(nu)/sqrt(bc2) may be formed as div_by_rcp without changing
@@ -223,6 +226,35 @@ FO_DEVI float round_to_grad_dtype(float x, int gdt) {
   if (gdt == FO_F16) return __half2float(__float2half_rn(x));
   return x;
 }
+// Global-norm clipping folded into the step (optax.clip_by_global_norm as the reference's GPT-2
+// recipe chains it in front of the optimizer, examples/train_gpt2_pretrain.py:56-70):
+//   norm = sqrt(sum of squares);  keep g if norm < max_norm, else g <- (g / norm.astype(g.dtype)) * max_norm
+// with the division and the product each rounded to the gradient dtype.
+struct Clip {
+  bool active;   // norm >= max_norm (or NaN): gradients are rescaled
+  bool div_ok;   // the reciprocal shortcut is exact for this divisor
+  float n_g;     // norm rounded to the gradient dtype
+  float rcp_n;   // RN(1 / n_g)
+  float m_g;     // max_norm rounded to the gradient dtype
+};
+FO_DEVI Clip load_clip(const double* sq_norm, float max_norm, int gdt) {
+  Clip c;
+  c.active = false; c.div_ok = true; c.n_g = 1.0f; c.rcp_n = 1.0f; c.m_g = 1.0f;
+  if (sq_norm == nullptr) return c;
+  const float norm = (float)sqrt(*sq_norm);
+  c.active = !(norm < max_norm);
+  c.n_g = round_to_grad_dtype(norm, gdt);
+  c.m_g = round_to_grad_dtype(max_norm, gdt);
+  c.rcp_n = __frcp_rn(c.n_g);
+  // Markstein's correction needs a correctly rounded reciprocal of a divisor whose mantissa is not all ones
+  c.div_ok = (__float_as_uint(c.n_g) & 0x7FFFFFu) != 0x7FFFFFu && c.n_g >= 9.5367432e-7f && c.n_g <= 1048576.0f;  // [2^-20, 2^20]
+  return c;
+}
+FO_DEVI float clip_ieee(float g, const Clip& c, int gdt) {
+  if (!c.active) return g;
+  return round_to_grad_dtype(fmul(round_to_grad_dtype(fdiv(g, c.n_g), gdt), c.m_g), gdt);
+}
+
 // the gradient of element i: the local value, or the mean over the ranks (see Peers)
 FO_DEVI float load_grad_mean(const void* grad, int gdt, unsigned long long i, const Peers& peers) {
   float g = load_grad(grad, gdt, i);
@@ -235,7 +267,7 @@ FO_DEVI float load_grad_mean(const void* grad, int gdt, unsigned long long i, co
 // out-of-range elements count as zeros (flashoptim_jax/quantization.py:20-26).
 template <int OPT, int PDT, int ECC_BITS, int STATE>
 __device__ __noinline__ void cold_chunk(const DevLeaf& L, const Hyp& h, int gdt, unsigned long long base,
-                                        const float* lut_m, const float* lut_v, const Peers& peers) {
+                                        const float* lut_m, const float* lut_v, const Peers& peers, const Clip& clip) {
   const unsigned long long n = L.n;
   const unsigned long long i0 = base + (unsigned long long)threadIdx.x * kPiece;
   const unsigned long long gi = i0 >> 5;
@@ -253,7 +285,7 @@ __device__ __noinline__ void cold_chunk(const DevLeaf& L, const Hyp& h, int gdt,
     const unsigned long long i = i0 + j;
     m[j] = 0.0f; root[j] = 0.0f;
     if (i < n) {
-      const float g = load_grad_mean(L.grad, gdt, i, peers);
+      const float g = clip_ieee(load_grad_mean(L.grad, gdt, i, peers), clip, gdt);
       float theta, old_f32 = 0.0f;
       uint32_t pb = 0;
       if constexpr (PDT == FO_F32) {
@@ -709,11 +741,59 @@ FO_DEVI bool merge_peer_grads(float2 (&g)[4], const int gdt, const Peers& peers,
   return rare;
 }
 
+// Global-norm clipping of a piece (see Clip), for gradients already known to be rescaled.
+// Same contract for REPAIR as hot_unpack.
+template <bool REPAIR>
+FO_DEVI bool clip_grads(float2 (&g)[4], const int gdt, const Clip& c) {
+  using namespace fast2;
+  // The reciprocal shortcut is exact for 2^-100 <= |g| <= 2^100, and for zeros up to their sign,
+  // which is put back below.  Magnitude bits minus one, as unsigned: zero wraps to the top and passes.
+  uint32_t lo = 0xFFFFFFFFu, hi = 0u;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const uint32_t a = (__float_as_uint(g[k].x) & 0x7FFFFFFFu) - 1u, b = (__float_as_uint(g[k].y) & 0x7FFFFFFFu) - 1u;
+    lo = min(lo, min(a, b));
+    hi = max(hi, max(a + 1u, b + 1u));
+  }
+  const bool rare = !c.div_ok || lo < 0x0D800000u - 1u || hi > 0x71800000u;  // 2^-100, 2^100
+  float2 q[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    q[k] = div_by_rcp2(g[k], sp(-c.n_g), sp(c.rcp_n));
+    q[k] = mk(copysignf(q[k].x, g[k].x), copysignf(q[k].y, g[k].y));
+  }
+  if constexpr (REPAIR) {
+    if (rare) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) q[k] = mk(fdiv(g[k].x, c.n_g), fdiv(g[k].y, c.n_g));
+    }
+  }
+  if (gdt == FO_BF16) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      unpack2<FO_BF16>(pack2<FO_BF16>(q[k].x, q[k].y), q[k].x, q[k].y);
+      q[k] = mul2(q[k], sp(c.m_g));
+      unpack2<FO_BF16>(pack2<FO_BF16>(q[k].x, q[k].y), g[k].x, g[k].y);
+    }
+  } else if (gdt == FO_F16) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      unpack2<FO_F16>(pack2<FO_F16>(q[k].x, q[k].y), q[k].x, q[k].y);
+      q[k] = mul2(q[k], sp(c.m_g));
+      unpack2<FO_F16>(pack2<FO_F16>(q[k].x, q[k].y), g[k].x, g[k].y);
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) g[k] = mul2(q[k], sp(c.m_g));
+  }
+  return rare;
+}
+
 FO_DEVI float sign_of(float x);
 
 template <int OPT, int PDT, int ECC_BITS, int STATE>
 __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base,
-                                        const float one, const float* lut_mw, const Peers& peers);
+                                        const float one, const float* lut_mw, const Peers& peers, const Clip& clip);
 
 // Second half of a hot chunk: update, split, requantize, store.  Each stage runs its packed
 // shortcut unconditionally.
@@ -725,7 +805,7 @@ __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const in
 // The stored bits are those of the IEEE path in every case.
 template <bool REPAIR, int OPT, int PDT, int ECC_BITS, int STATE>
 FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base, const float one,
-                        bool rare, Unpacked& u, const float* lut_mw, const Peers& peers) {
+                        bool rare, Unpacked& u, const float* lut_mw, const Peers& peers, const Clip& clip) {
   using namespace fast2;
   const float2 one2 = sp(one);
   float2 (&g)[4] = u.g;
@@ -927,7 +1007,7 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
   // ---- first pass: one decision per warp -----------------------------------------------------------------
   if constexpr (!REPAIR) {
     if (__any_sync(0xFFFFFFFFu, rare)) {
-      warm_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, one, lut_mw, peers);
+      warm_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, one, lut_mw, peers, clip);
       return;
     }
   } else {
@@ -971,7 +1051,7 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
 // first pass for that warp, against about seven times for the scalar IEEE path.
 template <int OPT, int PDT, int ECC_BITS, int STATE>
 __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base,
-                                        const float one, const float* lut_mw, const Peers& peers) {
+                                        const float one, const float* lut_mw, const Peers& peers, const Clip& clip) {
   Raw<OPT, PDT, ECC_BITS, STATE> raw;
   hot_load<OPT, PDT, ECC_BITS, STATE>(L, gdt, base + threadIdx.x * kPiece, raw);
   Unpacked u;
@@ -988,7 +1068,8 @@ __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const in
       }
     });
   }
-  hot_finish<true, OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, one, false, u, lut_mw, peers);
+  if (clip.active) clip_grads<true>(u.g, gdt, clip);
+  hot_finish<true, OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, one, false, u, lut_mw, peers, clip);
 }
 
 // exact dequantization tables, one entry per code byte (built once per block)
@@ -1039,6 +1120,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
   const uint32_t stage_end = stage0 + (uint32_t)p.stages * stage_bytes;
   const uint32_t toff = threadIdx.x * kPiece;
   const uint32_t grid = gridDim.x;
+  const Clip clip = load_clip(p.sq_norm, p.max_norm, p.grad_dtype);
   uint32_t c = blockIdx.x;  // this block's next position in the sequence
   for (int l = 0; l < p.n_leaves; ++l) {
     const uint32_t first = p.first_block[l], next = p.first_block[l + 1];
@@ -1107,11 +1189,15 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
           });
           rare = rare || odd;
         }
-        hot_finish<false, OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, base, p.one, rare, u, lut_mw, p.peers);
+        if (clip.active) {
+          const bool odd = clip_grads<false>(u.g, p.grad_dtype, clip);
+          rare = rare || odd;
+        }
+        hot_finish<false, OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, base, p.one, rare, u, lut_mw, p.peers, clip);
       }
     }
     for (; ch < end; ch += grid)
-      cold_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, (unsigned long long)ch * kChunk, lut_m, lut_v, p.peers);
+      cold_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, (unsigned long long)ch * kChunk, lut_m, lut_v, p.peers, clip);
     c = first + ch;
   }
 }
@@ -1123,6 +1209,7 @@ __global__ void __launch_bounds__(256) step_kernel_generic(const __grid_constant
   __shared__ float lut_m[256], lut_v[256];
   __shared__ unsigned int smax_m[kGenericTile], smax_v[kGenericTile];
   build_luts(lut_m, lut_v);
+  const Clip clip = load_clip(p.sq_norm, p.max_norm, p.grad_dtype);
   int lo = 0, hi = p.n_leaves;
   while (hi - lo > 1) {
     int mid = (lo + hi) >> 1;
@@ -1147,7 +1234,7 @@ __global__ void __launch_bounds__(256) step_kernel_generic(const __grid_constant
     m[k] = 0.0f; root[k] = 0.0f;
     if (li < tile && i < n) {
       const unsigned long long gi = i / G;
-      const float g = load_grad(L.grad, p.grad_dtype, i);
+      const float g = clip_ieee(load_grad(L.grad, p.grad_dtype, i), clip, p.grad_dtype);
       float theta, old_f32 = 0.0f;
       uint32_t pb = 0;
       if constexpr (PDT == FO_F32) {

@@ -24,6 +24,8 @@ between backward and the collectives.
 
 from __future__ import annotations
 
+import contextlib
+
 from typing import Any, Callable, Dict, List, NamedTuple, Optional, Tuple
 
 import torch
@@ -165,11 +167,17 @@ class Zero1Optimizer:
                 averages them (fp32 sum in rank order starting with its own, one rounding to the
                 gradient dtype) as it goes; a one-element all-reduce before the launch makes sure that
                 every rank's gradients are complete.  Same restrictions.
+    max_grad_norm
+                clip the (averaged) gradients at this global norm, as optax.clip_by_global_norm in front
+                of the optimizer does (examples/train_gpt2_pretrain.py:56-70): every rank sums the squares
+                of its reduce-scattered slice on the device, the sums are all-reduced, and the step kernel
+                rescales the gradients as it loads them.  Needs the reduce-scattered gradients in memory,
+                so not together with fused_reduce_scatter.
     """
 
     def __init__(self, optimizer: str, params: Any, *, group=None, step_fn: Optional[StepFn] = None,
                  n_slices: Optional[int] = None, fused_allgather: bool = False, fused_reduce_scatter: bool = False,
-                 **hparams):
+                 max_grad_norm: Optional[float] = None, **hparams):
         self.kind = optimizer
         if optimizer not in ("adamw", "adam", "lion", "sgd", "sgdw"):
             raise ValueError(f"unknown optimizer {optimizer!r}")
@@ -215,6 +223,13 @@ class Zero1Optimizer:
             if n_slices not in (None, 1):
                 raise ValueError("fused collectives work on whole buckets: n_slices must be 1")
             n_slices = 1
+        self.max_grad_norm = None if max_grad_norm is None else float(max_grad_norm)
+        if self.max_grad_norm is not None:
+            if self.fused_reduce_scatter:
+                raise ValueError("max_grad_norm needs the reduce-scattered gradients: fused_reduce_scatter must be off")
+            if device.type != "cuda":
+                raise ValueError("max_grad_norm needs CUDA tensors")
+            n_slices = 1  # the norm is known only after the last reduce-scatter: nothing to pipeline
         self.peer_offsets: List[List[int]] = []
         self.peer_grad_offsets: List[List[int]] = []
         self.buckets: List[BucketLayout] = []
@@ -434,6 +449,20 @@ class Zero1Optimizer:
             dist.all_reduce(self._token, group=self.group)  # every rank's gradients are complete before any kernel reads them
         else:
             self.reduce_scatter_grads()
+        with self._clip_context():
+            return self._launch_and_gather()
+
+    def _clip_context(self):
+        """Global-norm clipping for the launches of this step: the squares of this rank's slices (padding is
+        zero), summed over the ranks."""
+        if self.max_grad_norm is None:
+            return contextlib.nullcontext()
+        sq = eng.sq_norm_of(list(self.grad_shards))
+        if self.world_size > 1:
+            dist.all_reduce(sq, group=self.group)
+        return eng.grad_clip(sq, self.max_grad_norm)
+
+    def _launch_and_gather(self) -> Any:
         if self.fused_allgather or self.fused_reduce_scatter:
             work = self.local_work()
             for b in range(len(self.buckets)):

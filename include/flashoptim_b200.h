@@ -138,12 +138,36 @@ typedef struct FoStepDesc {
    * ranks' kernels have completed.  NULL: the local gradient is used as it is.
    * With n_peers > 0 at least one of the two offset tables must be given; group size 32 only. */
   const int64_t* peer_grad_offsets;
+  /* Global-norm gradient clipping folded into the step (optax.clip_by_global_norm chained in front
+   * of the optimizer by the reference's GPT-2 recipe, examples/train_gpt2_pretrain.py:56-70):
+   * grad_sq_norm points to a device double holding the sum of squares of ALL gradients of the
+   * step (fo_sq_norm writes it; with sharded gradients the caller adds the ranks' sums first).
+   * With norm = (float)sqrt(*grad_sq_norm): gradients are used as they are if norm < max_grad_norm,
+   * else each is replaced by RN_g(RN_g(g / RN_g(norm)) * RN_g(max_grad_norm)), RN_g = rounding to
+   * grad_dtype.  Applied after the averaging over peers.  NULL: no clipping. */
+  const double* grad_sq_norm;
+  float max_grad_norm;
+  uint32_t reserved2;
 } FoStepDesc;
 #define FO_MAX_PEERS 7
 
 /* Replaces pl.pallas_call(...) of _fused_flash_adamw_leaf_impl (adamw.py:225-353) and of
  * fused_momentum_leaf_impl (momentum_kernel.py:183-302), for a whole pytree at once. */
 int fo_step(const FoStepDesc* desc, void* cuda_stream);
+
+/* Sum of squares of a list of device arrays of one dtype (the gradient pytree, or one dtype
+ * bucket of it), for global-norm clipping (optax.global_norm as used through
+ * examples/train_gpt2_pretrain.py:58): squares exact in fp32, summed in fp32 over short runs and
+ * in fp64 beyond, in an order that depends only on the array sizes (same inputs, same bits).
+ * *out (device) receives the sum, or has it added when accumulate != 0 (further buckets).
+ * workspace: FO_SQ_NORM_WORKSPACE_BYTES bytes of device memory the calls of one stream may share. */
+typedef struct FoArray {
+  const void* data;
+  uint64_t n;
+} FoArray;
+#define FO_SQ_NORM_WORKSPACE_BYTES 16384
+int fo_sq_norm(const FoArray* arrays, uint32_t n_arrays, int32_t dtype, int32_t accumulate, double* out,
+               void* workspace, void* cuda_stream);
 
 /* Codecs on fp32 arrays; n elements, scales has ceil(n/group_size) fp16 entries.
  * scale_floor selects the guard of FO_FLAG_SCALE_FLOOR.

@@ -34,7 +34,7 @@ guard applied to an all-zero group scale and in how AdamW hands back the param.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import NamedTuple, Optional, Tuple, Union
+from typing import List, NamedTuple, Optional, Sequence, Tuple, Union
 
 import ml_dtypes
 import numpy as np
@@ -467,3 +467,39 @@ def init_momentum_leaf(
     if use_ecc_leaf(param, master_weight_bits):
         ecc = np.zeros(param.shape, dtype=np.int8 if master_weight_bits == 24 else np.int16)
     return mu, ecc
+
+
+# ---- global-norm gradient clipping in front of the step ------------------------------------------
+#
+# The reference's GPT-2 recipe chains optax.clip_by_global_norm before tx.step
+# (examples/train_gpt2_pretrain.py:56-70).  optax is a third-party dependency of the examples
+# (unpinned, not vendored); its published algorithm is
+#     g_norm  = sqrt(sum over leaves of sum(|g|^2))
+#     trigger = g_norm < max_norm
+#     g      <- g if trigger else (g / g_norm.astype(g.dtype)) * max_norm
+# with every operation carried out in the leaf's dtype (XLA evaluates bf16 / fp16 element-wise
+# operations in fp32 and rounds the result).  The order in which XLA sums the squares is not
+# specified, so the norm itself is "parity unpinned": this restatement takes squares exactly,
+# sums them in float64 and rounds the square root to fp32; the element-wise part is exact given
+# the norm.
+
+
+def global_sq_norm(grads: Sequence[np.ndarray]) -> float:
+    return float(sum(np.sum(np.asarray(g, dtype=np.float64) ** 2) for g in grads))
+
+
+def clip_by_global_norm(grads: Sequence[np.ndarray], max_norm: float, sq_norm: Optional[float] = None) -> List[np.ndarray]:
+    """Clipped copies of `grads`.  `sq_norm` overrides the sum of squares (to feed the value a device computed)."""
+    if sq_norm is None:
+        sq_norm = global_sq_norm(grads)
+    norm = np.float32(np.sqrt(np.float64(sq_norm)))
+    if norm < np.float32(max_norm):
+        return [np.array(g, copy=True) for g in grads]
+    out = []
+    for g in grads:
+        dt = g.dtype
+        n_g = np.float32(norm.astype(dt))
+        m_g = np.float32(np.float32(max_norm).astype(dt))
+        q = (g.astype(np.float32) / n_g).astype(np.float32).astype(dt)
+        out.append((q.astype(np.float32) * m_g).astype(np.float32).astype(dt))
+    return out

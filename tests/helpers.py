@@ -106,7 +106,7 @@ def oracle_step(opt: int, grad: np.ndarray, leaf: LeafArrays, state: int, group_
 
 def abi_step(opt: int, grads: List, leaves: List[LeafArrays], state: int, group_size: int, hypers: List, hyper_of: List[int],
              param_dtype: int, grad_dtype: int, ecc_bits: int, stream: int = 0, expect_ok: bool = True,
-             peer_param_offsets=None, peer_grad_offsets=None) -> int:
+             peer_param_offsets=None, peer_grad_offsets=None, grad_sq_norm=None, max_grad_norm: float = 0.0) -> int:
     """One fo_step call through the C ABI on torch device tensors (in place)."""
     from flashoptim_jax_b200 import _lib
 
@@ -128,6 +128,8 @@ def abi_step(opt: int, grads: List, leaves: List[LeafArrays], state: int, group_
     d = _lib.FoStepDesc(struct_size=ctypes.sizeof(_lib.FoStepDesc), opt=opt, param_dtype=param_dtype, grad_dtype=grad_dtype,
                         ecc_bits=ecc_bits, state=state, group_size=group_size, n_leaves=len(leaves), n_hypers=len(hypers),
                         leaves=ctypes.cast(L, ctypes.c_void_p), hypers=ctypes.cast(H, ctypes.c_void_p))
+    if grad_sq_norm is not None:
+        d.grad_sq_norm, d.max_grad_norm = grad_sq_norm.data_ptr(), float(max_grad_norm)
     keep = []
     for name, offs in (("peer_param_offsets", peer_param_offsets), ("peer_grad_offsets", peer_grad_offsets)):
         if offs is not None:

@@ -144,3 +144,28 @@ def test_two_ranks_with_their_own_gradients_step_on_the_mean(tmp_path, mode):
         assert torch.equal(a, b)
     for a, b in zip(got["state"], want_s):
         assert a.dtype == b.dtype and torch.equal(a, b)
+
+
+def test_one_rank_with_max_grad_norm_equals_the_clipping_wrapper():
+    import torch
+
+    import flashoptim_jax_b200 as fo
+    from flashoptim_jax_b200 import tree
+    from flashoptim_jax_b200.clipping import clip_by_global_norm
+    from flashoptim_jax_b200.zero1 import Zero1Optimizer
+
+    dev = torch.device("cuda", 0)
+    z = Zero1Optimizer("adamw", _params(dev), max_grad_norm=0.05, **HP)
+    tx = clip_by_global_norm(fo.flash_adamw(donate=True, **HP), 0.05)
+    params = _params(dev)
+    state = tx.init(params)
+    for t in range(3):
+        z.step(_grads(t, dev))
+        params, state = tx.step(params, state, _grads(t, dev))
+    torch.cuda.synchronize()
+    for a, b in zip(tree.tree_leaves(z.params), tree.tree_leaves(params)):
+        assert torch.equal(a, b)
+    plain = Zero1Optimizer("adamw", _params(dev), **HP)
+    for t in range(3):
+        plain.step(_grads(t, dev))
+    assert any(not torch.equal(a, b) for a, b in zip(tree.tree_leaves(z.params), tree.tree_leaves(plain.params)))  # the clip did bite

@@ -218,3 +218,24 @@ def test_ecc_bounds_and_error_shrinks_for_random_fp32():
         fixed = np.abs(xs - rec).astype(np.float64)
         normal = np.abs(xs) > (1e-30 if dt is BF16 else 1e-3)
         assert fixed[normal].sum() * gain * 0.5 < plain[normal].sum() + 1e-300
+
+
+def test_clip_by_global_norm_known_answers():
+    # a 3-4-5 triangle: norm 5, clipped to 1 -> 0.6, 0.8 (fp32 division then product, each rounded once)
+    g = [np.array([3.0], dtype=np.float32), np.array([4.0], dtype=np.float32)]
+    assert O.global_sq_norm(g) == 25.0
+    out = O.clip_by_global_norm(g, 1.0)
+    assert out[0][0] == np.float32(3.0) / np.float32(5.0) and out[1][0] == np.float32(4.0) / np.float32(5.0)
+    # below the threshold nothing changes (norm < max_norm, strict)
+    same = O.clip_by_global_norm(g, 5.5)
+    assert same[0][0] == 3.0 and same[1][0] == 4.0
+    at = O.clip_by_global_norm(g, 5.0)  # norm == max_norm rescales: (g / 5) * 5
+    assert at[0][0] == (np.float32(3.0) / np.float32(5.0)) * np.float32(5.0)
+    # 16-bit leaves: norm and max_norm are cast to the leaf dtype, quotient and product are rounded to it
+    import ml_dtypes
+
+    b = [np.array([3.0, -4.0, 0.0], dtype=ml_dtypes.bfloat16)]
+    out = O.clip_by_global_norm(b, 0.3)
+    m = np.float32(np.float32(0.3).astype(ml_dtypes.bfloat16))
+    want = [(np.float32(np.float32(x / 5.0).astype(ml_dtypes.bfloat16)) * m).astype(ml_dtypes.bfloat16) for x in (3.0, -4.0, 0.0)]
+    assert [float(v) for v in out[0]] == [float(w) for w in want] and out[0].dtype == ml_dtypes.bfloat16
