@@ -136,6 +136,31 @@ def sq_norm_of(tensors: List[torch.Tensor], out: Optional[torch.Tensor] = None, 
     return out
 
 
+# ---- per-step scalars on the device (graph-capturable steps) ---------------------------------------
+
+
+def step_scalars(count: torch.Tensor, learning_rate: Any, b1: float, b2: float, write_count: bool) -> torch.Tensor:
+    """float32[3] = {lr, 1 - b1^(count+1), 1 - b2^(count+1)} formed on the device from the device counter
+    (adamw.py:510, 526-528); `learning_rate` is a number or a 0-d float32 CUDA tensor.  With `write_count`
+    the counter is advanced in place.  The result is what FoHyper.dev_scalars points to."""
+    if not (count.is_cuda and count.dtype == torch.int32 and count.numel() == 1):
+        raise ValueError("a capturable step keeps `count` as a 0-d int32 CUDA tensor")
+    lr_ptr, lr_const = 0, 0.0
+    if isinstance(learning_rate, torch.Tensor):
+        if not (learning_rate.is_cuda and learning_rate.dtype == torch.float32 and learning_rate.numel() == 1):
+            raise ValueError("a tensor learning rate must be a 0-d float32 CUDA tensor")
+        lr_ptr = learning_rate.data_ptr()
+    elif callable(learning_rate):
+        raise ValueError("a capturable step cannot call a schedule on the host: pass a CUDA tensor and update it yourself")
+    else:
+        lr_const = float(learning_rate)
+    out = torch.empty(3, dtype=torch.float32, device=count.device)
+    with torch.cuda.device(count.device):
+        _lib.check(_lib.lib().fo_step_scalars(count.data_ptr(), lr_ptr, lr_const, float(b1), float(b2), out.data_ptr(),
+                                              count.data_ptr() if write_count else 0, stream_ptr(count.device)))
+    return out
+
+
 def launch(opt: int, work: List[LeafWork], peer_param_offsets: Optional[List[int]] = None,
            peer_grad_offsets: Optional[List[int]] = None) -> int:
     """Issue one fo_step per bucket (per <=16 hyper sets); returns the number of calls.
@@ -176,7 +201,7 @@ def launch(opt: int, work: List[LeafWork], peer_param_offsets: Optional[List[int
             leaves["hyper"] = [h for _, h in pending]
             hypers = np.zeros(len(hyper_index), dtype=HYPER_DTYPE)
             for hp, idx in hyper_index.items():
-                hypers[idx] = hp + (0,)
+                hypers[idx] = hp if len(hp) == len(HYPER_DTYPE.names) else hp + (0,)
             desc = _lib.FoStepDesc(
                 struct_size=ctypes.sizeof(_lib.FoStepDesc), opt=opt, param_dtype=pdt, grad_dtype=gdt, ecc_bits=ecc_bits,
                 state=state, group_size=group_size, n_leaves=len(pending), n_hypers=len(hyper_index),

@@ -45,7 +45,7 @@ def adam_hyper(config: Dict[str, Any], lr: float, count: int, decoupled_weight_d
 
 
 def _make_adam_transform(learning_rate, b1, b2, eps, weight_decay, quantize, master_weight_bits, group_size, fused,
-                         decoupled_weight_decay, param_groups, name, donate) -> utils.FlashOptimizer:
+                         decoupled_weight_decay, param_groups, name, donate, capturable=False) -> utils.FlashOptimizer:
     utils._validate_master_weight_bits(master_weight_bits)
     utils._validate_fused_group_size(group_size, quantize=quantize, fused=fused)
     defaults = {
@@ -62,6 +62,35 @@ def _make_adam_transform(learning_rate, b1, b2, eps, weight_decay, quantize, mas
             eccs.append(eng.init_ecc(leaf, config["master_weight_bits"]))
         return FlashAdamState(count=torch.zeros((), dtype=torch.int32), mu=treedef.unflatten(mus),
                               nu=treedef.unflatten(nus), ecc=treedef.unflatten(eccs))
+
+    def capturable_step_fn(params: Any, state: FlashAdamState, grads: Any):
+        """The same step with no host scalar in it: the counter stays on the device, and the learning rate
+        (a number or a 0-d CUDA tensor the caller updates), count + 1 and the bias corrections (adamw.py:510,
+        526-528) are formed there by fo_step_scalars, so the call can be captured in a CUDA graph and replayed."""
+        param_pl, grad_leaves, (ecc_leaves, mu_leaves, nu_leaves), treedef = eng.flatten_step_inputs(
+            name, params, grads, [state.ecc, state.mu, state.nu])
+        leaves = [as_tensor(leaf) for _, leaf in param_pl]
+        count = as_tensor(state.count, dtype=torch.int32)
+        if not count.is_cuda:
+            count = count.to(leaves[0].device)  # first step after an init on the host
+        configs = [utils._group_config_for_path(path, leaf, defaults, param_groups) for (path, _), leaf in zip(param_pl, leaves)]
+        keys = [tuple(sorted(((k, id(v) if isinstance(v, torch.Tensor) else v) for k, v in c.items()), key=lambda kv: kv[0]))
+                for c in configs]
+        distinct = list(dict.fromkeys(keys))
+        scalars = {}
+        for i, key in enumerate(distinct):
+            c = configs[keys.index(key)]
+            scalars[key] = eng.step_scalars(count, c["learning_rate"], c["b1"], c["b2"], write_count=i == len(distinct) - 1)
+        work: List[eng.LeafWork] = []
+        new_p, new_e, new_m, new_v = [], [], [], []
+        for leaf, key, config, g, e, m, v in zip(leaves, keys, configs, grad_leaves, ecc_leaves, mu_leaves, nu_leaves):
+            hyper = adam_hyper(config, 0.0, 1, decoupled_weight_decay) + (scalars[key].data_ptr(),)  # lr, bc1, bc2 come from the device
+            w, p_out, e_out, m_out, v_out = eng.make_work(leaf, g, e, m, v, config, hyper, donate, has_nu=True)
+            work.append(w)
+            new_p.append(p_out); new_e.append(e_out); new_m.append(m_out); new_v.append(v_out)
+        eng.launch(_lib.FO_OPT_ADAM, work)
+        new_state = FlashAdamState(count=count, mu=treedef.unflatten(new_m), nu=treedef.unflatten(new_v), ecc=treedef.unflatten(new_e))
+        return treedef.unflatten(new_p), new_state
 
     def step_fn(params: Any, state: FlashAdamState, grads: Any):
         old_count = as_tensor(state.count, dtype=torch.int32).cpu()
@@ -83,23 +112,25 @@ def _make_adam_transform(learning_rate, b1, b2, eps, weight_decay, quantize, mas
                                    nu=treedef.unflatten(new_v), ecc=treedef.unflatten(new_e))
         return treedef.unflatten(new_p), new_state
 
-    return utils.FlashOptimizer(init=init_fn, step=step_fn)
+    return utils.FlashOptimizer(init=init_fn, step=capturable_step_fn if capturable else step_fn)
 
 
 def flash_adam(learning_rate=1e-3, b1: float = 0.9, b2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.0,
                quantize: bool = True, master_weight_bits: Optional[int] = 24, group_size: int = 32, fused: bool = True,
-               param_groups: Optional[List[Dict[str, Any]]] = None, donate: bool = False) -> utils.FlashOptimizer:
+               param_groups: Optional[List[Dict[str, Any]]] = None, donate: bool = False,
+               capturable: bool = False) -> utils.FlashOptimizer:
     """Adam with weight decay added to the gradient (flashoptim_jax/adamw.py:595-613)."""
     return _make_adam_transform(learning_rate, b1, b2, eps, weight_decay, quantize, master_weight_bits, group_size, fused,
-                                False, param_groups, "flash_adam", donate)
+                                False, param_groups, "flash_adam", donate, capturable)
 
 
 def flash_adamw(learning_rate=1e-3, b1: float = 0.9, b2: float = 0.999, eps: float = 1e-8, weight_decay: float = 1e-2,
                 quantize: bool = True, master_weight_bits: Optional[int] = 24, group_size: int = 32, fused: bool = True,
-                param_groups: Optional[List[Dict[str, Any]]] = None, donate: bool = False) -> utils.FlashOptimizer:
+                param_groups: Optional[List[Dict[str, Any]]] = None, donate: bool = False,
+                capturable: bool = False) -> utils.FlashOptimizer:
     """AdamW, decoupled weight decay (flashoptim_jax/adamw.py:616-634)."""
     return _make_adam_transform(learning_rate, b1, b2, eps, weight_decay, quantize, master_weight_bits, group_size, fused,
-                                True, param_groups, "flash_adamw", donate)
+                                True, param_groups, "flash_adamw", donate, capturable)
 
 
 def flash_adamw_state_dict(state: FlashAdamState) -> Dict[str, Any]:

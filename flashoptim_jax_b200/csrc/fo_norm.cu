@@ -74,6 +74,16 @@ __global__ void sq_norm_final(const double* partials, int n, double* out, int ac
   *out = s;
 }
 
+__global__ void step_scalars_kernel(const int32_t* count, const float* lr_dev, float lr_const, float b1, float b2, float* out3,
+                                    int32_t* count_out) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const int32_t c = *count + 1;
+  out3[0] = lr_dev != nullptr ? *lr_dev : lr_const;
+  out3[1] = fsub(1.0f, (float)pow((double)b1, (double)c));
+  out3[2] = fsub(1.0f, (float)pow((double)b2, (double)c));
+  if (count_out != nullptr) *count_out = c;
+}
+
 }  // namespace fo
 
 using namespace fo;
@@ -129,4 +139,13 @@ extern "C" int fo_sq_norm(const FoArray* arrays, uint32_t n_arrays, int32_t dtyp
     ++count;
   }
   return flush();
+}
+
+extern "C" int fo_step_scalars(const int32_t* count, const float* lr_dev, float lr_const, float b1, float b2, float* out3,
+                               int32_t* count_out, void* cuda_stream) {
+  if (count == nullptr || out3 == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_step_scalars: null count / out3");
+  step_scalars_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(count, lr_dev, lr_const, b1, b2, out3, count_out);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(FO_ERR_CUDA, "fo_step_scalars: launch failed: %s", cudaGetErrorString(e));
+  return FO_OK;
 }

@@ -155,6 +155,15 @@ typedef struct FoStepDesc {
  * fused_momentum_leaf_impl (momentum_kernel.py:183-302), for a whole pytree at once. */
 int fo_step(const FoStepDesc* desc, void* cuda_stream);
 
+/* Per-step scalars formed on the device, so that a whole step can be captured in a CUDA graph
+ * with no host scalar in it (the reference forms them as traced values inside its jitted step:
+ * count + 1 at adamw.py:510, learning rate at adamw.py:526, bias corrections at adamw.py:527-528).
+ *   c = *count + 1;  out3 = { lr, 1 - b1^c, 1 - b2^c }   (the power in float64, rounded once to fp32)
+ * lr = *lr_dev when lr_dev is not NULL, else lr_const.  count_out (may equal count, may be NULL)
+ * receives c.  out3 is what FoHyper.dev_scalars points to. */
+int fo_step_scalars(const int32_t* count, const float* lr_dev, float lr_const, float b1, float b2, float* out3,
+                    int32_t* count_out, void* cuda_stream);
+
 /* Sum of squares of a list of device arrays of one dtype (the gradient pytree, or one dtype
  * bucket of it), for global-norm clipping (optax.global_norm as used through
  * examples/train_gpt2_pretrain.py:58): squares exact in fp32, summed in fp32 over short runs and
