@@ -8,7 +8,7 @@ namespace fo {
 int fail(int code, const char* fmt, ...);
 
 constexpr int kNormMaxArrays = 160;   // per launch (kernel-parameter table)
-constexpr int kNormBlocksPerSm = 4;
+constexpr int kNormBlocksPerSm = 8;
 constexpr int kNormMaxBlocks = 2048;  // doubles in the workspace
 
 struct NormParams {
@@ -29,6 +29,11 @@ FO_DEVI float sq_run(const uint4& w0, const uint4& w1, int dt) {
   return s;
 }
 
+// one chunk of this kernel: kNormPieces pieces of kPiece elements per thread, kChunk apart, so that
+// every thread has that many independent 128-bit loads in flight
+constexpr int kNormPieces = 4;
+constexpr unsigned long long kNormChunk = (unsigned long long)kChunk * kNormPieces;
+
 __global__ void __launch_bounds__(kThreads) sq_norm_partial(const __grid_constant__ NormParams p, double* partials) {
   __shared__ double warp_sums[kThreads / 32];
   double acc = 0.0;
@@ -36,25 +41,33 @@ __global__ void __launch_bounds__(kThreads) sq_norm_partial(const __grid_constan
   int a = 0;
   for (uint32_t c = blockIdx.x; c < total; c += gridDim.x) {
     while (c >= p.first_chunk[a + 1]) ++a;
-    const unsigned long long i0 = (unsigned long long)(c - p.first_chunk[a]) * kChunk + (unsigned long long)threadIdx.x * kPiece;
+    const unsigned long long base = (unsigned long long)(c - p.first_chunk[a]) * kNormChunk + (unsigned long long)threadIdx.x * kPiece;
     const unsigned long long n = p.n[a];
-    if (i0 >= n) continue;
-    if (p.aligned[a] && i0 + kPiece <= n) {
-      uint4 w0, w1 = make_uint4(0u, 0u, 0u, 0u);
-      if (p.dtype == FO_F32) {
-        w0 = __ldcs((const uint4*)((const float*)p.data[a] + i0));
-        w1 = __ldcs((const uint4*)((const float*)p.data[a] + i0) + 1);
-      } else {
-        w0 = __ldcs((const uint4*)((const unsigned short*)p.data[a] + i0));
+    if (p.aligned[a] && base + (kNormPieces - 1) * (unsigned long long)kChunk + kPiece <= n) {
+      uint4 w0[kNormPieces], w1[kNormPieces];
+#pragma unroll
+      for (int k = 0; k < kNormPieces; ++k) {
+        const unsigned long long i0 = base + (unsigned long long)k * kChunk;
+        w1[k] = make_uint4(0u, 0u, 0u, 0u);
+        if (p.dtype == FO_F32) {
+          w0[k] = __ldcs((const uint4*)((const float*)p.data[a] + i0));
+          w1[k] = __ldcs((const uint4*)((const float*)p.data[a] + i0) + 1);
+        } else {
+          w0[k] = __ldcs((const uint4*)((const unsigned short*)p.data[a] + i0));
+        }
       }
-      acc += (double)sq_run(w0, w1, p.dtype);
+#pragma unroll
+      for (int k = 0; k < kNormPieces; ++k) acc += (double)sq_run(w0[k], w1[k], p.dtype);
     } else {
-      float s = 0.0f;
-      for (int j = 0; j < kPiece && i0 + j < n; ++j) {
-        const float g = load_grad(p.data[a], p.dtype, i0 + j);
-        s = __fmaf_rn(g, g, s);
+      for (int k = 0; k < kNormPieces; ++k) {
+        const unsigned long long i0 = base + (unsigned long long)k * kChunk;
+        float s = 0.0f;
+        for (int j = 0; j < kPiece && i0 + j < n; ++j) {
+          const float g = load_grad(p.data[a], p.dtype, i0 + j);
+          s = __fmaf_rn(g, g, s);
+        }
+        acc += (double)s;
       }
-      acc += (double)s;
     }
   }
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
@@ -125,7 +138,7 @@ extern "C" int fo_sq_norm(const FoArray* arrays, uint32_t n_arrays, int32_t dtyp
   for (uint32_t i = 0; i < n_arrays; ++i) {
     if (arrays[i].n == 0) continue;
     if (arrays[i].data == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_sq_norm: array %u: null data", i);
-    const unsigned long long nc = (arrays[i].n + kChunk - 1) / kChunk;
+    const unsigned long long nc = (arrays[i].n + kNormChunk - 1) / kNormChunk;
     if (nc > 0x7FFFFFFFull) return fail(FO_ERR_TOO_LARGE, "fo_sq_norm: array %u with %llu elements exceeds one launch", i, (unsigned long long)arrays[i].n);
     if (count == kNormMaxArrays || chunks + nc > 0x7FFFFFFFull) {
       int rc = flush();

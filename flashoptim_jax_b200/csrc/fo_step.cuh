@@ -524,7 +524,7 @@ FO_DEVI uint2 lds64(uint32_t a) {
 // start the copies of this thread's piece at element i0 of every stream into the stage at
 // shared address st (the group scales are not staged: they are two bytes per 32 elements)
 template <int OPT, int PDT, int ECC_BITS, int STATE>
-FO_DEVI void stage_fill(const DevLeaf& L, const int gdt, const uint32_t i0, const uint32_t st, const Peers& peers) {
+FO_DEVI void stage_fill(const DevLeaf& L, const int gdt, const uint32_t i0, const uint32_t st, const Peers& peers, const int ng) {
   using S = Stage<OPT, PDT, ECC_BITS, STATE>;
   const uint32_t t16 = threadIdx.x * 16u, t8 = threadIdx.x * 8u;
   if constexpr (PDT == FO_F32) {
@@ -547,15 +547,21 @@ FO_DEVI void stage_fill(const DevLeaf& L, const int gdt, const uint32_t i0, cons
     }
   }
   uint32_t gs = st + S::kOffGrad;
-  for (int r = -1; r < peers.ng; ++r) {  // own gradient, then the peers'
-    const char* g = (const char*)L.grad + (r < 0 ? 0ll : peers.gdelta[r]);
+  if (gdt == FO_F32) {
+    copy_async16_l1(gs + t16, (const float*)L.grad + i0);
+    copy_async16_l1(gs + 16u * kThreads + t16, (const float*)L.grad + i0 + 4);
+  } else {
+    copy_async16(gs + t16, (const unsigned short*)L.grad + i0);
+  }
+  for (int r = 0; r < ng; ++r) {  // the peers' pieces follow this rank's
+    const char* g = (const char*)L.grad + peers.gdelta[r];
+    gs += (uint32_t)S::grad_bytes(gdt);
     if (gdt == FO_F32) {
       copy_async16_l1(gs + t16, (const float*)g + i0);
       copy_async16_l1(gs + 16u * kThreads + t16, (const float*)g + i0 + 4);
     } else {
       copy_async16(gs + t16, (const unsigned short*)g + i0);
     }
-    gs += (uint32_t)S::grad_bytes(gdt);
   }
 }
 
@@ -791,9 +797,9 @@ FO_DEVI bool clip_grads(float2 (&g)[4], const int gdt, const Clip& c) {
 
 FO_DEVI float sign_of(float x);
 
-template <int OPT, int PDT, int ECC_BITS, int STATE>
+template <int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
 __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base,
-                                        const float one, const float* lut_mw, const Peers& peers, const Clip& clip);
+                                        const float one, const float* lut_mw, const Peers& peers, const Clip* clip);
 
 // Second half of a hot chunk: update, split, requantize, store.  Each stage runs its packed
 // shortcut unconditionally.
@@ -803,9 +809,9 @@ __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const in
 // REPAIR = true (warm_chunk): the lane that holds such a value (exact zeros are the common case:
 // untouched rows, padding, zero gradients) redoes that stage with IEEE operations, then stores.
 // The stored bits are those of the IEEE path in every case.
-template <bool REPAIR, int OPT, int PDT, int ECC_BITS, int STATE>
+template <bool REPAIR, int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
 FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base, const float one,
-                        bool rare, Unpacked& u, const float* lut_mw, const Peers& peers, const Clip& clip) {
+                        bool rare, Unpacked& u, const float* lut_mw, const Peers& peers, const Clip* clip) {
   using namespace fast2;
   const float2 one2 = sp(one);
   float2 (&g)[4] = u.g;
@@ -1007,7 +1013,7 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
   // ---- first pass: one decision per warp -----------------------------------------------------------------
   if constexpr (!REPAIR) {
     if (__any_sync(0xFFFFFFFFu, rare)) {
-      warm_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, one, lut_mw, peers, clip);
+      warm_chunk<OPT, PDT, ECC_BITS, STATE, AUX>(L, h, gdt, base, one, lut_mw, peers, clip);
       return;
     }
   } else {
@@ -1049,14 +1055,14 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
 // Second chance for a warp whose first pass met a value outside a shortcut's range: the same
 // packed arithmetic from a fresh load, with per-lane IEEE repairs.  About twice the cost of a
 // first pass for that warp, against about seven times for the scalar IEEE path.
-template <int OPT, int PDT, int ECC_BITS, int STATE>
+template <int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
 __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base,
-                                        const float one, const float* lut_mw, const Peers& peers, const Clip& clip) {
+                                        const float one, const float* lut_mw, const Peers& peers, const Clip* clip) {
   Raw<OPT, PDT, ECC_BITS, STATE> raw;
   hot_load<OPT, PDT, ECC_BITS, STATE>(L, gdt, base + threadIdx.x * kPiece, raw);
   Unpacked u;
   hot_unpack<true, OPT, PDT, ECC_BITS, STATE>(raw, gdt, lut_mw, one, u);
-  if (peers.ng > 0) {
+  if (AUX && peers.ng > 0) {
     const uint32_t i0 = base + threadIdx.x * kPiece;
     merge_peer_grads<true>(u.g, gdt, peers, [&](int r, uint4& w0, uint4& w1) {
       const char* g = (const char*)L.grad + peers.gdelta[r];
@@ -1068,8 +1074,8 @@ __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const in
       }
     });
   }
-  if (clip.active) clip_grads<true>(u.g, gdt, clip);
-  hot_finish<true, OPT, PDT, ECC_BITS, STATE>(L, h, gdt, base, one, false, u, lut_mw, peers, clip);
+  if (AUX && clip->active) clip_grads<true>(u.g, gdt, *clip);
+  hot_finish<true, OPT, PDT, ECC_BITS, STATE, AUX>(L, h, gdt, base, one, false, u, lut_mw, peers, clip);
 }
 
 // exact dequantization tables, one entry per code byte (built once per block)
@@ -1104,7 +1110,9 @@ FO_DEVI bool leaf_is_hot(const StepParams& p, int l) {
 // the straight-line path with nothing per chunk but a counter and the prefetch of the block's
 // next chunk; what is left (a ragged last chunk, unaligned leaves, hyper-parameter sets outside
 // the shortcuts' range) goes to the scalar IEEE path.
-template <int OPT, int PDT, int ECC_BITS, int STATE>
+// AUX: the instantiation that also averages the peers' gradients and / or clips by the global
+// norm; the plain one carries none of that code or state.
+template <int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
 __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const __grid_constant__ StepParams p) {
   __shared__ float lut_m[256], lut_v[256];
   __shared__ float lut_m_wide[STATE == FO_STATE_QUANT ? 256 * kLutCopies : 1];
@@ -1115,12 +1123,13 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
   const float* lut_mw = lut_m_wide + (STATE == FO_STATE_QUANT ? (threadIdx.x & (kLutCopies - 1)) : 0);
   extern __shared__ __align__(16) unsigned char stage_mem[];  // p.stages stages of Stage::bytes(grad dtype)
   using S = Stage<OPT, PDT, ECC_BITS, STATE>;
-  const uint32_t stage_bytes = (uint32_t)S::bytes(p.grad_dtype, p.peers.ng);
+  const int ng = AUX ? p.peers.ng : 0;
+  const uint32_t stage_bytes = (uint32_t)S::bytes(p.grad_dtype, ng);
   const uint32_t stage0 = (uint32_t)__cvta_generic_to_shared(stage_mem);
   const uint32_t stage_end = stage0 + (uint32_t)p.stages * stage_bytes;
   const uint32_t toff = threadIdx.x * kPiece;
   const uint32_t grid = gridDim.x;
-  const Clip clip = load_clip(p.sq_norm, p.max_norm, p.grad_dtype);
+  const Clip clip = load_clip(AUX ? p.sq_norm : nullptr, p.max_norm, p.grad_dtype);
   uint32_t c = blockIdx.x;  // this block's next position in the sequence
   for (int l = 0; l < p.n_leaves; ++l) {
     const uint32_t first = p.first_block[l], next = p.first_block[l + 1];
@@ -1141,7 +1150,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
       // iteration is the one read in the iteration before, whose values have been consumed.
       uint32_t fill_ch = ch, fill_base = base, wr = stage0;
       for (int k = 1; k < p.stages; ++k) {
-        if (fill_ch < hot_end) stage_fill<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, fill_base + toff, wr, p.peers);
+        if (fill_ch < hot_end) stage_fill<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, fill_base + toff, wr, p.peers, ng);
         copy_commit();
         fill_ch += grid; fill_base += stride; wr += stage_bytes;
       }
@@ -1153,12 +1162,15 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
         if constexpr (OPT == FO_OPT_ADAM) vsc = ((const __half*)L.nu_scales)[(base + toff) >> 5];
       }
       for (; ch < hot_end; ch += grid, base += stride) {
-        if (fill_ch < hot_end) stage_fill<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, fill_base + toff, wr, p.peers);
+        if (fill_ch < hot_end) stage_fill<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, fill_base + toff, wr, p.peers, ng);
         copy_commit();
         fill_ch += grid; fill_base += stride;
         wr += stage_bytes;
         if (wr == stage_end) wr = stage0;
-        switch (p.stages) {  // all but the oldest group may still be pending
+        if (!AUX || p.stages <= 3) {  // all but the oldest group may still be pending; local streams use 2 or 3 stages
+          if (p.stages == 3) copy_wait<2>();
+          else copy_wait<1>();
+        } else switch (p.stages) {
           case 2: copy_wait<1>(); break;
           case 3: copy_wait<2>(); break;
           case 4: copy_wait<3>(); break;
@@ -1181,7 +1193,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
         }
         Unpacked u;
         bool rare = hot_unpack<false, OPT, PDT, ECC_BITS, STATE>(raw, p.grad_dtype, lut_mw, p.one, u);
-        if (p.peers.ng > 0) {
+        if (AUX && ng > 0) {
           const bool odd = merge_peer_grads<false>(u.g, p.grad_dtype, p.peers, [&](int r, uint4& w0, uint4& w1) {
             const uint32_t at = peer_grads + (uint32_t)r * (uint32_t)S::grad_bytes(p.grad_dtype) + threadIdx.x * 16u;
             w0 = lds128(at);
@@ -1189,11 +1201,11 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
           });
           rare = rare || odd;
         }
-        if (clip.active) {
+        if (AUX && clip.active) {
           const bool odd = clip_grads<false>(u.g, p.grad_dtype, clip);
           rare = rare || odd;
         }
-        hot_finish<false, OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, base, p.one, rare, u, lut_mw, p.peers, clip);
+        hot_finish<false, OPT, PDT, ECC_BITS, STATE, AUX>(L, h, p.grad_dtype, base, p.one, rare, u, lut_mw, p.peers, AUX ? &clip : nullptr);
       }
     }
     for (; ch < end; ch += grid)
@@ -1307,7 +1319,8 @@ constexpr int kSmemPerSm = 227 * 1024, kSmemReservedPerBlock = 1024;
 
 template <int OPT, int PDT, int ECC_BITS, int STATE>
 cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStream_t s) {
-  auto kernel = step_kernel<OPT, PDT, ECC_BITS, STATE>;
+  const bool aux = p_in.peers.ng > 0 || p_in.sq_norm != nullptr;
+  auto kernel = aux ? step_kernel<OPT, PDT, ECC_BITS, STATE, true> : step_kernel<OPT, PDT, ECC_BITS, STATE, false>;
   static int static_smem = -1;  // the same on every device
   if (static_smem < 0) {
     cudaFuncAttributes attr;
@@ -1324,11 +1337,13 @@ cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStre
     blocks_per_sm = 1;
     stages = (kSmemPerSm - kSmemReservedPerBlock - static_smem) / per_stage;
   }
+  static_assert(kMaxStages <= 3, "the plain kernel waits for 2 or 3 stages only");
   const int max_stages = p_in.peers.ng > 0 ? kMaxStagesPeers : kMaxStages;
   if (stages > max_stages) stages = max_stages;
   if (stages < 2) return cudaErrorInvalidConfiguration;
   const int dynamic_smem = stages * per_stage;
-  static bool opted_in[64] = {false};  // per device ordinal: the opt-in above 48 KB belongs to the device's copy of the function
+  static bool opted[2][64] = {};  // per kernel and device ordinal: the opt-in above 48 KB belongs to the device's copy of the function
+  bool* opted_in = opted[aux ? 1 : 0];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
