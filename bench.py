@@ -288,7 +288,9 @@ def run_ours(args):
     e2e = None
     if not args.no_e2e:
         e2e = measure_e2e(args, zero, device, ggen, world, barrier, total_params)
-    finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline, e2e, n_launch, clocks)
+    link_bytes = (sum(g.numel() * g.element_size() for g in pytree.tree_leaves(zero.grads))
+                  + sum(q.numel() * q.element_size() for q in pytree.tree_leaves(zero.params)))
+    finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline, e2e, n_launch, clocks, link_bytes)
 
 
 def measure_e2e(args, zero, device, ggen, world, barrier, total_params):
@@ -341,7 +343,7 @@ def measure_e2e(args, zero, device, ggen, world, barrier, total_params):
             "ms_per_step": e2e_s * 1e3, "steps": e2e_steps}
 
 
-def finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline, e2e, n_launch, clocks):
+def finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline, e2e, n_launch, clocks, link_bytes):
     import torch.distributed as dist
 
     if rank == 0:
@@ -365,9 +367,7 @@ def finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline
             # What must cross NVLink per GPU and direction in one ZeRO-1 step: (N-1)/N of the gradients in
             # (reduce-scatter) and of the parameters out (all-gather), and the same amounts the other way
             # for the peers.  770 GB/s: peer copy per direction measured on this pool.
-            grad_bytes = sum(g.numel() * g.element_size() for g in pytree.tree_leaves(zero.grads))
-            param_bytes = sum(q.numel() * q.element_size() for q in pytree.tree_leaves(zero.params))
-            per_direction = (grad_bytes + param_bytes) * (world - 1) / world
+            per_direction = link_bytes * (world - 1) / world
             achieved = per_direction / (ms_per_step * 1e-3) / 1e9
             line["nvlink"] = {"bytes_per_direction_per_gpu": per_direction, "achieved": achieved, "peak": 770.0, "unit": "GB/s",
                               "frac": achieved / 770.0, "floor_ms": per_direction / 770e9 * 1e3}
