@@ -186,6 +186,9 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
+        # whatever NCCL has to say (its version line at NCCL_DEBUG=VERSION, warnings) goes to stderr:
+        # stdout carries the one JSON line only
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=device)
 
     shapes = WORKLOADS[args.workload]()
@@ -224,7 +227,7 @@ def run_ours(args):
 
     zero = Zero1Optimizer("adamw", params, step_fn=counting_launch, fused_allgather=(world > 1 and not args.nccl_allgather),
                           fused_reduce_scatter=(world > 1 and not args.nccl_reduce_scatter and args.clip is None),
-                          max_grad_norm=args.clip, **HPARAMS)
+                          max_grad_norm=args.clip, n_slices=args.slices, **HPARAMS)
     del params
     torch.cuda.empty_cache()
     ggen = torch.Generator(device=device)
@@ -357,7 +360,7 @@ def finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline
             "config": {"workload": args.workload, "leaves": len(shapes), "params": total_params, "optimizer": "flash_adamw",
                        **HPARAMS, "grad_dtype": "bf16", "parallelism": "single" if world == 1 else f"zero1x{world}",
                        "reduce_scatter": None if world == 1 else ("nccl" if (args.nccl_reduce_scatter or args.clip is not None) else "fused into the step kernel (peer loads)"),
-                       "clip_global_norm": args.clip,
+                       "clip_global_norm": args.clip, "slices": args.slices,
                        "allgather": None if world == 1 else ("nccl" if args.nccl_allgather else "fused into the step kernel (peer stores)"),
                        "l2": "working set per step (>= 14 B/param) exceeds the 126 MB L2, no flush needed"},
             "roofline": roofline, "cpu_baseline": base, "e2e": e2e, "gpu_launches": n_launch, "clocks": clocks,
@@ -386,6 +389,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (used for ncu captures)")
     ap.add_argument("--nccl-allgather", action="store_true", help="N > 1: NCCL all-gather after the step instead of peer stores inside it")
+    ap.add_argument("--slices", type=int, default=None,
+                    help="N > 1 with both NCCL collectives: slices per bucket whose reduce-scatter / step / all-gather overlap")
     ap.add_argument("--clip", type=float, default=None,
                     help="clip the gradients at this global norm inside the step (adds the sum-of-squares sweep; off by default)")
     ap.add_argument("--nccl-reduce-scatter", action="store_true", help="N > 1: NCCL reduce-scatter before the step instead of peer loads inside it")
