@@ -171,7 +171,32 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+_REAL_STDOUT = None
+
+
+def quiet_stdout():
+    """Point file descriptor 1 at stderr for the duration of the run: libraries that write to stdout on their own
+    (NCCL prints its version there at NCCL_DEBUG=VERSION) must not add lines to the one JSON line of the result."""
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line):
+    """The one JSON line, on the real stdout."""
+    text = json.dumps(line) + "\n"
+    sys.stdout.flush()
+    if _REAL_STDOUT is None:
+        sys.stdout.write(text)
+        sys.stdout.flush()
+    else:
+        os.write(_REAL_STDOUT, text.encode())
+
+
 def run_ours(args):
+    quiet_stdout()
     import torch
     import torch.distributed as dist
 
@@ -186,9 +211,6 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
-        # whatever NCCL has to say (its version line at NCCL_DEBUG=VERSION, warnings) goes to stderr:
-        # stdout carries the one JSON line only
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=device)
 
     shapes = WORKLOADS[args.workload]()
@@ -374,7 +396,7 @@ def finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline
             achieved = per_direction / (ms_per_step * 1e-3) / 1e9
             line["nvlink"] = {"bytes_per_direction_per_gpu": per_direction, "achieved": achieved, "peak": 770.0, "unit": "GB/s",
                               "frac": achieved / 770.0, "floor_ms": per_direction / 770e9 * 1e3}
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
