@@ -34,7 +34,7 @@ UNIT = "params/s"
 BYTES_PER_PARAM_BF16_ECC16 = (2 + 2 + 2 + 1 + 1 + 0.125) + (2 + 2 + 1 + 1 + 0.125)  # 14.25
 BYTES_PER_PARAM_F32 = (4 + 4 + 1 + 1 + 0.125) + (4 + 1 + 1 + 0.125)                   # 16.25
 # DRAM bytes per parameter seen by one ncu capture of the bf16 kernel (profiles/), scaled to a launch by its parameter count
-NCU_DRAM_BYTES_PER_PARAM = 13.43  # profiles/step_kernel_adam_bf16_ecc16_quant__one_64M_leaf.md: 901.3 MB per 67,108,864 params; traffic is proportional to the parameter count
+NCU_DRAM_BYTES_PER_PARAM = 13.47  # profiles/step_kernel_adam_bf16_ecc16_quant__one_64M_leaf.md: 904.3 MB per 67,108,864 params; traffic is proportional to the parameter count
 
 
 def llama3_8b_shapes():
