@@ -161,6 +161,23 @@ def step_scalars(count: torch.Tensor, learning_rate: Any, b1: float, b2: float, 
     return out
 
 
+def device_step_scalars(count: Any, leaves: List[torch.Tensor], configs: List[Dict[str, Any]]):
+    """For a capturable step: advance the device counter and form each hyper-parameter group's scalars on the
+    device.  Returns (counter tensor, per-leaf pointer to its group's float32[3], tensors to keep alive until the
+    launch has been issued)."""
+    count = as_tensor(count, dtype=torch.int32)
+    if not count.is_cuda:
+        count = count.to(leaves[0].device)  # first step after an init on the host
+    keys = [tuple(sorted(((k, id(v) if isinstance(v, torch.Tensor) else v) for k, v in c.items()), key=lambda kv: kv[0]))
+            for c in configs]
+    distinct = list(dict.fromkeys(keys))
+    scalars = {}
+    for i, key in enumerate(distinct):
+        c = configs[keys.index(key)]
+        scalars[key] = step_scalars(count, c["learning_rate"], c.get("b1", 0.0), c.get("b2", 0.0), write_count=i == len(distinct) - 1)
+    return count, [scalars[key].data_ptr() for key in keys], list(scalars.values())
+
+
 def launch(opt: int, work: List[LeafWork], peer_param_offsets: Optional[List[int]] = None,
            peer_grad_offsets: Optional[List[int]] = None) -> int:
     """Issue one fo_step per bucket (per <=16 hyper sets); returns the number of calls.

@@ -70,21 +70,12 @@ def _make_adam_transform(learning_rate, b1, b2, eps, weight_decay, quantize, mas
         param_pl, grad_leaves, (ecc_leaves, mu_leaves, nu_leaves), treedef = eng.flatten_step_inputs(
             name, params, grads, [state.ecc, state.mu, state.nu])
         leaves = [as_tensor(leaf) for _, leaf in param_pl]
-        count = as_tensor(state.count, dtype=torch.int32)
-        if not count.is_cuda:
-            count = count.to(leaves[0].device)  # first step after an init on the host
         configs = [utils._group_config_for_path(path, leaf, defaults, param_groups) for (path, _), leaf in zip(param_pl, leaves)]
-        keys = [tuple(sorted(((k, id(v) if isinstance(v, torch.Tensor) else v) for k, v in c.items()), key=lambda kv: kv[0]))
-                for c in configs]
-        distinct = list(dict.fromkeys(keys))
-        scalars = {}
-        for i, key in enumerate(distinct):
-            c = configs[keys.index(key)]
-            scalars[key] = eng.step_scalars(count, c["learning_rate"], c["b1"], c["b2"], write_count=i == len(distinct) - 1)
+        count, pointers, _alive = eng.device_step_scalars(state.count, leaves, configs)
         work: List[eng.LeafWork] = []
         new_p, new_e, new_m, new_v = [], [], [], []
-        for leaf, key, config, g, e, m, v in zip(leaves, keys, configs, grad_leaves, ecc_leaves, mu_leaves, nu_leaves):
-            hyper = adam_hyper(config, 0.0, 1, decoupled_weight_decay) + (scalars[key].data_ptr(),)  # lr, bc1, bc2 come from the device
+        for leaf, ptr, config, g, e, m, v in zip(leaves, pointers, configs, grad_leaves, ecc_leaves, mu_leaves, nu_leaves):
+            hyper = adam_hyper(config, 0.0, 1, decoupled_weight_decay) + (ptr,)  # lr, bc1, bc2 come from the device
             w, p_out, e_out, m_out, v_out = eng.make_work(leaf, g, e, m, v, config, hyper, donate, has_nu=True)
             work.append(w)
             new_p.append(p_out); new_e.append(e_out); new_m.append(m_out); new_v.append(v_out)

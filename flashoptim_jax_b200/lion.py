@@ -36,7 +36,8 @@ def lion_hyper(config: Dict[str, Any], lr: float):
 
 def flash_lion(learning_rate=1e-4, b1: float = 0.9, b2: float = 0.99, weight_decay: float = 0.0, quantize: bool = True,
                master_weight_bits: Optional[int] = 24, group_size: int = 32, fused: bool = True,
-               param_groups: Optional[List[Dict[str, Any]]] = None, donate: bool = False) -> utils.FlashOptimizer:
+               param_groups: Optional[List[Dict[str, Any]]] = None, donate: bool = False,
+               capturable: bool = False) -> utils.FlashOptimizer:
     name = "flash_lion"
     utils._validate_master_weight_bits(master_weight_bits)
     utils._validate_fused_group_size(group_size, quantize=quantize, fused=fused)
@@ -50,6 +51,22 @@ def flash_lion(learning_rate=1e-4, b1: float = 0.9, b2: float = 0.99, weight_dec
         mus = [eng.init_moment(leaf, c["group_size"], c["quantize"], torch.int8) for _, leaf, c in entries]
         eccs = [eng.init_ecc(leaf, c["master_weight_bits"]) for _, leaf, c in entries]
         return FlashLionState(count=torch.zeros((), dtype=torch.int32), mu=treedef.unflatten(mus), ecc=treedef.unflatten(eccs))
+
+    def capturable_step_fn(params: Any, state: FlashLionState, grads: Any):
+        """The same step with no host scalar in it (counter and learning rate stay on the device, see
+        flash_adamw(capturable=True)): capturable in a CUDA graph."""
+        param_pl, grad_leaves, (ecc_leaves, mu_leaves), treedef = eng.flatten_step_inputs(
+            name, params, grads, [state.ecc, state.mu])
+        leaves = [as_tensor(leaf) for _, leaf in param_pl]
+        configs = [utils._group_config_for_path(path, leaf, defaults, param_groups) for (path, _), leaf in zip(param_pl, leaves)]
+        count, pointers, _alive = eng.device_step_scalars(state.count, leaves, configs)
+        work, new_p, new_e, new_m = [], [], [], []
+        for leaf, ptr, config, g, e, m in zip(leaves, pointers, configs, grad_leaves, ecc_leaves, mu_leaves):
+            w, p_out, e_out, m_out, _ = eng.make_work(leaf, g, e, m, None, config, lion_hyper(config, 0.0) + (ptr,), donate, has_nu=False)
+            work.append(w)
+            new_p.append(p_out); new_e.append(e_out); new_m.append(m_out)
+        eng.launch(_lib.FO_OPT_LION, work)
+        return treedef.unflatten(new_p), FlashLionState(count=count, mu=treedef.unflatten(new_m), ecc=treedef.unflatten(new_e))
 
     def step_fn(params: Any, state: FlashLionState, grads: Any):
         old_count = as_tensor(state.count, dtype=torch.int32).cpu()
@@ -69,7 +86,7 @@ def flash_lion(learning_rate=1e-4, b1: float = 0.9, b2: float = 0.99, weight_dec
                                    mu=treedef.unflatten(new_m), ecc=treedef.unflatten(new_e))
         return treedef.unflatten(new_p), new_state
 
-    return utils.FlashOptimizer(init=init_fn, step=step_fn)
+    return utils.FlashOptimizer(init=init_fn, step=capturable_step_fn if capturable else step_fn)
 
 
 def flash_lion_state_dict(state: FlashLionState) -> Dict[str, Any]:

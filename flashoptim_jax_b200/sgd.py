@@ -43,7 +43,7 @@ def sgd_hyper(config: Dict[str, Any], lr: float, decoupled_weight_decay: bool):
 
 
 def _make_sgd_transform(learning_rate, momentum, dampening, weight_decay, nesterov, quantize, master_weight_bits,
-                        group_size, fused, decoupled_weight_decay, param_groups, name, donate) -> utils.FlashOptimizer:
+                        group_size, fused, decoupled_weight_decay, param_groups, name, donate, capturable=False) -> utils.FlashOptimizer:
     utils._validate_master_weight_bits(master_weight_bits)
     utils._validate_fused_group_size(group_size, quantize=quantize, fused=fused)
     _validate_sgd_hparams(momentum, dampening, nesterov)
@@ -65,6 +65,27 @@ def _make_sgd_transform(learning_rate, momentum, dampening, weight_decay, nester
                 mus.append(utils.no_state_leaf(leaf.device))
             eccs.append(eng.init_ecc(leaf, c["master_weight_bits"]))
         return FlashSGDState(count=torch.zeros((), dtype=torch.int32), mu=treedef.unflatten(mus), ecc=treedef.unflatten(eccs))
+
+    def capturable_step_fn(params: Any, state: FlashSGDState, grads: Any):
+        """The same step with no host scalar in it (counter and learning rate stay on the device, see
+        flash_adamw(capturable=True)): capturable in a CUDA graph."""
+        param_pl, grad_leaves, (ecc_leaves, mu_leaves), treedef = eng.flatten_step_inputs(
+            name, params, grads, [state.ecc, state.mu])
+        leaves = [as_tensor(leaf) for _, leaf in param_pl]
+        configs = [utils._group_config_for_path(path, leaf, defaults, param_groups) for (path, _), leaf in zip(param_pl, leaves)]
+        count, pointers, _alive = eng.device_step_scalars(state.count, leaves, configs)
+        work, new_p, new_e, new_m = [], [], [], []
+        for leaf, ptr, config, g, e, m in zip(leaves, pointers, configs, grad_leaves, ecc_leaves, mu_leaves):
+            use_momentum = config["momentum"] > 0.0
+            if use_momentum and not utils._has_state_leaf(m):
+                raise ValueError(f"{name}: momentum > 0 needs a momentum buffer in the state; re-run init()")
+            hyper = sgd_hyper(config, 0.0, decoupled_weight_decay) + (ptr,)
+            w, p_out, e_out, m_out, _ = eng.make_work(leaf, g, e, m, None, config, hyper, donate, has_nu=False,
+                                                      use_momentum=use_momentum)
+            work.append(w)
+            new_p.append(p_out); new_e.append(e_out); new_m.append(m_out)
+        eng.launch(_lib.FO_OPT_SGD, work)
+        return treedef.unflatten(new_p), FlashSGDState(count=count, mu=treedef.unflatten(new_m), ecc=treedef.unflatten(new_e))
 
     def step_fn(params: Any, state: FlashSGDState, grads: Any):
         old_count = as_tensor(state.count, dtype=torch.int32).cpu()
@@ -88,23 +109,25 @@ def _make_sgd_transform(learning_rate, momentum, dampening, weight_decay, nester
                                   mu=treedef.unflatten(new_m), ecc=treedef.unflatten(new_e))
         return treedef.unflatten(new_p), new_state
 
-    return utils.FlashOptimizer(init=init_fn, step=step_fn)
+    return utils.FlashOptimizer(init=init_fn, step=capturable_step_fn if capturable else step_fn)
 
 
 def flash_sgd(learning_rate=1e-3, momentum: float = 0.0, dampening: float = 0.0, weight_decay: float = 0.0,
               nesterov: bool = False, quantize: bool = True, master_weight_bits: Optional[int] = 24, group_size: int = 32,
-              fused: bool = True, param_groups: Optional[List[Dict[str, Any]]] = None, donate: bool = False) -> utils.FlashOptimizer:
+              fused: bool = True, param_groups: Optional[List[Dict[str, Any]]] = None, donate: bool = False,
+              capturable: bool = False) -> utils.FlashOptimizer:
     """SGD with weight decay added to the gradient (flashoptim_jax/sgd.py:267-287)."""
     return _make_sgd_transform(learning_rate, momentum, dampening, weight_decay, nesterov, quantize, master_weight_bits,
-                               group_size, fused, False, param_groups, "flash_sgd", donate)
+                               group_size, fused, False, param_groups, "flash_sgd", donate, capturable)
 
 
 def flash_sgdw(learning_rate=1e-3, momentum: float = 0.0, dampening: float = 0.0, weight_decay: float = 0.0,
                nesterov: bool = False, quantize: bool = True, master_weight_bits: Optional[int] = 24, group_size: int = 32,
-               fused: bool = True, param_groups: Optional[List[Dict[str, Any]]] = None, donate: bool = False) -> utils.FlashOptimizer:
+               fused: bool = True, param_groups: Optional[List[Dict[str, Any]]] = None, donate: bool = False,
+              capturable: bool = False) -> utils.FlashOptimizer:
     """SGD with decoupled weight decay (flashoptim_jax/sgd.py:290-310)."""
     return _make_sgd_transform(learning_rate, momentum, dampening, weight_decay, nesterov, quantize, master_weight_bits,
-                               group_size, fused, True, param_groups, "flash_sgdw", donate)
+                               group_size, fused, True, param_groups, "flash_sgdw", donate, capturable)
 
 
 def flash_sgd_state_dict(state: FlashSGDState) -> Dict[str, Any]:

@@ -79,3 +79,34 @@ def test_step_captured_in_a_cuda_graph_replays_like_eager_steps():
     for name in ("mu", "nu", "ecc"):
         for a, b in zip(tree.tree_leaves(getattr(state, name)), tree.tree_leaves(getattr(plain_state, name))):
             assert torch.equal(torch.as_tensor(a), torch.as_tensor(b))
+
+
+@pytest.mark.parametrize("name,kw", [("flash_lion", dict(weight_decay=1e-2)), ("flash_sgdw", dict(momentum=0.9, weight_decay=1e-2))])
+def test_capturable_lion_and_sgd_equal_the_host_scalar_steps(name, kw):
+    import torch
+
+    import flashoptim_jax_b200 as fo
+    from flashoptim_jax_b200 import tree
+
+    make = getattr(fo, name)
+    lrs = [1e-3, 5e-4, 2e-4]
+    want_p, plain_state = _tree(0, 0.02), None
+    for t, lr in enumerate(lrs):
+        plain = make(learning_rate=lr, master_weight_bits=24, donate=True, **kw)
+        if plain_state is None:
+            plain_state = plain.init(want_p)
+        want_p, plain_state = plain.step(want_p, plain_state, _tree(100 + t, 1e-3))
+    lr_dev = torch.tensor(lrs[0], dtype=torch.float32, device="cuda")
+    tx = make(learning_rate=lr_dev, master_weight_bits=24, donate=True, capturable=True, **kw)
+    params = _tree(0, 0.02)
+    state = tx.init(params)
+    for t, lr in enumerate(lrs):
+        lr_dev.fill_(lr)
+        params, state = tx.step(params, state, _tree(100 + t, 1e-3))
+    torch.cuda.synchronize()
+    assert state.count.is_cuda and int(state.count) == 3
+    for a, b in zip(tree.tree_leaves(params), tree.tree_leaves(want_p)):
+        assert torch.equal(a, b)
+    for field in ("mu", "ecc"):
+        for a, b in zip(tree.tree_leaves(getattr(state, field)), tree.tree_leaves(getattr(plain_state, field))):
+            assert torch.equal(torch.as_tensor(a), torch.as_tensor(b))
