@@ -227,7 +227,7 @@ def run_ours(args):
     kernel_ms = {}  # per (param dtype code) -> list of launch durations
     pending = []
 
-    def timed_launch(opt, work, peers=None, grad_peers=None):
+    def timed_launch(opt, work, peers=None, grad_peers=None, mc_param=0, mc_grad=0):
         by_bucket = {}
         for w in work:
             by_bucket.setdefault(w.bucket, []).append(w)
@@ -235,21 +235,21 @@ def run_ours(args):
         for bucket, items in by_bucket.items():
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            calls += eng.launch(opt, items, peers, grad_peers)
+            calls += eng.launch(opt, items, peers, grad_peers, mc_param, mc_grad)
             e1.record()
             pending.append((bucket[1], sum(w.param.numel() for w in items), e0, e1))
         return calls
 
     launches = [0]
 
-    def counting_launch(opt, work, peers=None, grad_peers=None):
-        n = timed_launch(opt, work, peers, grad_peers)
+    def counting_launch(opt, work, peers=None, grad_peers=None, mc_param=0, mc_grad=0):
+        n = timed_launch(opt, work, peers, grad_peers, mc_param, mc_grad)
         launches[0] += n
         return n
 
     zero = Zero1Optimizer("adamw", params, step_fn=counting_launch, fused_allgather=(world > 1 and not args.nccl_allgather),
                           fused_reduce_scatter=(world > 1 and not args.nccl_reduce_scatter and args.clip is None),
-                          max_grad_norm=args.clip, n_slices=args.slices, **HPARAMS)
+                          max_grad_norm=args.clip, n_slices=args.slices, use_switch=False if args.no_switch else None, **HPARAMS)
     del params
     torch.cuda.empty_cache()
     ggen = torch.Generator(device=device)
@@ -315,7 +315,8 @@ def run_ours(args):
         e2e = measure_e2e(args, zero, device, ggen, world, barrier, total_params)
     link_bytes = (sum(g.numel() * g.element_size() for g in pytree.tree_leaves(zero.grads))
                   + sum(q.numel() * q.element_size() for q in pytree.tree_leaves(zero.params)))
-    finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline, e2e, n_launch, clocks, link_bytes)
+    zero_info = {"mc": list(zero.mc_param_offsets) + list(zero.mc_grad_offsets)}
+    finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline, e2e, n_launch, clocks, link_bytes, zero_info)
 
 
 def measure_e2e(args, zero, device, ggen, world, barrier, total_params):
@@ -368,7 +369,7 @@ def measure_e2e(args, zero, device, ggen, world, barrier, total_params):
             "ms_per_step": e2e_s * 1e3, "steps": e2e_steps}
 
 
-def finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline, e2e, n_launch, clocks, link_bytes):
+def finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline, e2e, n_launch, clocks, link_bytes, zero_info):
     import torch.distributed as dist
 
     if rank == 0:
@@ -383,6 +384,7 @@ def finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline
                        **HPARAMS, "grad_dtype": "bf16", "parallelism": "single" if world == 1 else f"zero1x{world}",
                        "reduce_scatter": None if world == 1 else ("nccl" if (args.nccl_reduce_scatter or args.clip is not None) else "fused into the step kernel (peer loads)"),
                        "clip_global_norm": args.clip, "slices": args.slices,
+                       "switch": None if world == 1 else bool(any(zero_info["mc"])),
                        "allgather": None if world == 1 else ("nccl" if args.nccl_allgather else "fused into the step kernel (peer stores)"),
                        "l2": "working set per step (>= 14 B/param) exceeds the 126 MB L2, no flush needed"},
             "roofline": roofline, "cpu_baseline": base, "e2e": e2e, "gpu_launches": n_launch, "clocks": clocks,
@@ -411,6 +413,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (used for ncu captures)")
     ap.add_argument("--nccl-allgather", action="store_true", help="N > 1: NCCL all-gather after the step instead of peer stores inside it")
+    ap.add_argument("--no-switch", action="store_true",
+                    help="N > 1: fused collectives over point-to-point peer accesses only (no multicast through the NVLink switch)")
     ap.add_argument("--slices", type=int, default=None,
                     help="N > 1 with both NCCL collectives: slices per bucket whose reduce-scatter / step / all-gather overlap")
     ap.add_argument("--clip", type=float, default=None,

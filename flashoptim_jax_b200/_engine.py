@@ -179,13 +179,15 @@ def device_step_scalars(count: Any, leaves: List[torch.Tensor], configs: List[Di
 
 
 def launch(opt: int, work: List[LeafWork], peer_param_offsets: Optional[List[int]] = None,
-           peer_grad_offsets: Optional[List[int]] = None) -> int:
+           peer_grad_offsets: Optional[List[int]] = None, mc_param_offset: int = 0, mc_grad_offset: int = 0) -> int:
     """Issue one fo_step per bucket (per <=16 hyper sets); returns the number of calls.
 
     peer_param_offsets: byte distances from every param address to the same element of each peer
     GPU's replica; when given, the kernel also stores the updated parameters there.
     peer_grad_offsets: byte distances from every grad address to the same element of each peer GPU's
-    gradient buffer; when given, the kernel averages the gradients over the ranks as it reads them."""
+    gradient buffer; when given, the kernel averages the gradients over the ranks as it reads them.
+    mc_param_offset / mc_grad_offset: byte distances to the multicast mappings of the same buffers; when
+    non-zero the two exchanges go through the NVLink switch (one multicast store, one multicast load-reduce)."""
     peers = np.asarray(peer_param_offsets or [], dtype=np.int64)
     grad_peers = np.asarray(peer_grad_offsets or [], dtype=np.int64)
     if len(peers) and len(grad_peers) and len(peers) != len(grad_peers):
@@ -226,6 +228,7 @@ def launch(opt: int, work: List[LeafWork], peer_param_offsets: Optional[List[int
                 n_peers=n_peers, peer_param_offsets=peers.ctypes.data if len(peers) else None,
                 peer_grad_offsets=grad_peers.ctypes.data if len(grad_peers) else None,
             )
+            desc.mc_param_offset, desc.mc_grad_offset = int(mc_param_offset), int(mc_grad_offset)
             clip = getattr(_clip, "value", None)
             if clip is not None:
                 desc.grad_sq_norm, desc.max_grad_norm = clip[0].data_ptr(), clip[1]

@@ -63,6 +63,7 @@ class FoStepDesc(ctypes.Structure):
         ("n_peers", ctypes.c_uint32), ("reserved", ctypes.c_uint32), ("peer_param_offsets", ctypes.c_void_p),
         ("peer_grad_offsets", ctypes.c_void_p),
         ("grad_sq_norm", ctypes.c_void_p), ("max_grad_norm", ctypes.c_float), ("reserved2", ctypes.c_uint32),
+        ("mc_param_offset", ctypes.c_int64), ("mc_grad_offset", ctypes.c_int64),
     ]
 
 

@@ -143,6 +143,14 @@ extern "C" int fo_step(const FoStepDesc* d, void* cuda_stream) {
     p.peers.ranks_pow2 = (ranks & (ranks - 1)) == 0;
   }
 
+  if (d->mc_param_offset != 0) {
+    if (d->peer_param_offsets == nullptr || d->n_peers == 0) return fail(FO_ERR_INVALID_ARG, "fo_step: mc_param_offset without peer_param_offsets");
+    p.peers.mc_pdelta = (long long)d->mc_param_offset;
+  }
+  if (d->mc_grad_offset != 0) {
+    if (d->peer_grad_offsets == nullptr || d->n_peers == 0) return fail(FO_ERR_INVALID_ARG, "fo_step: mc_grad_offset without peer_grad_offsets");
+    p.peers.mc_gdelta = (long long)d->mc_grad_offset;
+  }
   p.sq_norm = d->grad_sq_norm;
   p.max_norm = d->max_grad_norm;
 

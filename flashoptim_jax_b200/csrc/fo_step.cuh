@@ -91,7 +91,28 @@ struct Peers {
   float rcp_ranks;    // RN(1 / (ng + 1))
   int ranks_pow2;     // the division by the rank count is exact for every input
   int pad;
+  // NVLink-switch forms of the two exchanges (0 = off; the point-to-point tables above stay valid
+  // and serve the ragged ends): byte distance from a local address to the multicast address of
+  // the same element.  A multicast store reaches every rank's replica, this one's included; a
+  // multicast load-reduce returns the sum over all ranks' gradients, added up in the switch in
+  // fp32 and rounded to the gradient dtype.
+  long long mc_pdelta;
+  long long mc_gdelta;
 };
+
+FO_DEVI uint4 multicast_sum(const void* p, const int gdt) {
+  uint4 v;
+  if (gdt == FO_BF16)
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  else
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+FO_DEVI void multicast_store(void* p, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 template <typename T>
 FO_DEVI void store_to_peers(const Peers& peers, T* local, const T& v) {
   for (int r = 0; r < peers.n; ++r) *reinterpret_cast<T*>(reinterpret_cast<char*>(local) + peers.delta[r]) = v;
@@ -496,6 +517,7 @@ constexpr int kMaxStages = FO_MAX_STAGES;   // local streams: deeper brings noth
 #define FO_MAX_STAGES_PEERS 8
 #endif
 constexpr int kMaxStagesPeers = FO_MAX_STAGES_PEERS;  // gradients read from peers over NVLink: several times the latency to cover
+constexpr int kSwitchBatch = 4;  // multicast load-reduces a thread keeps in flight
 FO_DEVI void copy_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -524,7 +546,8 @@ FO_DEVI uint2 lds64(uint32_t a) {
 // start the copies of this thread's piece at element i0 of every stream into the stage at
 // shared address st (the group scales are not staged: they are two bytes per 32 elements)
 template <int OPT, int PDT, int ECC_BITS, int STATE>
-FO_DEVI void stage_fill(const DevLeaf& L, const int gdt, const uint32_t i0, const uint32_t st, const Peers& peers, const int ng) {
+FO_DEVI void stage_fill(const DevLeaf& L, const int gdt, const uint32_t i0, const uint32_t st, const Peers& peers, const int ng,
+                        const bool with_grad = true) {
   using S = Stage<OPT, PDT, ECC_BITS, STATE>;
   const uint32_t t16 = threadIdx.x * 16u, t8 = threadIdx.x * 8u;
   if constexpr (PDT == FO_F32) {
@@ -546,6 +569,7 @@ FO_DEVI void stage_fill(const DevLeaf& L, const int gdt, const uint32_t i0, cons
       copy_async16_l1(st + S::kOffNu + 16u * kThreads + t16, (const float*)L.nu + i0 + 4);
     }
   }
+  if (!with_grad) return;  // the gradients arrive as sums from the switch (see the ring in step_kernel)
   uint32_t gs = st + S::kOffGrad;
   if (gdt == FO_F32) {
     copy_async16_l1(gs + t16, (const float*)L.grad + i0);
@@ -708,13 +732,15 @@ FO_DEVI void grad_pairs(const uint4& w0, const uint4& w1, const int gdt, float2 
   else pairs_of16<FO_F16>(w0, o);
 }
 
+template <bool REPAIR>
+FO_DEVI bool mean_of_sum(float2 (&g)[4], const int gdt, const Peers& peers);
+
 // Reduce-scatter folded into the step (see Peers): g holds this rank's gradients on entry and the
 // mean over the ranks, rounded to the gradient dtype, on return.  fetch(r, w0, w1) delivers the
 // words of peer r's piece.  Same contract for REPAIR as hot_unpack.
 template <bool REPAIR, typename Fetch>
 FO_DEVI bool merge_peer_grads(float2 (&g)[4], const int gdt, const Peers& peers, Fetch fetch) {
   using namespace fast2;
-  bool rare = false;
   for (int r = 0; r < peers.ng; ++r) {
     uint4 w0, w1 = make_uint4(0u, 0u, 0u, 0u);
     fetch(r, w0, w1);
@@ -723,6 +749,14 @@ FO_DEVI bool merge_peer_grads(float2 (&g)[4], const int gdt, const Peers& peers,
 #pragma unroll
     for (int k = 0; k < 4; ++k) g[k] = add2(g[k], pg[k]);
   }
+  return mean_of_sum<REPAIR>(g, gdt, peers);
+}
+
+// second half of the averaging: g holds the sum over the ranks on entry
+template <bool REPAIR>
+FO_DEVI bool mean_of_sum(float2 (&g)[4], const int gdt, const Peers& peers) {
+  using namespace fast2;
+  bool rare = false;
   float2 mean[4];
 #pragma unroll
   for (int k = 0; k < 4; ++k) mean[k] = div_by_rcp2(g[k], sp(peers.neg_ranks), sp(peers.rcp_ranks));
@@ -1023,14 +1057,24 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
   if constexpr (PDT == FO_F32) {
     const float4 lo = make_float4(theta[0].x, theta[0].y, theta[1].x, theta[1].y);
     const float4 hi = make_float4(theta[2].x, theta[2].y, theta[3].x, theta[3].y);
-    __stcs((float4*)((float*)L.param + i0), lo);
-    __stcs((float4*)((float*)L.param + i0) + 1, hi);
-    store_to_peers(peers, (float4*)((float*)L.param + i0), lo);
-    store_to_peers(peers, (float4*)((float*)L.param + i0) + 1, hi);
+    if (AUX && peers.mc_pdelta != 0) {
+      char* mc = (char*)((float*)L.param + i0) + peers.mc_pdelta;
+      multicast_store(mc, make_uint4(__float_as_uint(lo.x), __float_as_uint(lo.y), __float_as_uint(lo.z), __float_as_uint(lo.w)));
+      multicast_store(mc + 16, make_uint4(__float_as_uint(hi.x), __float_as_uint(hi.y), __float_as_uint(hi.z), __float_as_uint(hi.w)));
+    } else {
+      __stcs((float4*)((float*)L.param + i0), lo);
+      __stcs((float4*)((float*)L.param + i0) + 1, hi);
+      store_to_peers(peers, (float4*)((float*)L.param + i0), lo);
+      store_to_peers(peers, (float4*)((float*)L.param + i0) + 1, hi);
+    }
   } else {
     const uint4 w = make_uint4(nw[0], nw[1], nw[2], nw[3]);
-    __stcs((uint4*)((unsigned short*)L.param + i0), w);
-    store_to_peers(peers, (uint4*)((unsigned short*)L.param + i0), w);
+    if (AUX && peers.mc_pdelta != 0) {
+      multicast_store((char*)((unsigned short*)L.param + i0) + peers.mc_pdelta, w);
+    } else {
+      __stcs((uint4*)((unsigned short*)L.param + i0), w);
+      store_to_peers(peers, (uint4*)((unsigned short*)L.param + i0), w);
+    }
     if constexpr (ECC_BITS == 16) __stcs((uint4*)((short*)L.ecc + i0), ecc_out);
     if constexpr (ECC_BITS == 8) __stcs((uint2*)((signed char*)L.ecc + i0), make_uint2(ecc_out.x, ecc_out.y));
   }
@@ -1123,10 +1167,17 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
   const float* lut_mw = lut_m_wide + (STATE == FO_STATE_QUANT ? (threadIdx.x & (kLutCopies - 1)) : 0);
   extern __shared__ __align__(16) unsigned char stage_mem[];  // p.stages stages of Stage::bytes(grad dtype)
   using S = Stage<OPT, PDT, ECC_BITS, STATE>;
-  const int ng = AUX ? p.peers.ng : 0;
+  // gradients summed in the NVLink switch (16-bit gradients only; fp32 leaves take the point-to-point route)
+  const bool switch_sum = AUX && p.peers.mc_gdelta != 0 && p.grad_dtype != FO_F32;
+  const int ng = (AUX && !switch_sum) ? p.peers.ng : 0;
   const uint32_t stage_bytes = (uint32_t)S::bytes(p.grad_dtype, ng);
   const uint32_t stage0 = (uint32_t)__cvta_generic_to_shared(stage_mem);
   const uint32_t stage_end = stage0 + (uint32_t)p.stages * stage_bytes;
+  // Ring of kSwitchBatch thread-private slots behind the stages.  A multicast load-reduce takes
+  // several microseconds and no asynchronous copy can issue one, so each thread keeps a batch of
+  // them in registers: at every kSwitchBatch-th iteration it parks the batch that has arrived in
+  // the ring (the sums for this and the next iterations) and issues the next batch.
+  const uint32_t ring0 = stage_end;
   const uint32_t toff = threadIdx.x * kPiece;
   const uint32_t grid = gridDim.x;
   const Clip clip = load_clip(AUX ? p.sq_norm : nullptr, p.max_norm, p.grad_dtype);
@@ -1149,8 +1200,17 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
       // groups still pending always tells which chunk has landed).  The stage filled in an
       // iteration is the one read in the iteration before, whose values have been consumed.
       uint32_t fill_ch = ch, fill_base = base, wr = stage0;
+      uint4 batch[kSwitchBatch] = {};
+      uint32_t turn = 0;  // iteration number inside the run, modulo kSwitchBatch
+      const char* mc_grad = (const char*)L.grad + p.peers.mc_gdelta;
+      if (switch_sum) {
+#pragma unroll
+        for (int k = 0; k < kSwitchBatch; ++k)
+          if (ch + (uint32_t)k * grid < hot_end)
+            batch[k] = multicast_sum(mc_grad + (size_t)(base + (uint32_t)k * stride + toff) * 2u, p.grad_dtype);
+      }
       for (int k = 1; k < p.stages; ++k) {
-        if (fill_ch < hot_end) stage_fill<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, fill_base + toff, wr, p.peers, ng);
+        if (fill_ch < hot_end) stage_fill<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, fill_base + toff, wr, p.peers, ng, !switch_sum);
         copy_commit();
         fill_ch += grid; fill_base += stride; wr += stage_bytes;
       }
@@ -1162,7 +1222,16 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
         if constexpr (OPT == FO_OPT_ADAM) vsc = ((const __half*)L.nu_scales)[(base + toff) >> 5];
       }
       for (; ch < hot_end; ch += grid, base += stride) {
-        if (fill_ch < hot_end) stage_fill<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, fill_base + toff, wr, p.peers, ng);
+        if (switch_sum && turn == 0) {
+#pragma unroll
+          for (int k = 0; k < kSwitchBatch; ++k) {  // park what has arrived, ask for the batch after it
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(ring0 + (uint32_t)k * (16u * kThreads) + threadIdx.x * 16u),
+                         "r"(batch[k].x), "r"(batch[k].y), "r"(batch[k].z), "r"(batch[k].w) : "memory");
+            if (ch + (uint32_t)(kSwitchBatch + k) * grid < hot_end)
+              batch[k] = multicast_sum(mc_grad + (size_t)(base + (uint32_t)(kSwitchBatch + k) * stride + toff) * 2u, p.grad_dtype);
+          }
+        }
+        if (fill_ch < hot_end) stage_fill<OPT, PDT, ECC_BITS, STATE>(L, p.grad_dtype, fill_base + toff, wr, p.peers, ng, !switch_sum);
         copy_commit();
         fill_ch += grid; fill_base += stride;
         wr += stage_bytes;
@@ -1193,6 +1262,13 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
         }
         Unpacked u;
         bool rare = hot_unpack<false, OPT, PDT, ECC_BITS, STATE>(raw, p.grad_dtype, lut_mw, p.one, u);
+        if (switch_sum) {
+          const uint4 sum = lds128(ring0 + turn * (16u * kThreads) + threadIdx.x * 16u);
+          turn = turn + 1 == kSwitchBatch ? 0u : turn + 1;
+          grad_pairs(sum, sum, p.grad_dtype, u.g);
+          const bool odd = mean_of_sum<false>(u.g, p.grad_dtype, p.peers);
+          rare = rare || odd;
+        }
         if (AUX && ng > 0) {
           const bool odd = merge_peer_grads<false>(u.g, p.grad_dtype, p.peers, [&](int r, uint4& w0, uint4& w1) {
             const uint32_t at = peer_grads + (uint32_t)r * (uint32_t)S::grad_bytes(p.grad_dtype) + threadIdx.x * 16u;
@@ -1319,7 +1395,9 @@ constexpr int kSmemPerSm = 227 * 1024, kSmemReservedPerBlock = 1024;
 
 template <int OPT, int PDT, int ECC_BITS, int STATE>
 cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStream_t s) {
-  const bool aux = p_in.peers.ng > 0 || p_in.sq_norm != nullptr;
+  const bool aux = p_in.peers.ng > 0 || p_in.sq_norm != nullptr || p_in.peers.mc_pdelta != 0 || p_in.peers.mc_gdelta != 0;
+  const bool switch_sum = p_in.peers.mc_gdelta != 0 && p_in.grad_dtype != FO_F32;
+  const int ring_bytes = switch_sum ? kSwitchBatch * 16 * kThreads : 0;
   auto kernel = aux ? step_kernel<OPT, PDT, ECC_BITS, STATE, true> : step_kernel<OPT, PDT, ECC_BITS, STATE, false>;
   static int static_smem = -1;  // the same on every device
   if (static_smem < 0) {
@@ -1330,18 +1408,18 @@ cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStre
   }
   // as many stages as fit beside the tables with min_blocks(OPT) blocks on an SM; when the peers'
   // gradient pieces make a stage too large for two of them, with one block on an SM
-  const int per_stage = Stage<OPT, PDT, ECC_BITS, STATE>::bytes(p_in.grad_dtype, p_in.peers.ng);
+  const int per_stage = Stage<OPT, PDT, ECC_BITS, STATE>::bytes(p_in.grad_dtype, switch_sum ? 0 : p_in.peers.ng);
   int blocks_per_sm = min_blocks(OPT);
-  int stages = (kSmemPerSm / blocks_per_sm - kSmemReservedPerBlock - static_smem) / per_stage;
+  int stages = (kSmemPerSm / blocks_per_sm - kSmemReservedPerBlock - static_smem - ring_bytes) / per_stage;
   if (stages < 2) {
     blocks_per_sm = 1;
-    stages = (kSmemPerSm - kSmemReservedPerBlock - static_smem) / per_stage;
+    stages = (kSmemPerSm - kSmemReservedPerBlock - static_smem - ring_bytes) / per_stage;
   }
   static_assert(kMaxStages <= 3, "the plain kernel waits for 2 or 3 stages only");
-  const int max_stages = p_in.peers.ng > 0 ? kMaxStagesPeers : kMaxStages;
+  const int max_stages = (p_in.peers.ng > 0 && !switch_sum) ? kMaxStagesPeers : kMaxStages;
   if (stages > max_stages) stages = max_stages;
   if (stages < 2) return cudaErrorInvalidConfiguration;
-  const int dynamic_smem = stages * per_stage;
+  const int dynamic_smem = stages * per_stage + ring_bytes;
   static bool opted[2][64] = {};  // per kernel and device ordinal: the opt-in above 48 KB belongs to the device's copy of the function
   bool* opted_in = opted[aux ? 1 : 0];
   int dev = 0;

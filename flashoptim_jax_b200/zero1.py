@@ -167,6 +167,12 @@ class Zero1Optimizer:
                 averages them (fp32 sum in rank order starting with its own, one rounding to the
                 gradient dtype) as it goes; a one-element all-reduce before the launch makes sure that
                 every rank's gradients are complete.  Same restrictions.
+    use_switch  route the fused collectives through the NVLink switch where the symmetric allocation has a
+                multicast mapping: parameters leave as one multicast store instead of one store per peer,
+                16-bit gradients arrive as one multicast load-reduce (summed in the switch) instead of one
+                load per peer, so each direction of the links carries the volume of one replica whatever
+                the rank count.  None: when available.  Sums of more than two ranks are then added in the
+                switch's order, not in rank order.
     max_grad_norm
                 clip the (averaged) gradients at this global norm, as optax.clip_by_global_norm in front
                 of the optimizer does (examples/train_gpt2_pretrain.py:56-70): every rank sums the squares
@@ -177,7 +183,7 @@ class Zero1Optimizer:
 
     def __init__(self, optimizer: str, params: Any, *, group=None, step_fn: Optional[StepFn] = None,
                  n_slices: Optional[int] = None, fused_allgather: bool = False, fused_reduce_scatter: bool = False,
-                 max_grad_norm: Optional[float] = None, **hparams):
+                 max_grad_norm: Optional[float] = None, use_switch: Optional[bool] = None, **hparams):
         self.kind = optimizer
         if optimizer not in ("adamw", "adam", "lion", "sgd", "sgdw"):
             raise ValueError(f"unknown optimizer {optimizer!r}")
@@ -230,8 +236,11 @@ class Zero1Optimizer:
             if device.type != "cuda":
                 raise ValueError("max_grad_norm needs CUDA tensors")
             n_slices = 1  # the norm is known only after the last reduce-scatter: nothing to pipeline
+        self.use_switch = use_switch
         self.peer_offsets: List[List[int]] = []
         self.peer_grad_offsets: List[List[int]] = []
+        self.mc_param_offsets: List[int] = []
+        self.mc_grad_offsets: List[int] = []
         self.buckets: List[BucketLayout] = []
         self.flat_params: List[torch.Tensor] = []
         self.flat_grads: List[torch.Tensor] = []
@@ -243,8 +252,8 @@ class Zero1Optimizer:
         grad_views: List[Optional[torch.Tensor]] = [None] * len(leaves)
         for dtype, ids in by_dtype.items():
             layout = plan_bucket(dtype, ids, [leaves[i].numel() for i in ids], self.world_size, n_slices)
-            flat_p = self._alloc_flat(layout.total, dtype, self.fused_allgather, self.peer_offsets)
-            flat_g = self._alloc_flat(layout.total, dtype, self.fused_reduce_scatter, self.peer_grad_offsets)
+            flat_p = self._alloc_flat(layout.total, dtype, self.fused_allgather, self.peer_offsets, self.mc_param_offsets)
+            flat_g = self._alloc_flat(layout.total, dtype, self.fused_reduce_scatter, self.peer_grad_offsets, self.mc_grad_offsets)
             for i, start in zip(ids, layout.starts):
                 n = leaves[i].numel()
                 flat_p[start:start + n].copy_(leaves[i].reshape(-1))
@@ -270,11 +279,12 @@ class Zero1Optimizer:
 
     # ---- construction helpers ---------------------------------------------------------------------
 
-    def _alloc_flat(self, n: int, dtype: torch.dtype, symmetric: bool, offsets: List[List[int]]) -> torch.Tensor:
+    def _alloc_flat(self, n: int, dtype: torch.dtype, symmetric: bool, offsets: List[List[int]], mc_offsets: List[int]) -> torch.Tensor:
         """Flat buffer of a bucket; when a fused collective works on it, a symmetric allocation whose peer
         mappings give the byte offsets from this rank's buffer to every other rank's (appended to `offsets`,
         peers in rank order)."""
         if not symmetric:
+            mc_offsets.append(0)
             return torch.zeros(n, dtype=dtype, device=self.device)
         import torch.distributed._symmetric_memory as symm_mem
 
@@ -284,6 +294,10 @@ class Zero1Optimizer:
         handle = symm_mem.rendezvous(buf, pg.group_name)
         ptrs = list(handle.buffer_ptrs)
         offsets.append([int(ptrs[r]) - int(ptrs[self.rank]) for r in range(self.world_size) if r != self.rank])
+        multicast = int(getattr(handle, "multicast_ptr", 0) or 0)
+        if self.use_switch and not multicast:
+            raise ValueError("use_switch=True, but the symmetric allocation has no multicast mapping on this system")
+        mc_offsets.append(multicast - int(ptrs[self.rank]) if (multicast and self.use_switch is not False) else 0)
         self._symm_handles = getattr(self, "_symm_handles", []) + [handle]
         return buf
 
@@ -469,7 +483,8 @@ class Zero1Optimizer:
                 items = [w for w, (_, _, wb, _) in zip(work, self._static_work) if wb == b]
                 if items:
                     self._step_fn(self.opt_code, items, self.peer_offsets[b] if self.fused_allgather else None,
-                                  self.peer_grad_offsets[b] if self.fused_reduce_scatter else None)
+                                  self.peer_grad_offsets[b] if self.fused_reduce_scatter else None,
+                                  self.mc_param_offsets[b], self.mc_grad_offsets[b])
             self.count += 1
             if self.fused_allgather:
                 # all ranks' kernels are complete: their stores into this replica, their reads of these gradients

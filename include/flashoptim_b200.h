@@ -148,6 +148,19 @@ typedef struct FoStepDesc {
   const double* grad_sq_norm;
   float max_grad_norm;
   uint32_t reserved2;
+  /* The same two exchanges through the NVLink switch (0 = off).  Byte distances from a local
+   * address to the multicast address that maps the same element on every rank (a multicast
+   * object bound to all ranks' buffers, e.g. the multicast pointer of a symmetric allocation).
+   * mc_param_offset: whole aligned chunks store their parameters once through the multicast address
+   * (the switch replicates them to every rank, this one included) instead of once per peer.
+   * mc_grad_offset: for 16-bit gradients, whole aligned chunks read one multicast load-reduce (the
+   * switch adds all ranks' values in fp32 and rounds the sum to grad_dtype) instead of one load per
+   * peer; the mean is that sum divided by (n_peers + 1), rounded to grad_dtype.  For a power-of-two
+   * rank count this equals the single rounding described above whenever the order of the additions
+   * does not matter (two ranks; equal gradients); otherwise the switch's order applies.
+   * Both need the matching point-to-point table as well, which serves ragged ends and rare values. */
+  int64_t mc_param_offset;
+  int64_t mc_grad_offset;
 } FoStepDesc;
 #define FO_MAX_PEERS 7
 

@@ -60,7 +60,7 @@ def test_one_rank_equals_plain_step():
             assert a.dtype == b.dtype and torch.equal(a.cpu(), b.cpu())
 
 
-def _worker(rank, world, port, out, mode="nccl", own_grads=False):
+def _worker(rank, world, port, out, mode="nccl", own_grads=False, use_switch=None):
     import torch
     import torch.distributed as dist
 
@@ -75,7 +75,9 @@ def _worker(rank, world, port, out, mode="nccl", own_grads=False):
         # nccl: three slices exercise the pipelined NCCL path; fused_ag: all-gather by peer stores inside the
         # kernel; fused: reduce-scatter by peer loads inside the kernel as well
         z = Zero1Optimizer("adamw", _params(dev), n_slices=3 if mode == "nccl" else 1, fused_allgather=mode != "nccl",
-                           fused_reduce_scatter=mode == "fused", **HP)
+                           fused_reduce_scatter=mode == "fused", use_switch=use_switch, **HP)
+        if use_switch is False:
+            assert not any(z.mc_param_offsets) and not any(z.mc_grad_offsets)
         for t in range(3):
             z.step(_grads(t + (100 * rank if own_grads else 0), dev))
         torch.cuda.synchronize()
@@ -169,3 +171,26 @@ def test_one_rank_with_max_grad_norm_equals_the_clipping_wrapper():
     for t in range(3):
         plain.step(_grads(t, dev))
     assert any(not torch.equal(a, b) for a, b in zip(tree.tree_leaves(z.params), tree.tree_leaves(plain.params)))  # the clip did bite
+
+
+def test_two_ranks_point_to_point_only(tmp_path):
+    """The fused collectives without the switch (use_switch=False): same bits."""
+    import torch
+    import torch.multiprocessing as mp
+
+    from flashoptim_jax_b200 import tree
+    from flashoptim_jax_b200.zero1 import Zero1Optimizer
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    dev = torch.device("cuda", 0)
+    single = Zero1Optimizer("adamw", _params(dev), **HP)
+    for t in range(3):
+        g0, g1 = _grads(t, dev), _grads(t + 100, dev)
+        single.step(tree.tree_map(lambda a, b: ((a.float() + b.float()) * 0.5).to(a.dtype), g0, g1))
+    want_p = [p.cpu() for p in tree.tree_leaves(single.params)]
+    out = str(tmp_path / "r0.pt")
+    mp.spawn(_worker, args=(2, _free_port(), out, "fused", True, False), nprocs=2, join=True)
+    got = torch.load(out, weights_only=False)
+    for a, b in zip(got["params"], want_p):
+        assert torch.equal(a, b)

@@ -29,7 +29,7 @@ def test_library_loads_and_exports_every_declared_symbol():
 def test_struct_sizes_match_the_header_layout():
     assert ctypes.sizeof(_lib.FoHyper) == 48
     assert ctypes.sizeof(_lib.FoLeaf) == 72
-    assert ctypes.sizeof(_lib.FoStepDesc) == 96
+    assert ctypes.sizeof(_lib.FoStepDesc) == 112
 
 
 def test_fo_step_rejects_bad_descriptors_without_touching_a_gpu():
