@@ -293,6 +293,8 @@ class Zero1Optimizer:
         pg = self.group if self.group is not None else dist.group.WORLD
         handle = symm_mem.rendezvous(buf, pg.group_name)
         ptrs = list(handle.buffer_ptrs)
+        if int(ptrs[self.rank]) != buf.data_ptr():
+            raise RuntimeError("symmetric allocation: the local mapping is not the tensor's address; peer offsets would be wrong")
         offsets.append([int(ptrs[r]) - int(ptrs[self.rank]) for r in range(self.world_size) if r != self.rank])
         multicast = int(getattr(handle, "multicast_ptr", 0) or 0)
         if self.use_switch and not multicast:
