@@ -249,7 +249,7 @@ def run_ours(args):
 
     zero = Zero1Optimizer("adamw", params, step_fn=counting_launch, fused_allgather=(world > 1 and not args.nccl_allgather),
                           fused_reduce_scatter=(world > 1 and not args.nccl_reduce_scatter and args.clip is None),
-                          max_grad_norm=args.clip, n_slices=args.slices, use_switch=False if args.no_switch else None, **HPARAMS)
+                          max_grad_norm=args.clip, n_slices=args.slices, use_switch=args.switch, **HPARAMS)
     del params
     torch.cuda.empty_cache()
     ggen = torch.Generator(device=device)
@@ -413,8 +413,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (used for ncu captures)")
     ap.add_argument("--nccl-allgather", action="store_true", help="N > 1: NCCL all-gather after the step instead of peer stores inside it")
-    ap.add_argument("--no-switch", action="store_true",
-                    help="N > 1: fused collectives over point-to-point peer accesses only (no multicast through the NVLink switch)")
+    ap.add_argument("--switch", action="store_true",
+                    help="N > 1: fused collectives through the NVLink switch (multicast store, multicast load-reduce); "
+                         "off by default: the switch's bf16 addition is not round-to-nearest, so parity with the reference is lost")
     ap.add_argument("--slices", type=int, default=None,
                     help="N > 1 with both NCCL collectives: slices per bucket whose reduce-scatter / step / all-gather overlap")
     ap.add_argument("--clip", type=float, default=None,

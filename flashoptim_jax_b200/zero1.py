@@ -167,12 +167,14 @@ class Zero1Optimizer:
                 averages them (fp32 sum in rank order starting with its own, one rounding to the
                 gradient dtype) as it goes; a one-element all-reduce before the launch makes sure that
                 every rank's gradients are complete.  Same restrictions.
-    use_switch  route the fused collectives through the NVLink switch where the symmetric allocation has a
-                multicast mapping: parameters leave as one multicast store instead of one store per peer,
-                16-bit gradients arrive as one multicast load-reduce (summed in the switch) instead of one
-                load per peer, so each direction of the links carries the volume of one replica whatever
-                the rank count.  None: when available.  Sums of more than two ranks are then added in the
-                switch's order, not in rank order.
+    use_switch  route the fused collectives through the NVLink switch (the symmetric allocations' multicast
+                mappings): parameters leave as one multicast store instead of one store per peer, 16-bit
+                gradients arrive as one multicast load-reduce instead of one load per peer, so each
+                direction of the links carries about one replica's volume whatever the rank count (a gain
+                from four ranks on; with two ranks the switch only adds traffic).  Off by default because
+                the switch's bf16 / fp16 addition is not IEEE round-to-nearest (measured: one in five
+                two-rank sums differs from the correctly rounded one in the last place), so results are
+                no longer bit-identical to the reference arithmetic unless all ranks hold equal gradients.
     max_grad_norm
                 clip the (averaged) gradients at this global norm, as optax.clip_by_global_norm in front
                 of the optimizer does (examples/train_gpt2_pretrain.py:56-70): every rank sums the squares
@@ -183,7 +185,7 @@ class Zero1Optimizer:
 
     def __init__(self, optimizer: str, params: Any, *, group=None, step_fn: Optional[StepFn] = None,
                  n_slices: Optional[int] = None, fused_allgather: bool = False, fused_reduce_scatter: bool = False,
-                 max_grad_norm: Optional[float] = None, use_switch: Optional[bool] = None, **hparams):
+                 max_grad_norm: Optional[float] = None, use_switch: bool = False, **hparams):
         self.kind = optimizer
         if optimizer not in ("adamw", "adam", "lion", "sgd", "sgdw"):
             raise ValueError(f"unknown optimizer {optimizer!r}")
@@ -299,7 +301,7 @@ class Zero1Optimizer:
         multicast = int(getattr(handle, "multicast_ptr", 0) or 0)
         if self.use_switch and not multicast:
             raise ValueError("use_switch=True, but the symmetric allocation has no multicast mapping on this system")
-        mc_offsets.append(multicast - int(ptrs[self.rank]) if (multicast and self.use_switch is not False) else 0)
+        mc_offsets.append(multicast - int(ptrs[self.rank]) if self.use_switch else 0)
         self._symm_handles = getattr(self, "_symm_handles", []) + [handle]
         return buf
 
