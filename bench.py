@@ -395,6 +395,10 @@ def finish(args, world, rank, shapes, total_params, value, ms_per_step, roofline
             # (reduce-scatter) and of the parameters out (all-gather), and the same amounts the other way
             # for the peers.  770 GB/s: peer copy per direction measured on this pool.
             per_direction = link_bytes * (world - 1) / world
+            if any(zero_info["mc"]):
+                # through the switch: every gradient leaves once (the switch adds), the reduced slice comes in;
+                # the parameter slice leaves once (the switch replicates), every replica's full copy comes in
+                per_direction = (link_bytes / 2) * (1 + 1 / world)
             achieved = per_direction / (ms_per_step * 1e-3) / 1e9
             line["nvlink"] = {"bytes_per_direction_per_gpu": per_direction, "achieved": achieved, "peak": 770.0, "unit": "GB/s",
                               "frac": achieved / 770.0, "floor_ms": per_direction / 770e9 * 1e3}
