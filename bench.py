@@ -327,30 +327,33 @@ def measure_e2e(args, zero, device, ggen, world, barrier, total_params):
     from flashoptim_jax_b200 import tree as pytree
 
     e2e_steps = max(1, min(args.steps, 2))
-    stage_elems = 1 << 28
-    stage = torch.empty(stage_elems, dtype=torch.bfloat16, pin_memory=True)
-    stage.copy_((torch.randn(stage_elems, device=device, generator=ggen) * 1e-4).to(torch.bfloat16).cpu())
-    stage32 = torch.full((4096,), 1e-4, dtype=torch.float32).pin_memory()
     grad_leaves = pytree.tree_leaves(zero.grads)
+    # pinned host gradients: every leaf is a window of one staging buffer (the values repeat; 16 GB of
+    # pinned memory per rank would be needed otherwise), fp32 norm leaves of a small one
+    stage_elems = max(1 << 28, max(g.numel() for g in grad_leaves))
+    stage = torch.empty(stage_elems, dtype=torch.bfloat16, pin_memory=True)
+    fill = 1 << 26
+    for lo in range(0, stage_elems, fill):
+        m = min(fill, stage_elems - lo)
+        stage[lo:lo + m].copy_((torch.randn(m, device=device, generator=ggen) * 1e-4).to(torch.bfloat16).cpu())
+    stage32 = torch.full((max(g.numel() for g in grad_leaves if g.dtype == torch.float32),), 1e-4, dtype=torch.float32).pin_memory()
+    host_leaves, off = [], 0
+    for g in grad_leaves:
+        n = g.numel()
+        if g.dtype == torch.float32:
+            host_leaves.append(stage32[:n].view(g.shape))
+            continue
+        if off + n > stage_elems:
+            off = 0
+        host_leaves.append(stage[off:off + n].view(g.shape))
+        off += n
+    host_grads = pytree.tree_unflatten(pytree.tree_structure(zero.grads), host_leaves)
     h2d = sum(g.numel() * g.element_size() for g in grad_leaves)
     probe = torch.empty(1, dtype=torch.float32).pin_memory()
     first_param = pytree.tree_leaves(zero.params)[0].view(-1)
 
     def e2e_step():
-        off = 0
-        for g in grad_leaves:  # host -> device copy of this step's gradients
-            flat = g.view(-1)
-            n = flat.numel()
-            if g.dtype == torch.float32:
-                flat.copy_(stage32[:n], non_blocking=True)
-                continue
-            done = 0
-            while done < n:
-                take = min(n - done, stage_elems - off)
-                flat[done:done + take].copy_(stage[off:off + take], non_blocking=True)
-                done += take
-                off = (off + take) % stage_elems
-        zero.step()
+        zero.step_from_host(host_grads)  # host -> device copies of this step's gradients, overlapped with the step on one rank
         probe.copy_(first_param[:1].float(), non_blocking=True)  # device -> host read of a result
         torch.cuda.current_stream().synchronize()
 

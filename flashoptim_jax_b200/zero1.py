@@ -450,6 +450,57 @@ class Zero1Optimizer:
         for handle in ag:
             handle.wait()
 
+    def step_from_host(self, host_grads: Any, n_groups: int = 8) -> Any:
+        """One optimizer step on gradients that live in (pinned) host memory.  On a single rank without
+        clipping the leaves are cut into `n_groups` groups of about equal size; the host-to-device copy
+        of a group runs on a copy stream while the step of the group before it runs, so the step hides
+        behind the transfer.  Otherwise (several ranks, clipping: the whole gradient must be there first)
+        it is a copy followed by `step()`.  Same result either way.  Returns `self.params`."""
+        leaves, treedef = pytree.tree_flatten(host_grads)
+        if treedef != self.treedef:
+            raise ValueError(f"{self.name} gradients must match parameter structure")
+        mine = pytree.tree_leaves(self.grads)
+        if self.world_size > 1 or self.max_grad_norm is not None or self.device.type != "cuda":
+            for dst, src in zip(mine, leaves):
+                dst.copy_(as_tensor(src).reshape(dst.shape), non_blocking=True)
+            return self.step()
+        work = self.local_work()  # one item per leaf on a single rank
+        by_leaf: Dict[int, eng.LeafWork] = {leaf: w for w, (_, leaf, _, _) in zip(work, self._static_work)}
+        total = sum(t.numel() * t.element_size() for t in mine)
+        main = torch.cuda.current_stream(self.device)
+        if getattr(self, "_copy_stream", None) is None:
+            self._copy_stream = torch.cuda.Stream(self.device)
+        copier = self._copy_stream
+        copier.wait_stream(main)  # the previous step has finished reading the gradient buffers
+        group: List[int] = []
+        acc, share = 0, total / max(1, n_groups)
+        order = list(range(len(mine)))
+
+        def flush():
+            nonlocal group
+            if not group:
+                return
+            with torch.cuda.stream(copier):
+                for i in group:
+                    mine[i].copy_(as_tensor(leaves[i]).reshape(mine[i].shape), non_blocking=True)
+                done = torch.cuda.Event()
+                done.record(copier)
+            main.wait_event(done)
+            items = [by_leaf[i] for i in group if i in by_leaf]
+            if items:
+                self._step_fn(self.opt_code, items)
+            group = []
+
+        for i in order:
+            group.append(i)
+            acc += mine[i].numel() * mine[i].element_size()
+            if acc >= share:
+                flush()
+                acc = 0
+        flush()
+        self.count += 1
+        return self.params
+
     def step(self, grads: Any = None) -> Any:
         """One optimizer step.  `grads` (optional) is copied into the flat gradient buffers;
         leave it out when backward already wrote into `self.grads`.  Returns `self.params`."""

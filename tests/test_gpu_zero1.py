@@ -202,3 +202,25 @@ def test_two_ranks_through_the_switch_with_equal_gradients(tmp_path):
         assert torch.equal(a, b)
     for a, b in zip(got["state"], want_s):
         assert a.dtype == b.dtype and torch.equal(a, b)
+
+
+def test_step_from_host_equals_step():
+    import torch
+
+    from flashoptim_jax_b200 import tree
+    from flashoptim_jax_b200.zero1 import Zero1Optimizer
+
+    dev = torch.device("cuda", 0)
+    a = Zero1Optimizer("adamw", _params(dev), **HP)
+    b = Zero1Optimizer("adamw", _params(dev), **HP)
+    for t in range(3):
+        g = _grads(t, dev)
+        host = tree.tree_map(lambda x: x.cpu().pin_memory(), g)
+        a.step(g)
+        b.step_from_host(host, n_groups=3)
+    torch.cuda.synchronize()
+    assert b.count == 3
+    for x, y in zip(tree.tree_leaves(a.params), tree.tree_leaves(b.params)):
+        assert torch.equal(x, y)
+    for x, y in zip(tree.tree_leaves(a.gather_state()), tree.tree_leaves(b.gather_state())):
+        assert torch.equal(torch.as_tensor(x), torch.as_tensor(y))
