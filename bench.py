@@ -247,9 +247,18 @@ def run_ours(args):
         launches[0] += n
         return n
 
-    zero = Zero1Optimizer("adamw", params, step_fn=counting_launch, fused_allgather=(world > 1 and not args.nccl_allgather),
-                          fused_reduce_scatter=(world > 1 and not args.nccl_reduce_scatter and args.clip is None),
-                          max_grad_norm=args.clip, n_slices=args.slices, use_switch=args.switch, **HPARAMS)
+    fused = {"fused_allgather": world > 1 and not args.nccl_allgather,
+             "fused_reduce_scatter": world > 1 and not args.nccl_reduce_scatter and args.clip is None}
+    try:
+        zero = Zero1Optimizer("adamw", params, step_fn=counting_launch, max_grad_norm=args.clip, n_slices=args.slices,
+                              use_switch=args.switch, **fused, **HPARAMS)
+    except Exception as e:  # no peer-mapped (symmetric) memory on this system: every rank fails alike
+        if not any(fused.values()):
+            raise
+        print(f"fused collectives unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+        args.nccl_allgather = args.nccl_reduce_scatter = True
+        args.switch = False
+        zero = Zero1Optimizer("adamw", params, step_fn=counting_launch, max_grad_norm=args.clip, n_slices=args.slices, **HPARAMS)
     del params
     torch.cuda.empty_cache()
     ggen = torch.Generator(device=device)
