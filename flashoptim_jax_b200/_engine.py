@@ -145,13 +145,24 @@ def step_scalars(count: torch.Tensor, learning_rate: Any, b1: float, b2: float, 
     the counter is advanced in place.  The result is what FoHyper.dev_scalars points to."""
     if not (count.is_cuda and count.dtype == torch.int32 and count.numel() == 1):
         raise ValueError("a capturable step keeps `count` as a 0-d int32 CUDA tensor")
+    from .schedules import DeviceSchedule
+
+    if isinstance(learning_rate, DeviceSchedule):  # evaluated on the device at the zero-based count (adamw.py:526)
+        out = torch.empty(3, dtype=torch.float32, device=count.device)
+        params = (ctypes.c_float * 3)(*learning_rate.device_params())
+        with torch.cuda.device(count.device):
+            _lib.check(_lib.lib().fo_step_scalars_schedule(count.data_ptr(), learning_rate.kind, params, float(b1), float(b2),
+                                                           out.data_ptr(), count.data_ptr() if write_count else 0,
+                                                           stream_ptr(count.device)))
+        return out
     lr_ptr, lr_const = 0, 0.0
     if isinstance(learning_rate, torch.Tensor):
         if not (learning_rate.is_cuda and learning_rate.dtype == torch.float32 and learning_rate.numel() == 1):
             raise ValueError("a tensor learning rate must be a 0-d float32 CUDA tensor")
         lr_ptr = learning_rate.data_ptr()
     elif callable(learning_rate):
-        raise ValueError("a capturable step cannot call a schedule on the host: pass a CUDA tensor and update it yourself")
+        raise ValueError("a capturable step cannot call a schedule on the host: pass a schedule from "
+                         "flashoptim_jax_b200.schedules, or a CUDA tensor that you update yourself")
     else:
         lr_const = float(learning_rate)
     out = torch.empty(3, dtype=torch.float32, device=count.device)

@@ -27,7 +27,7 @@ FO_SELFTEST_GROUP_DIV, FO_SELFTEST_CODE_TABLES, FO_SELFTEST_RCP, FO_SELFTEST_PAC
 EXPORTS = (
     "fo_step", "fo_quantize_momentum", "fo_dequantize_momentum", "fo_quantize_variance",
     "fo_dequantize_variance", "fo_split", "fo_reconstruct", "fo_selftest", "fo_selftest_static", "fo_version",
-    "fo_status_string", "fo_last_error", "fo_sq_norm", "fo_step_scalars",
+    "fo_status_string", "fo_last_error", "fo_sq_norm", "fo_step_scalars", "fo_step_scalars_schedule",
 )
 FO_SQ_NORM_WORKSPACE_BYTES = 16384
 
@@ -115,6 +115,8 @@ def lib() -> ctypes.CDLL:
     cdll.fo_sq_norm.argtypes = [ctypes.POINTER(FoArray), ctypes.c_uint32, i32, i32, vp, vp, vp]
     cdll.fo_step_scalars.restype = ctypes.c_int
     cdll.fo_step_scalars.argtypes = [vp, vp, ctypes.c_float, ctypes.c_float, ctypes.c_float, vp, vp, vp]
+    cdll.fo_step_scalars_schedule.restype = ctypes.c_int
+    cdll.fo_step_scalars_schedule.argtypes = [vp, i32, ctypes.POINTER(ctypes.c_float), ctypes.c_float, ctypes.c_float, vp, vp, vp]
     cdll.fo_version.restype = ctypes.c_int
     cdll.fo_version.argtypes = []
     cdll.fo_status_string.restype = ctypes.c_char_p

@@ -97,6 +97,27 @@ __global__ void step_scalars_kernel(const int32_t* count, const float* lr_dev, f
   if (count_out != nullptr) *count_out = c;
 }
 
+// examples/example_utils.py:94-103, one fp32 rounding per written operation
+FO_DEVI float warmup_cosine(float step, float total, float warmup, float peak) {
+  if (warmup > 0.0f && step < warmup) return fdiv(fmul(peak, fadd(step, 1.0f)), warmup);
+  const float span = fmaxf(1.0f, fsub(total, warmup));
+  const float progress = fminf(fmaxf(fdiv(fsub(step, warmup), span), 0.0f), 1.0f);
+  const float c = (float)cos((double)fmul(3.14159274101257324f, progress));  // f32(pi) * progress, as jnp.pi * progress
+  return fmul((float)((double)peak * 0.5), fadd(1.0f, c));
+}
+
+__global__ void step_scalars_schedule_kernel(const int32_t* count, int32_t schedule, float p0, float p1, float p2, float b1, float b2,
+                                             float* out3, int32_t* count_out) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const int32_t before = *count, c = before + 1;
+  float lr = 0.0f;
+  if (schedule == FO_SCHEDULE_WARMUP_COSINE) lr = warmup_cosine((float)before, p0, p1, p2);
+  out3[0] = lr;
+  out3[1] = fsub(1.0f, (float)pow((double)b1, (double)c));
+  out3[2] = fsub(1.0f, (float)pow((double)b2, (double)c));
+  if (count_out != nullptr) *count_out = c;
+}
+
 }  // namespace fo
 
 using namespace fo;
@@ -160,5 +181,15 @@ extern "C" int fo_step_scalars(const int32_t* count, const float* lr_dev, float 
   step_scalars_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(count, lr_dev, lr_const, b1, b2, out3, count_out);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(FO_ERR_CUDA, "fo_step_scalars: launch failed: %s", cudaGetErrorString(e));
+  return FO_OK;
+}
+
+extern "C" int fo_step_scalars_schedule(const int32_t* count, int32_t schedule, const float* p, float b1, float b2, float* out3,
+                                        int32_t* count_out, void* cuda_stream) {
+  if (count == nullptr || out3 == nullptr || p == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_step_scalars_schedule: null argument");
+  if (schedule != FO_SCHEDULE_WARMUP_COSINE) return fail(FO_ERR_INVALID_ARG, "fo_step_scalars_schedule: unknown schedule %d", schedule);
+  step_scalars_schedule_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(count, schedule, p[0], p[1], p[2], b1, b2, out3, count_out);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(FO_ERR_CUDA, "fo_step_scalars_schedule: launch failed: %s", cudaGetErrorString(e));
   return FO_OK;
 }

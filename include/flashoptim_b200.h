@@ -177,6 +177,17 @@ int fo_step(const FoStepDesc* desc, void* cuda_stream);
 int fo_step_scalars(const int32_t* count, const float* lr_dev, float lr_const, float b1, float b2, float* out3,
                     int32_t* count_out, void* cuda_stream);
 
+/* The same with the learning rate taken from a schedule evaluated on the device at the zero-based
+ * step *count (adamw.py:526 passes the count before its increment to the schedule).
+ * FO_SCHEDULE_WARMUP_COSINE restates make_warmup_cosine_schedule of the reference's examples
+ * (examples/example_utils.py:94-103) in fp32, p = host array {total_steps, warmup_steps, peak_lr}:
+ *   step < warmup:  peak * (step + 1) / warmup
+ *   else:           f32(peak * 0.5) * (1 + cos(pi * clip((step - warmup) / max(1, total - warmup), 0, 1)))
+ * with the cosine taken in float64 and rounded once (XLA's fp32 cos may differ in the last place). */
+#define FO_SCHEDULE_WARMUP_COSINE 1
+int fo_step_scalars_schedule(const int32_t* count, int32_t schedule, const float* p, float b1, float b2, float* out3,
+                             int32_t* count_out, void* cuda_stream);
+
 /* Sum of squares of a list of device arrays of one dtype (the gradient pytree, or one dtype
  * bucket of it), for global-norm clipping (optax.global_norm as used through
  * examples/train_gpt2_pretrain.py:58): squares exact in fp32, summed in fp32 over short runs and

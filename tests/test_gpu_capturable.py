@@ -110,3 +110,31 @@ def test_capturable_lion_and_sgd_equal_the_host_scalar_steps(name, kw):
     for field in ("mu", "ecc"):
         for a, b in zip(tree.tree_leaves(getattr(state, field)), tree.tree_leaves(getattr(plain_state, field))):
             assert torch.equal(torch.as_tensor(a), torch.as_tensor(b))
+
+
+def test_device_schedule_equals_its_host_formula_and_drives_a_capturable_step():
+    import torch
+
+    import flashoptim_jax_b200 as fo
+    from flashoptim_jax_b200 import _engine as eng
+    from flashoptim_jax_b200 import tree
+    from flashoptim_jax_b200.schedules import warmup_cosine
+
+    sched = warmup_cosine(total_steps=400, warmup_steps=37, peak_lr=3e-4)
+    count = torch.zeros((), dtype=torch.int32, device="cuda")
+    outs = [eng.step_scalars(count, sched, 0.9, 0.999, write_count=True) for _ in range(450)]
+    got = torch.stack(outs).cpu().numpy()[:, 0]
+    want = np.array([sched(c) for c in range(450)], dtype=np.float32)  # the schedule sees the zero-based count
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+    # the same schedule on the host (called with the count) and on the device (capturable) give the same steps
+    host_tx = fo.flash_adamw(learning_rate=sched, master_weight_bits=32, donate=True)
+    dev_tx = fo.flash_adamw(learning_rate=sched, master_weight_bits=32, donate=True, capturable=True)
+    hp, dp = _tree(0, 0.02), _tree(0, 0.02)
+    hs, ds = host_tx.init(hp), dev_tx.init(dp)
+    for t in range(4):
+        hp, hs = host_tx.step(hp, hs, _tree(100 + t, 1e-3))
+        dp, ds = dev_tx.step(dp, ds, _tree(100 + t, 1e-3))
+    torch.cuda.synchronize()
+    for a, b in zip(tree.tree_leaves(hp), tree.tree_leaves(dp)):
+        assert torch.equal(a, b)

@@ -5,6 +5,7 @@ import ctypes
 import os
 import re
 
+import numpy as np
 import pytest
 import torch
 
@@ -194,3 +195,17 @@ def test_schedule_sees_zero_based_counts_and_scalar_helpers():
     assert eng.one_minus(0.9, False) == np.float32(0.1)
     assert eng.one_minus(0.999, True) != eng.one_minus(0.999, False)
     assert eng.bias_correction(0.9, 1) == np.float32(1) - np.float32(0.9)
+
+
+def test_warmup_cosine_schedule_host_formula():
+    # examples/example_utils.py:94-103: linear warm-up to the peak, cosine decay to zero
+    from flashoptim_jax_b200.schedules import warmup_cosine
+
+    s = warmup_cosine(total_steps=100, warmup_steps=10, peak_lr=1e-3)
+    assert s(0) == float(np.float32(np.float32(1e-3) * np.float32(1.0)) / np.float32(10))
+    assert s(9) == float(np.float32(np.float32(1e-3) * np.float32(10.0)) / np.float32(10))  # the peak, at the last warm-up step
+    assert s(10) == float(np.float32(np.float32(0.5e-3) * np.float32(2.0)))              # progress 0: cos = 1
+    assert abs(s(55) - 0.5e-3) < 1e-9                                                    # half way: cos = 0
+    assert abs(s(100)) < 1e-10 and s(1000) == s(100)                                      # clipped at the end
+    assert warmup_cosine(50, 0, 2e-3)(0) == float(np.float32(np.float32(1e-3) * np.float32(2.0)))  # no warm-up: straight to the cosine
+    assert all(s(t) >= s(t + 1) for t in range(10, 100))
