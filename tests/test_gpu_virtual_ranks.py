@@ -93,3 +93,48 @@ def test_grad_peers_alone_and_argument_errors():
     rc = H.abi_step(C.SGD, [G0], [dev], C.STATE_QUANT, 64, [hp], [0], 1, 1, 16, expect_ok=False,
                     peer_grad_offsets=[G1.data_ptr() - G0.data_ptr()])
     assert rc == 2
+
+
+@pytest.mark.parametrize("world,gdt", [(2, 1), (4, 1), (3, 0)])
+def test_virtual_ranks_with_global_norm_clipping(world, gdt):
+    """Averaging over the ranks and clipping in the same launch: the mean is formed first, the clip acts on it
+    (the sum of squares is that of the mean gradients of all slices, as a sharded caller would all-reduce it)."""
+    import torch
+
+    from flashoptim_jax_b200 import _engine as eng
+
+    rng = np.random.default_rng(40 + world)
+    g_np = {0: np.float32, 1: ml_dtypes.bfloat16}[gdt]
+    per = 3 * 2048 + 5 * 32
+    n = per * world - 9
+    lo = [k * per for k in range(world)]
+    hi = [min(n, (k + 1) * per) for k in range(world)]
+    p0 = rng.normal(0, 0.05, n).astype(np.float32).astype(ml_dtypes.bfloat16)
+    refs = [H.fresh_leaf(p0[lo[k]:hi[k]].copy(), C.ADAM, C.STATE_QUANT, 16) for k in range(world)]
+    P = [H.to_torch(p0.copy()) for _ in range(world)]
+    G = [torch.zeros(n, dtype=torch.float32 if gdt == 0 else torch.bfloat16, device="cuda") for _ in range(world)]
+    devs = []
+    for k in range(world):
+        st = H.fresh_leaf(p0[lo[k]:hi[k]].copy(), C.ADAM, C.STATE_QUANT, 16).to_device()
+        st.param = P[k][lo[k]:hi[k]]
+        devs.append(st)
+    for t in range(2):
+        gs = [H.make_grad(rng, n, 2e-2, g_np) for _ in range(world)]
+        means = [_mean_grad([g[lo[k]:hi[k]] for g in gs], k, g_np) for k in range(world)]
+        sq = eng.sq_norm_of([H.to_torch(m) for m in means])
+        sq_host = float(sq.cpu())
+        assert np.float32(np.sqrt(sq_host)) > np.float32(0.5)  # the clip bites
+        hp = H.hyper_tuple(C.ADAM, O.FUSED, t + 1, lr=1e-2, wd=1e-2)
+        for k, g in enumerate(O.clip_by_global_norm(means, 0.5, sq_norm=sq_host)):
+            H.oracle_step(C.ADAM, g, refs[k], C.STATE_QUANT, 32, hp)
+        for k in range(world):
+            G[k].copy_(H.to_torch(gs[k]))
+        for k in range(world):
+            others = [j for j in range(world) if j != k]
+            H.abi_step(C.ADAM, [G[k][lo[k]:hi[k]]], [devs[k]], C.STATE_QUANT, 32, [hp], [0], 1, gdt, 16,
+                       peer_param_offsets=[P[j].data_ptr() - P[k].data_ptr() for j in others],
+                       peer_grad_offsets=[G[j].data_ptr() - G[k].data_ptr() for j in others],
+                       grad_sq_norm=sq, max_grad_norm=0.5)
+        torch.cuda.synchronize()
+    for k in range(world):
+        H.assert_leaf_equal(devs[k].to_host(), refs[k], f"rank {k} slice")
