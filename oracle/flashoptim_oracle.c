@@ -4,9 +4,10 @@
  * Same arithmetic as oracle/flashoptim_oracle.py, written as scalar loops over
  * quantization groups so that multi-gigabyte leaves finish in seconds and so that
  * the benchmark has a multi-threaded CPU baseline.  It is validated bit-for-bit
- * against the NumPy oracle by the CPU test-suite.  "Parity unpinned" against a
- * live run of the reference (JAX is not installed where this was written); pinned
- * on the reference tests' known answers through the NumPy oracle.
+ * against the NumPy oracle by the CPU test-suite, and it reproduces bit for bit the
+ * golden vectors that tests/golden/make_golden.py records from the reference's own
+ * source files (imported unmodified over a NumPy stand-in for jax; JAX itself is not
+ * installable where this was written).
  *
  * Build: see oracle/Makefile (gcc -O2 -ffp-contract=off -fno-fast-math -fopenmp).
  * Every fp32 operation below is a single IEEE operation; -ffp-contract=off keeps

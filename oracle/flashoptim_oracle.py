@@ -5,12 +5,15 @@ This module is a NumPy + ml_dtypes restatement of the reference's CPU-runnable
 It exists to check the CUDA library; nothing that ships may import it.  Only the
 tests, the smoke check and the benchmark's CPU-baseline leg use it.
 
-Parity status: the reference is a JAX program and JAX is not installed where this
-oracle was written, so no output of the live reference could be recorded.  The
-oracle is pinned on every exact known-answer the reference's own tests hold for
-this path (rounding ties, exact-bf16 inputs give zero ECC, closed-form single
-steps, state layout); bit-level codes/ECC are pinned by this restatement only —
-"parity unpinned" against a live reference run.
+Parity status: pinned on outputs of the reference's own text.  JAX is not
+installable where this oracle was written, so tests/golden/make_golden.py imports the
+reference's source files unmodified over a NumPy stand-in for the `jax` names they
+use (tests/jax_standin, with a NumPy interpreter for the Pallas kernels) and records
+what the reference's public API returns for both of its texts; this module and its C
+twin reproduce those vectors bit for bit (tests/test_golden.py).  Also pinned on every
+exact known answer the reference's own tests hold (tests/test_oracle_pins.py).  What
+the stand-in cannot show: XLA's own `pow` (bias corrections) and `ldexp` below
+2**-119, and the code Triton generates for the kernels on a GPU.
 
 Numerical contract (every function below keeps it):
   * strict IEEE fp32, one rounding per written operation, evaluated left to

@@ -1,14 +1,29 @@
-"""Generates the golden fixtures in this directory from the NumPy oracle.
+"""Generates the golden fixtures in this directory from the reference's own source files.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py [--reference /path/to/flashoptim-jax] [--check]
 
-The reference is a JAX program and JAX is not installed here, so these vectors come from the
-oracle (the restatement of the reference's code), not from a run of the reference itself.
-They pin the C oracle and the CUDA library against drift; config 1 of the benchmark
-definition (2048x2048 bf16 AdamW, 10 steps) is stored as SHA-256 digests of its final arrays.
+The reference (`flashoptim_jax`) is a JAX program and JAX is not installable here, so this script
+puts `tests/jax_standin` (a NumPy + ml_dtypes stand-in for the `jax` names the reference uses,
+with a NumPy interpreter for its Pallas kernels) on `sys.path`, imports the reference's package
+UNMODIFIED from its checkout, and drives it through its public API: `flash_adamw / flash_lion /
+flash_sgdw(...).init / .step`, `fused=True` (the Pallas kernel text) and `fused=False` (the jnp
+text).  The fixtures are therefore outputs of the reference's text, not of the restatement in
+`oracle/`.
+
+Primitive semantics that are NumPy's rather than XLA's in these vectors (see
+`tests/jax_standin/jax/numpy/__init__.py`): `ldexp` is an exact power-of-two scaling, `**` in the
+bias corrections is NumPy's fp32 `powf` (this script asserts that it equals the float64 power
+rounded once, for every count it uses), float->int casts act on values already clipped to
+range, 16-bit float arithmetic rounds once per operation.  `fused=True` means the kernel text
+under strict IEEE fp32, not Triton's generated code.
+
+`--check` regenerates everything in memory and compares with the committed files instead of
+writing them.
 """
 
+import argparse
 import hashlib
+import io
 import json
 import os
 import sys
@@ -17,74 +32,180 @@ import ml_dtypes
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
-
-from oracle import flashoptim_oracle as O  # noqa: E402
-
+STANDIN = os.path.join(os.path.dirname(HERE), "jax_standin")
 BF16 = np.dtype(ml_dtypes.bfloat16)
 
+HYPER = {
+    "adamw": dict(learning_rate=1e-3, b1=0.9, b2=0.999, eps=1e-8, weight_decay=1e-2),
+    "lion": dict(learning_rate=1e-4, b1=0.9, b2=0.99, weight_decay=1e-2),
+    "sgdw": dict(learning_rate=1e-2, momentum=0.9, weight_decay=1e-2),
+}
 
-def small_case(seed, n, dtype, mwb, opt, conv, steps=3):
+SMALL_CASES = [
+    (2048 + 65, BF16, 24, "adamw", "fused"), (2048 + 65, BF16, 32, "adamw", "unfused"),
+    (1000, np.dtype(np.float16), 32, "adamw", "fused"), (777, BF16, 24, "lion", "fused"),
+    (777, BF16, 24, "lion", "unfused"), (2111, BF16, 32, "sgdw", "fused"),
+    (300, np.dtype(np.float32), None, "adamw", "fused"),
+    (1500, BF16, 24, "sgdw", "unfused"), (1023, np.dtype(np.float16), 24, "lion", "unfused"),
+    (4129, BF16, 24, "adamw", "unfused"), (1031, np.dtype(np.float32), None, "sgdw", "unfused"),
+    (2048, BF16, None, "adamw", "fused"),
+]
+
+
+def import_reference(path):
+    """The reference package, unmodified, on top of the stand-in."""
+    if not os.path.isdir(os.path.join(path, "flashoptim_jax")):
+        raise SystemExit(f"no flashoptim_jax package under {path}")
+    for p in (path, STANDIN):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import jax  # noqa: F401  (the stand-in)
+
+    assert os.path.dirname(os.path.dirname(jax.__file__)) == STANDIN, "a real jax is installed: use it instead"
+    import flashoptim_jax
+
+    assert os.path.dirname(os.path.dirname(os.path.abspath(flashoptim_jax.__file__))) == os.path.abspath(path)
+    return flashoptim_jax
+
+
+def check_pow(betas, counts):
+    """NumPy's fp32 powf against the float64 power rounded once (what oracle and product use)."""
+    for b in betas:
+        for c in counts:
+            got = b ** np.float32(c)
+            want = np.float32(float(np.float32(b)) ** float(c))
+            assert got.dtype == np.float32 and got == want, (b, c, got, want)
+
+
+def make_tx(ref, opt, mwb, convention):
+    kw = dict(HYPER[opt], master_weight_bits=mwb, fused=(convention == "fused"))
+    return {"adamw": ref.flash_adamw, "lion": ref.flash_lion, "sgdw": ref.flash_sgdw}[opt](**kw)
+
+
+def bits(a):
+    a = np.asarray(a)
+    return a.view(np.uint16) if a.dtype.itemsize == 2 and a.dtype.kind not in "iu" else a
+
+
+def small_case(ref, seed, n, dtype, mwb, opt, convention, steps=3):
     rng = np.random.default_rng(seed)
     p = rng.normal(0, 0.02, n).astype(np.float32).astype(dtype)
     grads = [rng.normal(0, 1e-3, n).astype(np.float32).astype(BF16) for _ in range(steps)]
-    out = {"param0": p.view(np.uint16) if p.dtype.itemsize == 2 else p, "grads": np.stack([g.view(np.uint16) for g in grads])}
+    out = {"param0": bits(p), "grads": np.stack([bits(g) for g in grads])}
+    tx = make_tx(ref, opt, mwb, convention)
+    params = {"x": p}
+    state = tx.init(params)
+    for g in grads:
+        params, state = tx.step(params, state, {"x": g})
+    assert int(state.count) == steps
+    out.update(param=bits(params["x"]), mu=np.asarray(state.mu["x"].values), mu_scales=bits(state.mu["x"].scales))
     if opt == "adamw":
-        mu, nu, ecc = O.init_adam_leaf(p, 32, True, mwb)
-        for t, g in enumerate(grads, 1):
-            bc1, bc2 = O.bias_corrections(0.9, 0.999, t)
-            p, ecc, mu, nu = O.adam_leaf(g, p, ecc, mu, nu, lr=1e-3, b1=0.9, b2=0.999, eps=1e-8, weight_decay=1e-2,
-                                         decoupled_weight_decay=True, bias_correction1=bc1, bias_correction2=bc2,
-                                         master_weight_bits=mwb, conv=conv)
-        out.update(nu=nu.values, nu_scales=nu.scales.view(np.uint16))
-    elif opt == "lion":
-        mu, ecc = O.init_momentum_leaf(p, 32, True, mwb)
-        for g in grads:
-            p, ecc, mu = O.lion_leaf(g, p, ecc, mu, lr=1e-4, b1=0.9, b2=0.99, weight_decay=1e-2, master_weight_bits=mwb, conv=conv)
-    else:
-        mu, ecc = O.init_momentum_leaf(p, 32, True, mwb)
-        for g in grads:
-            p, ecc, mu = O.sgd_leaf(g, p, ecc, mu, lr=1e-2, momentum=0.9, dampening=0.0, weight_decay=1e-2, nesterov=False,
-                                    decoupled_weight_decay=True, master_weight_bits=mwb, conv=conv)
-    out.update(param=p.view(np.uint16) if p.dtype.itemsize == 2 else p, mu=mu.values, mu_scales=mu.scales.view(np.uint16))
-    if ecc is not None:
+        out.update(nu=np.asarray(state.nu["x"].values), nu_scales=bits(state.nu["x"].scales))
+    ecc = np.asarray(state.ecc["x"])
+    if ecc.shape != ():
         out["ecc"] = ecc
+    for k, v in out.items():
+        assert v.dtype != np.float64, k
     return out
 
 
-def config1_digests():
-    """BASELINE config 1: one 2048x2048 bf16 matrix N(0, 0.02), grads bf16 N(0, 1e-3), 10 AdamW steps, seed 0."""
-    from oracle import c_oracle as C
-    from tests import helpers as H
-
+def config1_digests(ref):
+    """Benchmark config 1: one 2048x2048 bf16 matrix N(0, 0.02), grads bf16 N(0, 1e-3), 10 AdamW steps,
+    lr 1e-3, betas (0.9, 0.999), eps 1e-8, wd 1e-2, 24-bit master, seed 0; both texts of the reference."""
     digests = {}
-    for conv in (O.FUSED, O.UNFUSED):
+    for convention in ("fused", "unfused"):
         rng = np.random.default_rng(0)
         p = rng.normal(0, 0.02, (2048, 2048)).astype(np.float32).astype(BF16)
-        leaf = H.fresh_leaf(p.reshape(-1), C.ADAM, C.STATE_QUANT, 8)
-        for t in range(1, 11):
-            g = rng.normal(0, 1e-3, 2048 * 2048).astype(np.float32).astype(BF16)
-            H.oracle_step(C.ADAM, g, leaf, C.STATE_QUANT, 32, H.hyper_tuple(C.ADAM, conv, t, lr=1e-3, wd=1e-2))
-        theta = C.reconstruct(leaf.param, leaf.ecc)
-        digests[conv.name] = {f: hashlib.sha256(np.ascontiguousarray(getattr(leaf, f)).tobytes()).hexdigest() for f in leaf.fields()}
-        digests[conv.name]["reconstructed_fp32"] = hashlib.sha256(theta.tobytes()).hexdigest()
+        tx = make_tx(ref, "adamw", 24, convention)
+        params = {"w": p}
+        state = tx.init(params)
+        for _ in range(10):
+            g = rng.normal(0, 1e-3, 2048 * 2048).astype(np.float32).astype(BF16).reshape(2048, 2048)
+            params, state = tx.step(params, state, {"w": g})
+        theta = ref.reconstruct_weights(params, state.ecc)["w"]
+        assert theta.dtype == np.float32
+        arrays = {"param": params["w"], "ecc": state.ecc["w"], "mu": state.mu["w"].values,
+                  "mu_scales": state.mu["w"].scales, "nu": state.nu["w"].values, "nu_scales": state.nu["w"].scales,
+                  "reconstructed_fp32": theta}
+        digests[convention] = {k: hashlib.sha256(np.ascontiguousarray(v).tobytes()).hexdigest() for k, v in arrays.items()}
     return digests
 
 
+def codec_vectors(ref):
+    """Direct calls of the reference's codecs (quantization.py, compression.py) on seeded inputs with
+    exact zeros, an all-zero group, a ragged tail, tiny and huge magnitudes."""
+    rng = np.random.default_rng(77)
+    n = 32 * 40 + 11
+    x = (rng.normal(0, 1, n) * np.exp(rng.uniform(-12, 4, n))).astype(np.float32)
+    x[64:96] = 0
+    x[5] = 0
+    v = np.square(x)
+    qm = ref.quantize_momentum(x, 32)
+    qv = ref.quantize_variance(v, 32)
+    theta = (rng.normal(0, 0.02, n) * np.exp(rng.uniform(-3, 3, n))).astype(np.float32)
+    theta[7] = 0
+    theta[8] = np.float32(2.0 ** -120)  # below the range where JAX's ldexp stays finite; NumPy's is exact
+    out = {"x": x, "v": v, "qm_values": qm.values, "qm_scales": bits(qm.scales), "qv_values": qv.values,
+           "qv_scales": bits(qv.scales), "dqm": ref.dequantize_momentum(qm, 32), "dqv": ref.dequantize_variance(qv, 32),
+           "theta": theta}
+    for tag, dt, mwb in (("bf16_8", BF16, 24), ("bf16_16", BF16, 32), ("f16_8", np.float16, 24), ("f16_16", np.float16, 32)):
+        lp, ecc = ref.split_leaf(theta, narrow_dtype=dt, master_weight_bits=mwb)
+        out[f"lp_{tag}"] = bits(lp)
+        out[f"ecc_{tag}"] = np.asarray(ecc)
+        out[f"recon_{tag}"] = ref.reconstruct_leaf(lp, ecc)
+    return {k: np.asarray(a) for k, a in out.items()}
+
+
+def npz_bytes(arrays):
+    buf = io.BytesIO()
+    np.savez_compressed(buf, **arrays)
+    return buf.getvalue()
+
+
+def same_npz(path, arrays):
+    if not os.path.exists(path):
+        return False
+    z = np.load(path)
+    return sorted(z.files) == sorted(arrays) and all(
+        z[k].dtype == arrays[k].dtype and z[k].shape == arrays[k].shape and np.array_equal(z[k], arrays[k]) for k in arrays)
+
+
 def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default=os.environ.get("FLASHOPTIM_REFERENCE", "/root/reference"))
+    ap.add_argument("--check", action="store_true")
+    args = ap.parse_args()
+    ref = import_reference(args.reference)
+    check_pow((0.9, 0.999), range(1, 11))
+
+    bad = []
     cases = {}
-    for i, (n, dtype, mwb, opt, conv) in enumerate([
-        (2048 + 65, BF16, 24, "adamw", O.FUSED), (2048 + 65, BF16, 32, "adamw", O.UNFUSED),
-        (1000, np.dtype(np.float16), 32, "adamw", O.FUSED), (777, BF16, 24, "lion", O.FUSED),
-        (777, BF16, 24, "lion", O.UNFUSED), (2111, BF16, 32, "sgdw", O.FUSED), (300, np.dtype(np.float32), None, "adamw", O.FUSED),
-    ]):
-        name = f"case{i}_{opt}_{np.dtype(dtype).name}_mwb{mwb}_{conv.name}"
-        np.savez_compressed(os.path.join(HERE, name + ".npz"), **small_case(1000 + i, n, dtype, mwb, opt, conv))
-        cases[name] = {"n": n, "dtype": np.dtype(dtype).name, "master_weight_bits": mwb, "optimizer": opt, "convention": conv.name}
-    with open(os.path.join(HERE, "cases.json"), "w") as f:
-        json.dump(cases, f, indent=1)
-    with open(os.path.join(HERE, "config1_digests.json"), "w") as f:
-        json.dump(config1_digests(), f, indent=1)
+    files = {}
+    for i, (n, dtype, mwb, opt, convention) in enumerate(SMALL_CASES):
+        name = f"case{i}_{opt}_{np.dtype(dtype).name}_mwb{mwb}_{convention}"
+        files[name + ".npz"] = small_case(ref, 1000 + i, n, dtype, mwb, opt, convention)
+        cases[name] = {"n": n, "dtype": np.dtype(dtype).name, "master_weight_bits": mwb, "optimizer": opt,
+                       "convention": convention}
+    files["codecs.npz"] = codec_vectors(ref)
+    for fname, arrays in files.items():
+        path = os.path.join(HERE, fname)
+        if args.check:
+            if not same_npz(path, arrays):
+                bad.append(fname)
+        else:
+            with open(path, "wb") as f:
+                f.write(npz_bytes(arrays))
+    for fname, obj in (("cases.json", cases), ("config1_digests.json", config1_digests(ref))):
+        path = os.path.join(HERE, fname)
+        if args.check:
+            if not os.path.exists(path) or json.load(open(path)) != obj:
+                bad.append(fname)
+        else:
+            with open(path, "w") as f:
+                json.dump(obj, f, indent=1)
+    if bad:
+        raise SystemExit("fixtures differ from the reference's output: " + ", ".join(bad))
+    print("checked" if args.check else "written", len(files) + 2, "fixtures")
 
 
 if __name__ == "__main__":
