@@ -829,6 +829,31 @@ FO_DEVI bool clip_grads(float2 (&g)[4], const int gdt, const Clip& c) {
   return rare;
 }
 
+// Addresses of the eight elements a thread owns in the current chunk, one per stream.  Inside a run
+// of consecutive chunks they advance by compile-time constants, so a later chunk's address is this
+// one plus an immediate.
+struct Piece {
+  const char* grad;
+  char* param;
+  char* ecc;
+  char* mu;
+  char* nu;
+  char* msc;  // the group's scale (four lanes share one)
+  char* vsc;
+};
+template <int PDT, int ECC_BITS, int STATE>
+FO_DEVI Piece piece_at(const DevLeaf& L, const int gdt, const uint32_t i0) {
+  Piece a;
+  a.grad = (const char*)L.grad + (size_t)i0 * (gdt == FO_F32 ? 4u : 2u);
+  a.param = (char*)L.param + (size_t)i0 * (PDT == FO_F32 ? 4u : 2u);
+  a.ecc = (char*)L.ecc + (size_t)i0 * (ECC_BITS == 16 ? 2u : 1u);
+  a.mu = (char*)L.mu + (size_t)i0 * (STATE == FO_STATE_FULL ? 4u : 1u);
+  a.nu = (char*)L.nu + (size_t)i0 * (STATE == FO_STATE_FULL ? 4u : 1u);
+  a.msc = (char*)L.mu_scales + (size_t)(i0 >> 5) * 2u;
+  a.vsc = (char*)L.nu_scales + (size_t)(i0 >> 5) * 2u;
+  return a;
+}
+
 FO_DEVI float sign_of(float x);
 
 template <int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
@@ -844,7 +869,7 @@ __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const in
 // untouched rows, padding, zero gradients) redoes that stage with IEEE operations, then stores.
 // The stored bits are those of the IEEE path in every case.
 template <bool REPAIR, int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
-FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base, const float one,
+FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base, const Piece& at, const float one,
                         bool rare, Unpacked& u, const float* lut_mw, const Peers& peers, const Clip* clip) {
   using namespace fast2;
   const float2 one2 = sp(one);
@@ -853,10 +878,6 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
   float2 (&m)[4] = u.m;
   float2 (&v)[4] = u.v;
   float2 nroot[4];  // Adam: -sqrt(second moment)
-  // 32-bit element offsets (one multiply-add per address): the host hands this kernel leaves of
-  // at most 2^31 elements, splitting longer ones
-  const uint32_t i0 = base + threadIdx.x * kPiece;
-  const uint32_t gi = i0 >> 5;
 
   // ---- update --------------------------------------------------------------------------------------
   const bool decoupled = (h.flags & FO_FLAG_DECOUPLED_WD) != 0;
@@ -1045,6 +1066,7 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
   }
 
   // ---- first pass: one decision per warp -----------------------------------------------------------------
+  (void)rare;
   if constexpr (!REPAIR) {
     if (__any_sync(0xFFFFFFFFu, rare)) {
       warm_chunk<OPT, PDT, ECC_BITS, STATE, AUX>(L, h, gdt, base, one, lut_mw, peers, clip);
@@ -1058,40 +1080,42 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
     const float4 lo = make_float4(theta[0].x, theta[0].y, theta[1].x, theta[1].y);
     const float4 hi = make_float4(theta[2].x, theta[2].y, theta[3].x, theta[3].y);
     if (AUX && peers.mc_pdelta != 0) {
-      char* mc = (char*)((float*)L.param + i0) + peers.mc_pdelta;
+      char* mc = at.param + peers.mc_pdelta;
       multicast_store(mc, make_uint4(__float_as_uint(lo.x), __float_as_uint(lo.y), __float_as_uint(lo.z), __float_as_uint(lo.w)));
       multicast_store(mc + 16, make_uint4(__float_as_uint(hi.x), __float_as_uint(hi.y), __float_as_uint(hi.z), __float_as_uint(hi.w)));
     } else {
-      __stcs((float4*)((float*)L.param + i0), lo);
-      __stcs((float4*)((float*)L.param + i0) + 1, hi);
-      store_to_peers(peers, (float4*)((float*)L.param + i0), lo);
-      store_to_peers(peers, (float4*)((float*)L.param + i0) + 1, hi);
+      __stcs((float4*)at.param, lo);
+      __stcs((float4*)at.param + 1, hi);
+      if constexpr (AUX) {
+        store_to_peers(peers, (float4*)at.param, lo);
+        store_to_peers(peers, (float4*)at.param + 1, hi);
+      }
     }
   } else {
     const uint4 w = make_uint4(nw[0], nw[1], nw[2], nw[3]);
     if (AUX && peers.mc_pdelta != 0) {
-      multicast_store((char*)((unsigned short*)L.param + i0) + peers.mc_pdelta, w);
+      multicast_store(at.param + peers.mc_pdelta, w);
     } else {
-      __stcs((uint4*)((unsigned short*)L.param + i0), w);
-      store_to_peers(peers, (uint4*)((unsigned short*)L.param + i0), w);
+      __stcs((uint4*)at.param, w);
+      if constexpr (AUX) store_to_peers(peers, (uint4*)at.param, w);
     }
-    if constexpr (ECC_BITS == 16) __stcs((uint4*)((short*)L.ecc + i0), ecc_out);
-    if constexpr (ECC_BITS == 8) __stcs((uint2*)((signed char*)L.ecc + i0), make_uint2(ecc_out.x, ecc_out.y));
+    if constexpr (ECC_BITS == 16) __stcs((uint4*)at.ecc, ecc_out);
+    if constexpr (ECC_BITS == 8) __stcs((uint2*)at.ecc, make_uint2(ecc_out.x, ecc_out.y));
   }
   if constexpr (STATE == FO_STATE_FULL) {
-    __stcs((float4*)((float*)L.mu + i0), make_float4(m[0].x, m[0].y, m[1].x, m[1].y));
-    __stcs((float4*)((float*)L.mu + i0) + 1, make_float4(m[2].x, m[2].y, m[3].x, m[3].y));
+    __stcs((float4*)at.mu, make_float4(m[0].x, m[0].y, m[1].x, m[1].y));
+    __stcs((float4*)at.mu + 1, make_float4(m[2].x, m[2].y, m[3].x, m[3].y));
     if constexpr (OPT == FO_OPT_ADAM) {
-      __stcs((float4*)((float*)L.nu + i0), make_float4(v[0].x, v[0].y, v[1].x, v[1].y));
-      __stcs((float4*)((float*)L.nu + i0) + 1, make_float4(v[2].x, v[2].y, v[3].x, v[3].y));
+      __stcs((float4*)at.nu, make_float4(v[0].x, v[0].y, v[1].x, v[1].y));
+      __stcs((float4*)at.nu + 1, make_float4(v[2].x, v[2].y, v[3].x, v[3].y));
     }
   } else if constexpr (STATE == FO_STATE_QUANT) {
     const bool writer = (threadIdx.x & 3) == 0;
-    __stcs((uint2*)((signed char*)L.mu + i0), mq);
-    if (writer) ((__half*)L.mu_scales)[gi] = __float2half_rn(am);
+    __stcs((uint2*)at.mu, mq);
+    if (writer) *(__half*)at.msc = __float2half_rn(am);
     if constexpr (OPT == FO_OPT_ADAM) {
-      __stcs((uint2*)((unsigned char*)L.nu + i0), vq);
-      if (writer) ((__half*)L.nu_scales)[gi] = __float2half_rn(av);
+      __stcs((uint2*)at.nu, vq);
+      if (writer) *(__half*)at.vsc = __float2half_rn(av);
     }
   }
 }
@@ -1119,7 +1143,131 @@ __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const in
     });
   }
   if (AUX && clip->active) clip_grads<true>(u.g, gdt, *clip);
-  hot_finish<true, OPT, PDT, ECC_BITS, STATE, AUX>(L, h, gdt, base, one, false, u, lut_mw, peers, clip);
+  const Piece at = piece_at<PDT, ECC_BITS, STATE>(L, gdt, base + threadIdx.x * kPiece);
+  hot_finish<true, OPT, PDT, ECC_BITS, STATE, AUX>(L, h, gdt, base, at, one, false, u, lut_mw, peers, clip);
+}
+
+// One block's run of consecutive whole chunks [ch, hot_end) of a leaf, for the kernel without peer or
+// clipping code.  Three stages of compile-time size; the loop body is unrolled three times, so
+// that the stage an iteration reads and the one it fills are fixed, and the thread's addresses
+// move once per three chunks: every access inside is a register plus an immediate.
+template <int OPT, int PDT, int ECC_BITS, int STATE>
+FO_DEVI void hot_run(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t ch, const uint32_t hot_end, const uint32_t stage0,
+                     const float one, const float* lut_mw, const Peers& peers) {
+  using S = Stage<OPT, PDT, ECC_BITS, STATE>;
+  constexpr int kPsz = PDT == FO_F32 ? 4 : 2, kEsz = ECC_BITS == 16 ? 2 : 1;
+  constexpr int kSsz = STATE == FO_STATE_FULL ? 4 : 1;   // bytes per element of a moment stream
+  constexpr uint32_t kSB = (uint32_t)S::bytes(FO_F32, 0);  // room for the widest gradients, whatever they are
+  const uint32_t n_it = hot_end - ch;
+  uint32_t base = ch * (uint32_t)kChunk;
+  uint32_t tid;
+  asm volatile("mov.u32 %0, %%tid.x;" : "=r"(tid));  // read once: otherwise re-read at every use
+  Piece at = piece_at<PDT, ECC_BITS, STATE>(L, gdt, base + tid * kPiece);
+  const uint32_t s16 = stage0 + tid * 16u, s8 = stage0 + tid * 8u;
+  const int gsz = gdt == FO_F32 ? 4 : 2;
+  // copies of the chunk `ahead` chunks after the one `at` points to, into stage `slot`
+  auto fill = [&](const int slot, const int ahead) {
+    const uint32_t o = (uint32_t)slot * kSB;
+    const char* pp = at.param + ahead * (kChunk * kPsz);
+    if constexpr (PDT == FO_F32) {
+      copy_async16_l1(s16 + o, pp);
+      copy_async16_l1(s16 + o + 16u * kThreads, pp + 16);
+    } else {
+      copy_async16(s16 + o, pp);
+    }
+    if constexpr (ECC_BITS == 16) copy_async16(s16 + o + S::kOffEcc, at.ecc + ahead * (kChunk * kEsz));
+    if constexpr (ECC_BITS == 8) copy_async8(s8 + o + S::kOffEcc, at.ecc + ahead * (kChunk * kEsz));
+    if constexpr (STATE == FO_STATE_QUANT) {
+      copy_async8(s8 + o + S::kOffMu, at.mu + ahead * kChunk);
+      if constexpr (OPT == FO_OPT_ADAM) copy_async8(s8 + o + S::kOffNu, at.nu + ahead * kChunk);
+    } else if constexpr (STATE == FO_STATE_FULL) {
+      copy_async16_l1(s16 + o + S::kOffMu, at.mu + ahead * (kChunk * 4));
+      copy_async16_l1(s16 + o + S::kOffMu + 16u * kThreads, at.mu + ahead * (kChunk * 4) + 16);
+      if constexpr (OPT == FO_OPT_ADAM) {
+        copy_async16_l1(s16 + o + S::kOffNu, at.nu + ahead * (kChunk * 4));
+        copy_async16_l1(s16 + o + S::kOffNu + 16u * kThreads, at.nu + ahead * (kChunk * 4) + 16);
+      }
+    }
+    if (gdt == FO_F32) {
+      copy_async16_l1(s16 + o + S::kOffGrad, at.grad + ahead * (kChunk * 4));
+      copy_async16_l1(s16 + o + S::kOffGrad + 16u * kThreads, at.grad + ahead * (kChunk * 4) + 16);
+    } else {
+      copy_async16(s16 + o + S::kOffGrad, at.grad + ahead * (kChunk * 2));
+    }
+  };
+  auto read = [&](const int slot, Raw<OPT, PDT, ECC_BITS, STATE>& r) {
+    const uint32_t o = (uint32_t)slot * kSB;
+    r.p0 = lds128(s16 + o);
+    if constexpr (PDT == FO_F32) r.p1 = lds128(s16 + o + 16u * kThreads);
+    if constexpr (ECC_BITS == 16) r.e = lds128(s16 + o + S::kOffEcc);
+    if constexpr (ECC_BITS == 8) {
+      const uint2 t = lds64(s8 + o + S::kOffEcc);
+      r.e.x = t.x; r.e.y = t.y;
+    }
+    if constexpr (STATE == FO_STATE_QUANT) {
+      r.mq = lds64(s8 + o + S::kOffMu);
+      if constexpr (OPT == FO_OPT_ADAM) r.vq = lds64(s8 + o + S::kOffNu);
+    } else if constexpr (STATE == FO_STATE_FULL) {
+      r.m0 = lds128(s16 + o + S::kOffMu);
+      r.m1 = lds128(s16 + o + S::kOffMu + 16u * kThreads);
+      if constexpr (OPT == FO_OPT_ADAM) {
+        r.v0 = lds128(s16 + o + S::kOffNu);
+        r.v1 = lds128(s16 + o + S::kOffNu + 16u * kThreads);
+      }
+    }
+    r.g0 = lds128(s16 + o + S::kOffGrad);
+    if (gdt == FO_F32) r.g1 = lds128(s16 + o + S::kOffGrad + 16u * kThreads);
+  };
+  if (0u < n_it) fill(0, 0);
+  copy_commit();
+  if (1u < n_it) fill(1, 1);
+  copy_commit();
+  __half msc = __float2half(0.0f), vsc = msc;  // the group scales go through registers, one chunk ahead
+  if constexpr (STATE == FO_STATE_QUANT) {
+    msc = *(const __half*)at.msc;
+    if constexpr (OPT == FO_OPT_ADAM) vsc = *(const __half*)at.vsc;
+  }
+  for (uint32_t it = 0; it < n_it; it += 3u) {
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+      if (it + (uint32_t)k >= n_it) break;
+      if (it + (uint32_t)(k + 2) < n_it) fill((k + 2) % 3, k + 2);
+      copy_commit();
+      copy_wait<2>();
+      Raw<OPT, PDT, ECC_BITS, STATE> raw;
+      read(k, raw);
+      raw.msc = msc; raw.vsc = vsc;
+      if constexpr (STATE == FO_STATE_QUANT) {
+        if (it + (uint32_t)(k + 1) < n_it) {
+          msc = *(const __half*)(at.msc + (k + 1) * (kChunk / 32 * 2));
+          if constexpr (OPT == FO_OPT_ADAM) vsc = *(const __half*)(at.vsc + (k + 1) * (kChunk / 32 * 2));
+        }
+      }
+      Unpacked u;
+      const bool rare = hot_unpack<false, OPT, PDT, ECC_BITS, STATE>(raw, gdt, lut_mw, one, u);
+      Piece cur;
+      cur.grad = at.grad;  // not used by the stores
+      cur.param = at.param + k * (kChunk * kPsz);
+      cur.ecc = at.ecc + k * (kChunk * kEsz);
+      cur.mu = at.mu + k * (kChunk * kSsz);
+      cur.nu = at.nu + k * (kChunk * kSsz);
+      cur.msc = at.msc + k * (kChunk / 32 * 2);
+      cur.vsc = at.vsc + k * (kChunk / 32 * 2);
+      hot_finish<false, OPT, PDT, ECC_BITS, STATE, false>(L, h, gdt, base + (uint32_t)k * kChunk, cur, one, rare, u, lut_mw, peers, nullptr);
+    }
+    base += 3u * (uint32_t)kChunk;
+    at.grad += 3 * kChunk * gsz;
+    at.param += 3 * kChunk * kPsz;
+    if constexpr (ECC_BITS != 0) at.ecc += 3 * kChunk * kEsz;
+    if constexpr (STATE != FO_STATE_NONE) {
+      at.mu += 3 * kChunk * kSsz;
+      if constexpr (OPT == FO_OPT_ADAM) at.nu += 3 * kChunk * kSsz;
+    }
+    if constexpr (STATE == FO_STATE_QUANT) {
+      at.msc += 3 * (kChunk / 32 * 2);
+      if constexpr (OPT == FO_OPT_ADAM) at.vsc += 3 * (kChunk / 32 * 2);
+    }
+  }
 }
 
 // exact dequantization tables, one entry per code byte (built once per block)
@@ -1179,11 +1327,16 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
   // the ring (the sums for this and the next iterations) and issues the next batch.
   const uint32_t ring0 = stage_end;
   const uint32_t toff = threadIdx.x * kPiece;
-  const uint32_t grid = gridDim.x;
   const Clip clip = load_clip(AUX ? p.sq_norm : nullptr, p.max_norm, p.grad_dtype);
-  uint32_t c = blockIdx.x;  // this block's next position in the sequence
+  const uint32_t total = p.first_block[p.n_leaves];
+  const uint32_t per = (total + gridDim.x - 1) / gridDim.x;
+  uint32_t c = blockIdx.x * per;  // this block's next position in the sequence
+  const uint32_t c_hi = min(total, c + per);
+  constexpr uint32_t grid = 1u;   // a block's chunks are consecutive
   for (int l = 0; l < p.n_leaves; ++l) {
-    const uint32_t first = p.first_block[l], next = p.first_block[l + 1];
+    const uint32_t first = p.first_block[l];
+    if (c >= c_hi) break;
+    const uint32_t next = min(p.first_block[l + 1], c_hi);
     if (c >= next) continue;
     const uint32_t end = next - first;  // chunks in this leaf
     uint32_t ch = c - first;            // this block's first chunk inside the leaf
@@ -1192,8 +1345,13 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
     // the CPU-path parameter hand-back (FO_FLAG_LP_DELTA) needs the old stored value to the end: IEEE path only
     bool hyper_ok = (h.flags & FO_FLAG_LP_DELTA) == 0;
     if constexpr (OPT == FO_OPT_ADAM) hyper_ok = hyper_ok && (h.flags & kFlagTameAdam) != 0;  // the reciprocal shortcut in the denominator
-    const uint32_t hot_end = (leaf_is_hot<OPT>(p, l) && hyper_ok) ? (uint32_t)(L.n / kChunk) : 0u;  // whole chunks
-    if (ch < hot_end) {
+    const uint32_t hot_end = (leaf_is_hot<OPT>(p, l) && hyper_ok) ? min(end, (uint32_t)(L.n / kChunk)) : 0u;  // whole chunks
+    if constexpr (!AUX) {
+      if (ch < hot_end) {
+        hot_run<OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, ch, hot_end, stage0, p.one, lut_mw, p.peers);
+        ch = hot_end;
+      }
+    } else if (ch < hot_end) {
       const uint32_t stride = grid * (uint32_t)kChunk;
       uint32_t base = ch * (uint32_t)kChunk;
       // Copy pipeline: one group per chunk (empty past the end of the run, so that the count of
@@ -1281,7 +1439,8 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
           const bool odd = clip_grads<false>(u.g, p.grad_dtype, clip);
           rare = rare || odd;
         }
-        hot_finish<false, OPT, PDT, ECC_BITS, STATE, AUX>(L, h, p.grad_dtype, base, p.one, rare, u, lut_mw, p.peers, AUX ? &clip : nullptr);
+        const Piece at = piece_at<PDT, ECC_BITS, STATE>(L, p.grad_dtype, base + toff);
+        hot_finish<false, OPT, PDT, ECC_BITS, STATE, AUX>(L, h, p.grad_dtype, base, at, p.one, rare, u, lut_mw, p.peers, AUX ? &clip : nullptr);
       }
     }
     for (; ch < end; ch += grid)
@@ -1395,7 +1554,7 @@ constexpr int kSmemPerSm = 227 * 1024, kSmemReservedPerBlock = 1024;
 
 template <int OPT, int PDT, int ECC_BITS, int STATE>
 cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStream_t s) {
-  const bool aux = p_in.peers.ng > 0 || p_in.sq_norm != nullptr || p_in.peers.mc_pdelta != 0 || p_in.peers.mc_gdelta != 0;
+  const bool aux = p_in.peers.n > 0 || p_in.peers.ng > 0 || p_in.sq_norm != nullptr || p_in.peers.mc_pdelta != 0 || p_in.peers.mc_gdelta != 0;
   const bool switch_sum = p_in.peers.mc_gdelta != 0 && p_in.grad_dtype != FO_F32;
   const int ring_bytes = switch_sum ? kSwitchBatch * 16 * kThreads : 0;
   auto kernel = aux ? step_kernel<OPT, PDT, ECC_BITS, STATE, true> : step_kernel<OPT, PDT, ECC_BITS, STATE, false>;
@@ -1408,17 +1567,18 @@ cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStre
   }
   // as many stages as fit beside the tables with min_blocks(OPT) blocks on an SM; when the peers'
   // gradient pieces make a stage too large for two of them, with one block on an SM
-  const int per_stage = Stage<OPT, PDT, ECC_BITS, STATE>::bytes(p_in.grad_dtype, switch_sum ? 0 : p_in.peers.ng);
+  // (the plain kernel runs three stages, each with room for fp32 gradients: see hot_run)
+  const int per_stage = Stage<OPT, PDT, ECC_BITS, STATE>::bytes(aux ? p_in.grad_dtype : FO_F32, switch_sum ? 0 : p_in.peers.ng);
   int blocks_per_sm = min_blocks(OPT);
   int stages = (kSmemPerSm / blocks_per_sm - kSmemReservedPerBlock - static_smem - ring_bytes) / per_stage;
-  if (stages < 2) {
-    blocks_per_sm = 1;
-    stages = (kSmemPerSm - kSmemReservedPerBlock - static_smem - ring_bytes) / per_stage;
+  while (stages < (aux ? 2 : 3) && blocks_per_sm > 1) {
+    --blocks_per_sm;
+    stages = (kSmemPerSm / blocks_per_sm - kSmemReservedPerBlock - static_smem - ring_bytes) / per_stage;
   }
   static_assert(kMaxStages <= 3, "the plain kernel waits for 2 or 3 stages only");
   const int max_stages = (p_in.peers.ng > 0 && !switch_sum) ? kMaxStagesPeers : kMaxStages;
   if (stages > max_stages) stages = max_stages;
-  if (stages < 2) return cudaErrorInvalidConfiguration;
+  if (stages < (aux ? 2 : 3)) return cudaErrorInvalidConfiguration;
   const int dynamic_smem = stages * per_stage + ring_bytes;
   static bool opted[2][64] = {};  // per kernel and device ordinal: the opt-in above 48 KB belongs to the device's copy of the function
   bool* opted_in = opted[aux ? 1 : 0];
