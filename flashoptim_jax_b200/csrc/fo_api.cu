@@ -18,22 +18,24 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
-static LaunchFn find_launcher(int opt, int pdt, int ecc_bits, int state, bool generic) {
+static Launcher find_launcher(int opt, int pdt, int ecc_bits, int state, bool generic, bool aux) {
+#define FO_PICK(stem) return aux ? stem##_aux(pdt, ecc_bits) : stem##_plain(pdt, ecc_bits)
   if (opt == FO_OPT_ADAM) {
     if (generic) return lookup_adam_generic(pdt, ecc_bits);
-    if (state == FO_STATE_QUANT) return lookup_adam_quant(pdt, ecc_bits);
-    if (state == FO_STATE_FULL) return lookup_adam_full(pdt, ecc_bits);
+    if (state == FO_STATE_QUANT) FO_PICK(lookup_adam_quant);
+    if (state == FO_STATE_FULL) FO_PICK(lookup_adam_full);
   } else if (opt == FO_OPT_LION) {
     if (generic) return lookup_lion_generic(pdt, ecc_bits);
-    if (state == FO_STATE_QUANT) return lookup_lion_quant(pdt, ecc_bits);
-    if (state == FO_STATE_FULL) return lookup_lion_full(pdt, ecc_bits);
+    if (state == FO_STATE_QUANT) FO_PICK(lookup_lion_quant);
+    if (state == FO_STATE_FULL) FO_PICK(lookup_lion_full);
   } else if (opt == FO_OPT_SGD) {
     if (generic) return lookup_sgd_generic(pdt, ecc_bits);
-    if (state == FO_STATE_QUANT) return lookup_sgd_quant(pdt, ecc_bits);
-    if (state == FO_STATE_FULL) return lookup_sgd_full(pdt, ecc_bits);
-    if (state == FO_STATE_NONE) return lookup_sgd_none(pdt, ecc_bits);
+    if (state == FO_STATE_QUANT) FO_PICK(lookup_sgd_quant);
+    if (state == FO_STATE_FULL) FO_PICK(lookup_sgd_full);
+    if (state == FO_STATE_NONE) FO_PICK(lookup_sgd_none);
   }
-  return nullptr;
+#undef FO_PICK
+  return Launcher{nullptr, 0u};
 }
 
 static DevHyper make_dev_hyper(const FoHyper& h, int opt) {
@@ -99,8 +101,8 @@ extern "C" int fo_step(const FoStepDesc* d, void* cuda_stream) {
   if (d->n_peers > 0 && d->peer_param_offsets == nullptr && d->peer_grad_offsets == nullptr)
     return fail(FO_ERR_INVALID_ARG, "fo_step: n_peers without peer_param_offsets or peer_grad_offsets");
   if (d->n_peers > 0 && generic) return fail(FO_ERR_UNSUPPORTED, "fo_step: peer replicas need group_size 32");
-  LaunchFn launch = find_launcher(d->opt, d->param_dtype, d->ecc_bits, d->state, generic);
-  if (launch == nullptr) return fail(FO_ERR_UNSUPPORTED, "fo_step: no kernel for this combination");
+  if (find_launcher(d->opt, d->param_dtype, d->ecc_bits, d->state, generic, false).launch == nullptr)
+    return fail(FO_ERR_UNSUPPORTED, "fo_step: no kernel for this combination");
 
   const bool need_mu = d->state != FO_STATE_NONE;
   const bool need_nu = need_mu && d->opt == FO_OPT_ADAM;
@@ -118,7 +120,6 @@ extern "C" int fo_step(const FoStepDesc* d, void* cuda_stream) {
   }
 
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  const unsigned long long chunk = chunk_elems(d->group_size, generic);
   LaunchInfo info;
   info.sm_count = sm_count_of_current_device();
   if (info.sm_count <= 0) return fail(FO_ERR_CUDA, "fo_step: cannot query the current device");
@@ -153,6 +154,11 @@ extern "C" int fo_step(const FoStepDesc* d, void* cuda_stream) {
   }
   p.sq_norm = d->grad_sq_norm;
   p.max_norm = d->max_grad_norm;
+  // the slice that runs this step, and the elements one of its chunks covers
+  const Launcher launcher = find_launcher(d->opt, d->param_dtype, d->ecc_bits, d->state, generic, step_needs_aux(p));
+  if (launcher.launch == nullptr) return fail(FO_ERR_UNSUPPORTED, "fo_step: no kernel for this combination");
+  const LaunchFn launch = launcher.launch;
+  const unsigned long long chunk = generic ? generic_tile_elems(d->group_size) : launcher.chunk;
 
   int count = 0;
   unsigned long long blocks = 0;

@@ -513,6 +513,10 @@ struct Stage {
   __host__ __device__ static constexpr int bytes(int gdt, int grad_peers) { return kOffGrad + grad_bytes(gdt) * (1 + grad_peers); }
 };
 constexpr int kMaxStages = FO_MAX_STAGES;   // local streams: deeper brings nothing (measured 2 = 3 = 4)
+#ifndef FO_PLAIN_STAGES
+#define FO_PLAIN_STAGES 3
+#endif
+constexpr int kPlainStages = FO_PLAIN_STAGES;  // stages (= unroll factor) of the kernel without peer or clipping code
 #ifndef FO_MAX_STAGES_PEERS
 #define FO_MAX_STAGES_PEERS 8
 #endif
@@ -1218,22 +1222,24 @@ FO_DEVI void hot_run(const DevLeaf& L, const Hyp& h, const int gdt, const uint32
     r.g0 = lds128(s16 + o + S::kOffGrad);
     if (gdt == FO_F32) r.g1 = lds128(s16 + o + S::kOffGrad + 16u * kThreads);
   };
-  if (0u < n_it) fill(0, 0);
-  copy_commit();
-  if (1u < n_it) fill(1, 1);
-  copy_commit();
+  constexpr int kS = kPlainStages;
+#pragma unroll
+  for (int k = 0; k < kS - 1; ++k) {
+    if ((uint32_t)k < n_it) fill(k, k);
+    copy_commit();
+  }
   __half msc = __float2half(0.0f), vsc = msc;  // the group scales go through registers, one chunk ahead
   if constexpr (STATE == FO_STATE_QUANT) {
     msc = *(const __half*)at.msc;
     if constexpr (OPT == FO_OPT_ADAM) vsc = *(const __half*)at.vsc;
   }
-  for (uint32_t it = 0; it < n_it; it += 3u) {
+  for (uint32_t it = 0; it < n_it; it += (uint32_t)kS) {
 #pragma unroll
-    for (int k = 0; k < 3; ++k) {
+    for (int k = 0; k < kS; ++k) {
       if (it + (uint32_t)k >= n_it) break;
-      if (it + (uint32_t)(k + 2) < n_it) fill((k + 2) % 3, k + 2);
+      if (it + (uint32_t)(k + kS - 1) < n_it) fill((k + kS - 1) % kS, k + kS - 1);
       copy_commit();
-      copy_wait<2>();
+      copy_wait<kS - 1>();
       Raw<OPT, PDT, ECC_BITS, STATE> raw;
       read(k, raw);
       raw.msc = msc; raw.vsc = vsc;
@@ -1255,17 +1261,17 @@ FO_DEVI void hot_run(const DevLeaf& L, const Hyp& h, const int gdt, const uint32
       cur.vsc = at.vsc + k * (kChunk / 32 * 2);
       hot_finish<false, OPT, PDT, ECC_BITS, STATE, false>(L, h, gdt, base + (uint32_t)k * kChunk, cur, one, rare, u, lut_mw, peers, nullptr);
     }
-    base += 3u * (uint32_t)kChunk;
-    at.grad += 3 * kChunk * gsz;
-    at.param += 3 * kChunk * kPsz;
-    if constexpr (ECC_BITS != 0) at.ecc += 3 * kChunk * kEsz;
+    base += (uint32_t)(kS * kChunk);
+    at.grad += kS * kChunk * gsz;
+    at.param += kS * kChunk * kPsz;
+    if constexpr (ECC_BITS != 0) at.ecc += kS * kChunk * kEsz;
     if constexpr (STATE != FO_STATE_NONE) {
-      at.mu += 3 * kChunk * kSsz;
-      if constexpr (OPT == FO_OPT_ADAM) at.nu += 3 * kChunk * kSsz;
+      at.mu += kS * kChunk * kSsz;
+      if constexpr (OPT == FO_OPT_ADAM) at.nu += kS * kChunk * kSsz;
     }
     if constexpr (STATE == FO_STATE_QUANT) {
-      at.msc += 3 * (kChunk / 32 * 2);
-      if constexpr (OPT == FO_OPT_ADAM) at.vsc += 3 * (kChunk / 32 * 2);
+      at.msc += kS * (kChunk / 32 * 2);
+      if constexpr (OPT == FO_OPT_ADAM) at.vsc += kS * (kChunk / 32 * 2);
     }
   }
 }
@@ -1536,10 +1542,9 @@ __global__ void __launch_bounds__(256) step_kernel_generic(const __grid_constant
   }
 }
 
-// elements one block iteration covers, as the host must assume when it builds first_block[]
-inline unsigned long long chunk_elems(int group_size, bool generic) {
-  if (generic) return (unsigned long long)(kGenericTile / group_size > 0 ? kGenericTile / group_size : 1) * group_size;
-  return (unsigned long long)kChunk;
+// elements one block of the any-group-size kernel covers
+inline unsigned int generic_tile_elems(int group_size) {
+  return (unsigned int)(kGenericTile / group_size > 0 ? kGenericTile / group_size : 1) * (unsigned int)group_size;
 }
 
 // grid of the persistent kernel: resident blocks per SM x SMs of the current device
@@ -1548,16 +1553,29 @@ struct LaunchInfo {
   int sm_count;
 };
 using LaunchFn = cudaError_t (*)(const StepParams&, const LaunchInfo&, cudaStream_t);
+// A kernel slice and the elements one of its chunks covers.  Block size, and with it the chunk, is a
+// property of the slice (the slices are compiled with their own FO_THREADS): the host builds
+// first_block[] from this number.
+struct Launcher {
+  LaunchFn launch;
+  unsigned int chunk;
+};
 
 // Shared memory of one SM that blocks may use, and what each block loses to the system.
 constexpr int kSmemPerSm = 227 * 1024, kSmemReservedPerBlock = 1024;
 
-template <int OPT, int PDT, int ECC_BITS, int STATE>
+// whether a step needs the kernel that carries the peer and clipping code
+inline bool step_needs_aux(const StepParams& p) {
+  return p.peers.n > 0 || p.peers.ng > 0 || p.sq_norm != nullptr || p.peers.mc_pdelta != 0 || p.peers.mc_gdelta != 0;
+}
+
+template <int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
 cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStream_t s) {
-  const bool aux = p_in.peers.n > 0 || p_in.peers.ng > 0 || p_in.sq_norm != nullptr || p_in.peers.mc_pdelta != 0 || p_in.peers.mc_gdelta != 0;
+  constexpr bool aux = AUX;
+  if (step_needs_aux(p_in) != aux) return cudaErrorInvalidValue;
   const bool switch_sum = p_in.peers.mc_gdelta != 0 && p_in.grad_dtype != FO_F32;
   const int ring_bytes = switch_sum ? kSwitchBatch * 16 * kThreads : 0;
-  auto kernel = aux ? step_kernel<OPT, PDT, ECC_BITS, STATE, true> : step_kernel<OPT, PDT, ECC_BITS, STATE, false>;
+  auto kernel = step_kernel<OPT, PDT, ECC_BITS, STATE, AUX>;
   static int static_smem = -1;  // the same on every device
   if (static_smem < 0) {
     cudaFuncAttributes attr;
@@ -1571,17 +1589,15 @@ cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStre
   const int per_stage = Stage<OPT, PDT, ECC_BITS, STATE>::bytes(aux ? p_in.grad_dtype : FO_F32, switch_sum ? 0 : p_in.peers.ng);
   int blocks_per_sm = min_blocks(OPT);
   int stages = (kSmemPerSm / blocks_per_sm - kSmemReservedPerBlock - static_smem - ring_bytes) / per_stage;
-  while (stages < (aux ? 2 : 3) && blocks_per_sm > 1) {
+  while (stages < (aux ? 2 : kPlainStages) && blocks_per_sm > 1) {
     --blocks_per_sm;
     stages = (kSmemPerSm / blocks_per_sm - kSmemReservedPerBlock - static_smem - ring_bytes) / per_stage;
   }
-  static_assert(kMaxStages <= 3, "the plain kernel waits for 2 or 3 stages only");
-  const int max_stages = (p_in.peers.ng > 0 && !switch_sum) ? kMaxStagesPeers : kMaxStages;
+  const int max_stages = !aux ? kPlainStages : ((p_in.peers.ng > 0 && !switch_sum) ? kMaxStagesPeers : kMaxStages);
   if (stages > max_stages) stages = max_stages;
-  if (stages < (aux ? 2 : 3)) return cudaErrorInvalidConfiguration;
+  if (stages < (aux ? 2 : kPlainStages)) return cudaErrorInvalidConfiguration;
   const int dynamic_smem = stages * per_stage + ring_bytes;
-  static bool opted[2][64] = {};  // per kernel and device ordinal: the opt-in above 48 KB belongs to the device's copy of the function
-  bool* opted_in = opted[aux ? 1 : 0];
+  static bool opted_in[64] = {};  // per device ordinal: the opt-in above 48 KB belongs to the device's copy of the function
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
@@ -1605,13 +1621,16 @@ cudaError_t launch_step_generic(const StepParams& p, const LaunchInfo& info, cud
   return cudaGetLastError();
 }
 
-// lookups implemented by the instantiation units (fo_step_inst.cu, one per slice);
-// each returns nullptr for a (param dtype, ecc width) pair that does not exist
-#define FO_DECLARE_LOOKUP(name) LaunchFn name(int pdt, int ecc_bits);
-FO_DECLARE_LOOKUP(lookup_adam_quant) FO_DECLARE_LOOKUP(lookup_adam_full) FO_DECLARE_LOOKUP(lookup_adam_generic)
-FO_DECLARE_LOOKUP(lookup_lion_quant) FO_DECLARE_LOOKUP(lookup_lion_full) FO_DECLARE_LOOKUP(lookup_lion_generic)
-FO_DECLARE_LOOKUP(lookup_sgd_quant) FO_DECLARE_LOOKUP(lookup_sgd_full) FO_DECLARE_LOOKUP(lookup_sgd_generic)
-FO_DECLARE_LOOKUP(lookup_sgd_none)
+// lookups implemented by the instantiation units (fo_step_inst.cu, one per slice: optimizer x state
+// kind x with / without the peer and clipping code); each returns {nullptr, 0} for a (param dtype,
+// ecc width) pair that does not exist
+#define FO_DECLARE_LOOKUP(name) Launcher name(int pdt, int ecc_bits);
+#define FO_DECLARE_PAIR(stem) FO_DECLARE_LOOKUP(stem##_plain) FO_DECLARE_LOOKUP(stem##_aux)
+FO_DECLARE_PAIR(lookup_adam_quant) FO_DECLARE_PAIR(lookup_adam_full) FO_DECLARE_LOOKUP(lookup_adam_generic)
+FO_DECLARE_PAIR(lookup_lion_quant) FO_DECLARE_PAIR(lookup_lion_full) FO_DECLARE_LOOKUP(lookup_lion_generic)
+FO_DECLARE_PAIR(lookup_sgd_quant) FO_DECLARE_PAIR(lookup_sgd_full) FO_DECLARE_LOOKUP(lookup_sgd_generic)
+FO_DECLARE_PAIR(lookup_sgd_none)
+#undef FO_DECLARE_PAIR
 #undef FO_DECLARE_LOOKUP
 
 }  // namespace fo

@@ -13,7 +13,7 @@ bit-identical to the single-device step whenever the averaged gradient is.
 
 Layout.  All leaves of one parameter dtype live in one flat buffer, each leaf starting at a
 multiple of 32 elements (a group boundary; also 16-byte alignment for the vector path).
-The buffer is cut into n_slices slices of world_size pieces, a piece being a multiple of 2048
+The buffer is cut into n_slices slices of world_size pieces, a piece being a multiple of 4096
 elements (one kernel chunk): rank r owns piece r of every slice; a leaf that straddles
 pieces is cut at group boundaries.  One slice is the unit of the collectives, so that the
 step of slice s runs while slice s+1 is still being reduce-scattered and the all-gathers
@@ -41,7 +41,7 @@ from .lion import lion_hyper
 from .sgd import sgd_hyper
 
 LEAF_ALIGN = 32      # elements: one quantization group
-SHARD_ALIGN = 2048   # elements: one kernel chunk
+SHARD_ALIGN = 4096   # elements: the largest kernel chunk (512-thread blocks x 8), so that a shard is whole chunks for every slice
 
 
 class Segment(NamedTuple):
