@@ -145,6 +145,7 @@ __host__ __device__ inline bool adam_is_tame(float eps, float sqrt_bc2) {
 struct Hyp {
   float lr, wd, b1, b2, omb1, omb2, eps;
   float decay, lr_bc1, sqrt_bc2, rcp_sqrt_bc2;
+  float m_lo, m_hi;  // Adam: first moments between these keep the update's numerator lr/bc1 * m inside [2^-70, 2^60]
   uint32_t flags;
 };
 
@@ -164,6 +165,14 @@ FO_DEVI Hyp load_hyper(const DevHyper& d) {
       h.rcp_sqrt_bc2 = __frcp_rn(h.sqrt_bc2);
       h.flags = (d.flags & ~kFlagTameAdam) | (adam_is_tame(d.eps, h.sqrt_bc2) ? kFlagTameAdam : 0u);
     }
+  }
+  h.m_lo = 0.0f; h.m_hi = 0.0f;
+  if constexpr (OPT == FO_OPT_ADAM) {
+    // quotients nudged two places inwards, so that m >= m_lo implies RN(|lr_bc1| * m) >= 2^-70 and
+    // m <= m_hi implies RN(|lr_bc1| * m) <= 2^60; lr = 0 gives m_lo = inf (everything takes the IEEE repairs)
+    const float lrb = fabsf(h.lr_bc1);
+    h.m_lo = fmul(fdiv(8.4703295e-22f, lrb), 1.0000005f);
+    h.m_hi = fmul(fdiv(1.1529215e18f, lrb), 0.9999995f);
   }
   return h;
 }
@@ -920,9 +929,11 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
     // sqrt <= 2^30 (so the denominator lies in [eps, 2^47]) and numerator magnitudes in [2^-70, 2^60].
     am_lane = maxabs8(m);
     av_lane = -min8(nroot);
-    const float lrb = fabsf(h.lr_bc1);
-    if (!(max8(nv) <= -1.0e-30f) || !(av_lane <= 1.0737418e9f) || !(fmul(minabs8(m), lrb) >= 8.4703295e-22f) ||
-        !(fmul(am_lane, lrb) <= 1.1529215e18f)) {
+    // (with quantized moments the largest square root is checked once per group below, after the
+    // shuffles; the repairing pass needs the answer per lane)
+    bool wild = !(max8(nv) <= -1.0e-30f) || !(minabs8(m) >= h.m_lo) || !(am_lane <= h.m_hi);
+    if constexpr (REPAIR || STATE != FO_STATE_QUANT) wild = wild || !(av_lane <= 1.0737418e9f);
+    if (wild) {
       rare = true;
       if constexpr (REPAIR) {
 #pragma unroll
@@ -1053,7 +1064,7 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
       const float2 av2 = sp(av), nrv2 = sp(-fast::rcp_rn(av));
 #pragma unroll
       for (int k = 0; k < 4; ++k) quant_v_bits2(nroot[k], av2, nrv2, one2, q[2 * k], q[2 * k + 1]);
-      if (!(av >= 1.0e-12f && av <= 1.0e30f)) {
+      if (!(av >= 1.0e-12f && av <= 1.0737418e9f)) {  // 2^30: also the limit of the packed Adam division
         rare = true;
         if constexpr (REPAIR) {
           const float safe = ieee::safe_scale(av, floor_mode);
@@ -1114,12 +1125,13 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
       __stcs((float4*)at.nu + 1, make_float4(v[2].x, v[2].y, v[3].x, v[3].y));
     }
   } else if constexpr (STATE == FO_STATE_QUANT) {
-    const bool writer = (threadIdx.x & 3) == 0;
+    // the four lanes of a group all store its scale: same value to the same address, one
+    // unpredicated instruction
     __stcs((uint2*)at.mu, mq);
-    if (writer) *(__half*)at.msc = __float2half_rn(am);
+    *(__half*)at.msc = __float2half_rn(am);
     if constexpr (OPT == FO_OPT_ADAM) {
       __stcs((uint2*)at.nu, vq);
-      if (writer) *(__half*)at.vsc = __float2half_rn(av);
+      *(__half*)at.vsc = __float2half_rn(av);
     }
   }
 }
