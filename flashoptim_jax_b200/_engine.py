@@ -189,6 +189,93 @@ def device_step_scalars(count: Any, leaves: List[torch.Tensor], configs: List[Di
     return count, [scalars[key].data_ptr() for key in keys], list(scalars.values())
 
 
+# ---- observing launches (benchmarks time every fo_step call with CUDA events) ----------------------
+
+_observer = None
+
+
+def set_launch_observer(fn) -> None:
+    """`fn(bucket_key, n_params)` must return a context manager; every fo_step call of this module then
+    runs inside it.  None switches observation off."""
+    global _observer
+    _observer = fn
+
+
+def _observed(key, n_params):
+    return contextlib.nullcontext() if _observer is None else _observer(key, n_params)
+
+
+class PreparedLaunch:
+    """The fo_step calls of a fixed list of leaves, with their descriptor tables built once.
+
+    The buffers of a sharded optimizer never move, so only the hyper-parameter values change from step
+    to step: `run` writes them into the prepared tables (one entry per distinct hyper-parameter group)
+    and issues the calls.  The host cost of a step is then proportional to the number of calls and
+    groups, not to the number of leaves (the per-leaf Python loop of the reference,
+    flashoptim_jax/adamw.py:522-540, runs once)."""
+
+    def __init__(self, opt: int, work: List[LeafWork], group_ids: List[int], peer_param_offsets: Optional[List[int]] = None,
+                 peer_grad_offsets: Optional[List[int]] = None, mc_param_offset: int = 0, mc_grad_offset: int = 0):
+        self.peers = np.asarray(peer_param_offsets or [], dtype=np.int64)
+        self.grad_peers = np.asarray(peer_grad_offsets or [], dtype=np.int64)
+        if len(self.peers) and len(self.grad_peers) and len(self.peers) != len(self.grad_peers):
+            raise ValueError("peer_param_offsets and peer_grad_offsets must name the same peers")
+        n_peers = max(len(self.peers), len(self.grad_peers))
+        buckets: Dict[Tuple[Any, ...], List[Tuple[LeafWork, int]]] = {}
+        for w, gid in zip(work, group_ids):
+            buckets.setdefault(w.bucket, []).append((w, gid))
+        self.calls: List[Dict[str, Any]] = []
+        for key, items in buckets.items():
+            dev_index, pdt, gdt, ecc_bits, state, group_size = key
+            start = 0
+            while start < len(items):
+                slots: Dict[int, int] = {}
+                end = start
+                while end < len(items) and (items[end][1] in slots or len(slots) < _lib.FO_MAX_HYPERS):
+                    slots.setdefault(items[end][1], len(slots))
+                    end += 1
+                part = items[start:end]
+                ws = [w for w, _ in part]
+                leaves = np.zeros(len(part), dtype=LEAF_DTYPE)
+                leaves["grad"] = [w.grad.data_ptr() for w in ws]
+                leaves["param"] = [w.param.data_ptr() for w in ws]
+                for name in ("ecc", "mu", "mu_scales", "nu", "nu_scales"):
+                    leaves[name] = [_ptr(getattr(w, name)) for w in ws]
+                leaves["n"] = [w.param.numel() for w in ws]
+                leaves["hyper"] = [slots[gid] for _, gid in part]
+                hypers = np.zeros(len(slots), dtype=HYPER_DTYPE)
+                desc = _lib.FoStepDesc(
+                    struct_size=ctypes.sizeof(_lib.FoStepDesc), opt=opt, param_dtype=pdt, grad_dtype=gdt, ecc_bits=ecc_bits,
+                    state=state, group_size=group_size, n_leaves=len(part), n_hypers=len(slots),
+                    leaves=leaves.ctypes.data, hypers=hypers.ctypes.data, n_peers=n_peers,
+                    peer_param_offsets=self.peers.ctypes.data if len(self.peers) else None,
+                    peer_grad_offsets=self.grad_peers.ctypes.data if len(self.grad_peers) else None,
+                )
+                desc.mc_param_offset, desc.mc_grad_offset = int(mc_param_offset), int(mc_grad_offset)
+                self.calls.append({"key": key, "desc": desc, "leaves": leaves, "hypers": hypers, "slots": list(slots.items()),
+                                   "device": torch.device("cuda", dev_index), "n_params": int(leaves["n"].sum()),
+                                   "keep": ws})  # the tensors stay alive as long as their addresses are in the tables
+                start = end
+
+    def run(self, hyper_of_group: Dict[int, Tuple[Any, ...]]) -> int:
+        lib = _lib.lib()
+        clip = getattr(_clip, "value", None)
+        for call in self.calls:
+            hypers = call["hypers"]
+            for gid, slot in call["slots"]:
+                hp = hyper_of_group[gid]
+                hypers[slot] = hp if len(hp) == len(HYPER_DTYPE.names) else hp + (0,)
+            desc = call["desc"]
+            if clip is not None:
+                desc.grad_sq_norm, desc.max_grad_norm = clip[0].data_ptr(), clip[1]
+            else:
+                desc.grad_sq_norm, desc.max_grad_norm = None, 0.0
+            device = call["device"]
+            with torch.cuda.device(device), _observed(call["key"], call["n_params"]):
+                _lib.check(lib.fo_step(ctypes.byref(desc), stream_ptr(device)))
+        return len(self.calls)
+
+
 def launch(opt: int, work: List[LeafWork], peer_param_offsets: Optional[List[int]] = None,
            peer_grad_offsets: Optional[List[int]] = None, mc_param_offset: int = 0, mc_grad_offset: int = 0) -> int:
     """Issue one fo_step per bucket (per <=16 hyper sets); returns the number of calls.
@@ -244,7 +331,7 @@ def launch(opt: int, work: List[LeafWork], peer_param_offsets: Optional[List[int
             if clip is not None:
                 desc.grad_sq_norm, desc.max_grad_norm = clip[0].data_ptr(), clip[1]
             device = torch.device("cuda", dev_index)
-            with torch.cuda.device(device):
+            with torch.cuda.device(device), _observed(key, int(leaves["n"].sum())):
                 _lib.check(lib.fo_step(ctypes.byref(desc), stream_ptr(device)))
             calls += 1
             hyper_index = {}

@@ -132,7 +132,7 @@ struct StepParams {
   Peers peers;
   const double* sq_norm;  // device: sum of squares of all gradients of the step (nullptr: no clipping)
   float max_norm;
-  int32_t pad;
+  uint32_t run_chunks;  // consecutive chunks a block takes at a time (set by the launcher)
 };
 
 // true when the quotient sqrt(nu)/sqrt(bc2) may be formed as div_by_rcp without changing
@@ -665,6 +665,195 @@ FO_DEVI float maxabs8(const float2 (&x)[4]) {
 // byte k of a word as an index
 FO_DEVI uint32_t byte_of(uint32_t w, int k) { return __byte_perm(w, 0u, 0x4440u | (uint32_t)k); }
 
+// Addresses of the eight elements a thread owns in the current chunk, one per stream.  Inside a run
+// of consecutive chunks they advance by compile-time constants, so a later chunk's address is this
+// one plus an immediate.
+struct Piece {
+  const char* grad;
+  char* param;
+  char* ecc;
+  char* mu;
+  char* nu;
+  char* msc;  // the group's scale (four lanes share one)
+  char* vsc;
+};
+template <int PDT, int ECC_BITS, int STATE>
+FO_DEVI Piece piece_at(const DevLeaf& L, const int gdt, const uint32_t i0) {
+  Piece a;
+  a.grad = (const char*)L.grad + (size_t)i0 * (gdt == FO_F32 ? 4u : 2u);
+  a.param = (char*)L.param + (size_t)i0 * (PDT == FO_F32 ? 4u : 2u);
+  a.ecc = (char*)L.ecc + (size_t)i0 * (ECC_BITS == 16 ? 2u : 1u);
+  a.mu = (char*)L.mu + (size_t)i0 * (STATE == FO_STATE_FULL ? 4u : 1u);
+  a.nu = (char*)L.nu + (size_t)i0 * (STATE == FO_STATE_FULL ? 4u : 1u);
+  a.msc = (char*)L.mu_scales + (size_t)(i0 >> 5) * 2u;
+  a.vsc = (char*)L.nu_scales + (size_t)(i0 >> 5) * 2u;
+  return a;
+}
+
+// master weights of a piece from the stored parameter words (p0, p1) and ECC words (e_in); same
+// contract for REPAIR as hot_unpack
+template <bool REPAIR, int PDT, int ECC_BITS>
+FO_DEVI bool unpack_master(const uint4& p0, const uint4& p1, const uint4& e_in, const float2 one2, float2 (&theta)[4]) {
+  using namespace fast2;
+  bool rare = false;
+  if constexpr (PDT == FO_F32) {
+    pairs_of(p0, p1, theta);
+  } else {
+    float2 old_lp[4];  // stored param as fp32
+    pairs_of16<PDT>(p0, old_lp);
+    if constexpr (ECC_BITS == 0) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) theta[k] = old_lp[k];
+    } else {
+      int e[8];
+      if constexpr (ECC_BITS == 16) {
+        const uint32_t w[4] = {e_in.x, e_in.y, e_in.z, e_in.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { e[2 * k] = (int)(short)(w[k] & 0xFFFFu); e[2 * k + 1] = (int)w[k] >> 16; }
+      } else {
+        const uint32_t w[2] = {e_in.x, e_in.y};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) e[k] = (int)(signed char)((w[k >> 2] >> (8 * (k & 3))) & 0xFFu);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        theta[k] = reconstruct_ordinary2<PDT, ECC_BITS>(old_lp[k], mk((float)e[2 * k], (float)e[2 * k + 1]), one2);
+      if constexpr (PDT == FO_BF16) {
+        // a value too small for the exponent-field shortcut (zero included)
+        if (!(minabs8(old_lp) >= fast::Ordinary<PDT>::kMin)) {
+          rare = true;
+          if constexpr (REPAIR) {
+            const uint32_t w[4] = {p0.x, p0.y, p0.z, p0.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              theta[k].x = repair_master<PDT, ECC_BITS>(w[k] & 0xFFFFu, e[2 * k]);
+              theta[k].y = repair_master<PDT, ECC_BITS>(w[k] >> 16, e[2 * k + 1]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  return rare;
+}
+
+// updated master weights -> parameter words and ECC words; same contract for REPAIR as hot_unpack
+template <bool REPAIR, int PDT, int ECC_BITS>
+FO_DEVI bool stored_form(const float2 (&theta)[4], uint32_t (&nw)[4], uint4& ecc_out) {
+  using namespace fast2;
+  bool rare = false;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) nw[k] = 0u;
+  ecc_out = make_uint4(0, 0, 0, 0);
+  if constexpr (PDT != FO_F32) {
+    float2 new_lp[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      nw[k] = pack2<PDT>(theta[k].x, theta[k].y);
+      unpack2<PDT>(nw[k], new_lp[k].x, new_lp[k].y);
+    }
+    if constexpr (ECC_BITS != 0) {
+      int ne[8];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) ecc_ordinary2<PDT, ECC_BITS>(theta[k], new_lp[k], ne[2 * k], ne[2 * k + 1]);
+      {
+        // outside these the exponent-field shortcut does not hold (tiny bf16 values), or the
+        // update overflowed the 16-bit range and the reference clips the ECC
+        bool odd = !(maxabs8(new_lp) <= 1.0e38f);
+        if constexpr (PDT == FO_BF16) odd = odd || !(minabs8(new_lp) >= fast::Ordinary<PDT>::kMin);
+        if (odd) {
+          rare = true;
+          if constexpr (REPAIR) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              ne[2 * k] = repair_ecc<PDT, ECC_BITS>(theta[k].x);
+              ne[2 * k + 1] = repair_ecc<PDT, ECC_BITS>(theta[k].y);
+            }
+          }
+        }
+      }
+      if constexpr (ECC_BITS == 16) {
+        ecc_out.x = pack_halves(ne[0], ne[1]); ecc_out.y = pack_halves(ne[2], ne[3]);
+        ecc_out.z = pack_halves(ne[4], ne[5]); ecc_out.w = pack_halves(ne[6], ne[7]);
+      } else {
+        ecc_out.x = pack_bytes(ne[0], ne[1], ne[2], ne[3]);
+        ecc_out.y = pack_bytes(ne[4], ne[5], ne[6], ne[7]);
+      }
+    }
+  }
+
+  return rare;
+}
+
+// A warp whose 256 gradients are +-0 and whose moment codes are all 0, the lasting state of rows that
+// never see a gradient (embedding rows of tokens that do not occur): the new moments are exactly zero
+// and so is the update term, so the step is the weight decay alone, the new codes and scales are
+// zeros.  Everything is read again from memory (the first pass has overwritten its registers with the
+// results of 0/0 arithmetic).
+// Returns false when a parameter lies outside the range of the packed split (the caller then takes
+// the repairing pass); nothing has been stored in that case.
+template <int OPT, int PDT, int ECC_BITS>
+__device__ __noinline__ bool zero_chunk(const uint32_t flags, const float wd, const float decay, const int gdt, const float one,
+                                        const char* p_grad, char* p_param, char* p_ecc, char* p_mu, char* p_nu, char* p_msc, char* p_vsc) {
+  // (addresses and scalars by value: a structure passed by reference would have to live in local memory)
+  using namespace fast2;
+  const float2 one2 = sp(one);
+  struct { const char* grad; char* param; char* ecc; char* mu; char* nu; char* msc; char* vsc; } at = {p_grad, p_param, p_ecc, p_mu, p_nu, p_msc, p_vsc};
+  struct { uint32_t flags; float wd, decay; } h = {flags, wd, decay};
+  // the test, on what is in memory: gradients +-0, all codes 0 (then the moments are zero whatever the
+  // scales say), and no weight decay folded into the gradient
+  if ((h.flags & FO_FLAG_DECOUPLED_WD) == 0 && h.wd != 0.0f) return false;
+  {
+    const uint4 g0 = __ldcs((const uint4*)at.grad);
+    uint32_t any = (g0.x | g0.y | g0.z | g0.w) & (gdt == FO_F32 ? 0x7FFFFFFFu : 0x7FFF7FFFu);
+    if (gdt == FO_F32) {
+      const uint4 g1 = __ldcs((const uint4*)at.grad + 1);
+      any |= (g1.x | g1.y | g1.z | g1.w) & 0x7FFFFFFFu;
+    }
+    const uint2 mq = __ldcs((const uint2*)at.mu);
+    any |= mq.x | mq.y;
+    if constexpr (OPT == FO_OPT_ADAM) {
+      const uint2 vq = __ldcs((const uint2*)at.nu);
+      any |= vq.x | vq.y;
+    }
+    if (!__all_sync(0xFFFFFFFFu, any == 0u)) return false;
+  }
+  uint4 p0, p1 = make_uint4(0, 0, 0, 0), e = make_uint4(0, 0, 0, 0);
+  p0 = __ldcs((const uint4*)at.param);
+  if constexpr (PDT == FO_F32) p1 = __ldcs((const uint4*)at.param + 1);
+  if constexpr (ECC_BITS == 16) e = __ldcs((const uint4*)at.ecc);
+  if constexpr (ECC_BITS == 8) {
+    const uint2 t = __ldcs((const uint2*)at.ecc);
+    e.x = t.x; e.y = t.y;
+  }
+  float2 theta[4];
+  bool rare = unpack_master<false, PDT, ECC_BITS>(p0, p1, e, one2, theta);
+  if (OPT == FO_OPT_LION || (h.flags & FO_FLAG_DECOUPLED_WD) != 0) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) theta[k] = mul2(theta[k], sp(h.decay));
+  }
+  uint32_t nw[4];
+  uint4 ecc_out;
+  rare = stored_form<false, PDT, ECC_BITS>(theta, nw, ecc_out) || rare;
+  if (__any_sync(0xFFFFFFFFu, rare)) return false;
+  if constexpr (PDT == FO_F32) {
+    __stcs((float4*)at.param, make_float4(theta[0].x, theta[0].y, theta[1].x, theta[1].y));
+    __stcs((float4*)at.param + 1, make_float4(theta[2].x, theta[2].y, theta[3].x, theta[3].y));
+  } else {
+    __stcs((uint4*)at.param, make_uint4(nw[0], nw[1], nw[2], nw[3]));
+    if constexpr (ECC_BITS == 16) __stcs((uint4*)at.ecc, ecc_out);
+    if constexpr (ECC_BITS == 8) __stcs((uint2*)at.ecc, make_uint2(ecc_out.x, ecc_out.y));
+  }
+  __stcs((uint2*)at.mu, make_uint2(0u, 0u));
+  *(__half*)at.msc = __float2half_rn(0.0f);
+  if constexpr (OPT == FO_OPT_ADAM) {
+    __stcs((uint2*)at.nu, make_uint2(0u, 0u));
+    *(__half*)at.vsc = __float2half_rn(0.0f);
+  }
+  return true;
+}
+
 // REPAIR = false: straight-line code; returns true when a value lies outside a shortcut's proven
 // range (the results are then not to be stored).  REPAIR = true: the affected lane redoes the stage
 // with IEEE operations and the results are always good.
@@ -677,44 +866,7 @@ FO_DEVI bool hot_unpack(const Raw<OPT, PDT, ECC_BITS, STATE>& r, const int gdt, 
   else if (gdt == FO_BF16) pairs_of16<FO_BF16>(r.g0, u.g);
   else pairs_of16<FO_F16>(r.g0, u.g);
 
-  if constexpr (PDT == FO_F32) {
-    pairs_of(r.p0, r.p1, u.theta);
-  } else {
-    float2 old_lp[4];  // stored param as fp32
-    pairs_of16<PDT>(r.p0, old_lp);
-    if constexpr (ECC_BITS == 0) {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) u.theta[k] = old_lp[k];
-    } else {
-      int e[8];
-      if constexpr (ECC_BITS == 16) {
-        const uint32_t w[4] = {r.e.x, r.e.y, r.e.z, r.e.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) { e[2 * k] = (int)(short)(w[k] & 0xFFFFu); e[2 * k + 1] = (int)w[k] >> 16; }
-      } else {
-        const uint32_t w[2] = {r.e.x, r.e.y};
-#pragma unroll
-        for (int k = 0; k < 8; ++k) e[k] = (int)(signed char)((w[k >> 2] >> (8 * (k & 3))) & 0xFFu);
-      }
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        u.theta[k] = reconstruct_ordinary2<PDT, ECC_BITS>(old_lp[k], mk((float)e[2 * k], (float)e[2 * k + 1]), one2);
-      if constexpr (PDT == FO_BF16) {
-        // a value too small for the exponent-field shortcut (zero included)
-        if (!(minabs8(old_lp) >= fast::Ordinary<PDT>::kMin)) {
-          rare = true;
-          if constexpr (REPAIR) {
-            const uint32_t w[4] = {r.p0.x, r.p0.y, r.p0.z, r.p0.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              u.theta[k].x = repair_master<PDT, ECC_BITS>(w[k] & 0xFFFFu, e[2 * k]);
-              u.theta[k].y = repair_master<PDT, ECC_BITS>(w[k] >> 16, e[2 * k + 1]);
-            }
-          }
-        }
-      }
-    }
-  }
+  rare = unpack_master<REPAIR, PDT, ECC_BITS>(r.p0, r.p1, r.e, one2, u.theta);
 
   if constexpr (STATE == FO_STATE_QUANT) {
     const float2 msc = sp(__half2float(r.msc));
@@ -840,31 +992,6 @@ FO_DEVI bool clip_grads(float2 (&g)[4], const int gdt, const Clip& c) {
     for (int k = 0; k < 4; ++k) g[k] = mul2(q[k], sp(c.m_g));
   }
   return rare;
-}
-
-// Addresses of the eight elements a thread owns in the current chunk, one per stream.  Inside a run
-// of consecutive chunks they advance by compile-time constants, so a later chunk's address is this
-// one plus an immediate.
-struct Piece {
-  const char* grad;
-  char* param;
-  char* ecc;
-  char* mu;
-  char* nu;
-  char* msc;  // the group's scale (four lanes share one)
-  char* vsc;
-};
-template <int PDT, int ECC_BITS, int STATE>
-FO_DEVI Piece piece_at(const DevLeaf& L, const int gdt, const uint32_t i0) {
-  Piece a;
-  a.grad = (const char*)L.grad + (size_t)i0 * (gdt == FO_F32 ? 4u : 2u);
-  a.param = (char*)L.param + (size_t)i0 * (PDT == FO_F32 ? 4u : 2u);
-  a.ecc = (char*)L.ecc + (size_t)i0 * (ECC_BITS == 16 ? 2u : 1u);
-  a.mu = (char*)L.mu + (size_t)i0 * (STATE == FO_STATE_FULL ? 4u : 1u);
-  a.nu = (char*)L.nu + (size_t)i0 * (STATE == FO_STATE_FULL ? 4u : 1u);
-  a.msc = (char*)L.mu_scales + (size_t)(i0 >> 5) * 2u;
-  a.vsc = (char*)L.nu_scales + (size_t)(i0 >> 5) * 2u;
-  return a;
 }
 
 FO_DEVI float sign_of(float x);
@@ -997,44 +1124,9 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
   }
 
   // ---- parameter (+ECC) in stored form --------------------------------------------------------------
-  uint32_t nw[4] = {0, 0, 0, 0};
-  uint4 ecc_out = make_uint4(0, 0, 0, 0);
-  if constexpr (PDT != FO_F32) {
-    float2 new_lp[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      nw[k] = pack2<PDT>(theta[k].x, theta[k].y);
-      unpack2<PDT>(nw[k], new_lp[k].x, new_lp[k].y);
-    }
-    if constexpr (ECC_BITS != 0) {
-      int ne[8];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) ecc_ordinary2<PDT, ECC_BITS>(theta[k], new_lp[k], ne[2 * k], ne[2 * k + 1]);
-      {
-        // outside these the exponent-field shortcut does not hold (tiny bf16 values), or the
-        // update overflowed the 16-bit range and the reference clips the ECC
-        bool odd = !(maxabs8(new_lp) <= 1.0e38f);
-        if constexpr (PDT == FO_BF16) odd = odd || !(minabs8(new_lp) >= fast::Ordinary<PDT>::kMin);
-        if (odd) {
-          rare = true;
-          if constexpr (REPAIR) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              ne[2 * k] = repair_ecc<PDT, ECC_BITS>(theta[k].x);
-              ne[2 * k + 1] = repair_ecc<PDT, ECC_BITS>(theta[k].y);
-            }
-          }
-        }
-      }
-      if constexpr (ECC_BITS == 16) {
-        ecc_out.x = pack_halves(ne[0], ne[1]); ecc_out.y = pack_halves(ne[2], ne[3]);
-        ecc_out.z = pack_halves(ne[4], ne[5]); ecc_out.w = pack_halves(ne[6], ne[7]);
-      } else {
-        ecc_out.x = pack_bytes(ne[0], ne[1], ne[2], ne[3]);
-        ecc_out.y = pack_bytes(ne[4], ne[5], ne[6], ne[7]);
-      }
-    }
-  }
+  uint32_t nw[4];
+  uint4 ecc_out;
+  rare = stored_form<REPAIR, PDT, ECC_BITS>(theta, nw, ecc_out) || rare;
 
   // ---- moments in stored form ------------------------------------------------------------------------
   uint2 mq = make_uint2(0, 0), vq = make_uint2(0, 0);
@@ -1084,11 +1176,13 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
   (void)rare;
   if constexpr (!REPAIR) {
     if (__any_sync(0xFFFFFFFFu, rare)) {
+      if constexpr (OPT == FO_OPT_ADAM && STATE == FO_STATE_QUANT && !AUX) {
+        // no new first moment of the warp differs from zero: look whether the whole piece is at rest
+        if (__all_sync(0xFFFFFFFFu, am_lane == 0.0f) && zero_chunk<OPT, PDT, ECC_BITS>(h.flags, h.wd, h.decay, gdt, one, at.grad, at.param, at.ecc, at.mu, at.nu, at.msc, at.vsc)) return;
+      }
       warm_chunk<OPT, PDT, ECC_BITS, STATE, AUX>(L, h, gdt, base, one, lut_mw, peers, clip);
       return;
     }
-  } else {
-    (void)rare;
   }
   // ---- stores ---------------------------------------------------------------------------------------------
   if constexpr (PDT == FO_F32) {
@@ -1264,7 +1358,7 @@ FO_DEVI void hot_run(const DevLeaf& L, const Hyp& h, const int gdt, const uint32
       Unpacked u;
       const bool rare = hot_unpack<false, OPT, PDT, ECC_BITS, STATE>(raw, gdt, lut_mw, one, u);
       Piece cur;
-      cur.grad = at.grad;  // not used by the stores
+      cur.grad = at.grad + k * (kChunk * gsz);
       cur.param = at.param + k * (kChunk * kPsz);
       cur.ecc = at.ecc + k * (kChunk * kEsz);
       cur.mu = at.mu + k * (kChunk * kSsz);
@@ -1346,12 +1440,21 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
   const uint32_t ring0 = stage_end;
   const uint32_t toff = threadIdx.x * kPiece;
   const Clip clip = load_clip(AUX ? p.sq_norm : nullptr, p.max_norm, p.grad_dtype);
+  // The chunks of all leaves form one sequence, cut into runs of p.run_chunks consecutive chunks; block b
+  // takes runs b, b + grid, b + 2 grid, ...  Inside a run every address advances by compile-time
+  // constants; dealing the runs out in turn spreads regions that cost more (rows at rest, ragged ends,
+  // values outside the shortcuts' ranges) over all blocks.
   const uint32_t total = p.first_block[p.n_leaves];
-  const uint32_t per = (total + gridDim.x - 1) / gridDim.x;
-  uint32_t c = blockIdx.x * per;  // this block's next position in the sequence
-  const uint32_t c_hi = min(total, c + per);
-  constexpr uint32_t grid = 1u;   // a block's chunks are consecutive
-  for (int l = 0; l < p.n_leaves; ++l) {
+  constexpr uint32_t grid = 1u;   // chunk stride inside a run
+  for (uint32_t run0 = blockIdx.x * p.run_chunks; run0 < total; run0 += gridDim.x * p.run_chunks) {
+  uint32_t c = run0;  // this block's next position in the sequence
+  const uint32_t c_hi = min(total, run0 + p.run_chunks);
+  int l_first = 0;
+  for (int l_end = p.n_leaves; l_end - l_first > 1;) {  // the leaf that holds position c
+    const int mid = (l_first + l_end) >> 1;
+    if (p.first_block[mid] <= c) l_first = mid; else l_end = mid;
+  }
+  for (int l = l_first; l < p.n_leaves; ++l) {
     const uint32_t first = p.first_block[l];
     if (c >= c_hi) break;
     const uint32_t next = min(p.first_block[l + 1], c_hi);
@@ -1464,6 +1567,7 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
     for (; ch < end; ch += grid)
       cold_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, (unsigned long long)ch * kChunk, lut_m, lut_v, p.peers, clip);
     c = first + ch;
+  }
   }
 }
 
@@ -1624,6 +1728,17 @@ cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStre
   p.stages = stages;
   unsigned int grid = (unsigned int)info.sm_count * blocks_per_sm;
   if (grid > info.total_chunks) grid = info.total_chunks;
+  // Run length: at most FO_RUN_MAX chunks (filling and draining the copy pipeline at a run's ends costs
+  // about one chunk's time, 0.5 % of such a run), and for small launches a quarter of a block's share,
+  // rounded up, so that no block gets more than four runs.
+#ifndef FO_RUN_DIV
+#define FO_RUN_DIV 4u
+#endif
+#ifndef FO_RUN_MAX
+#define FO_RUN_MAX 192u
+#endif
+  unsigned int run = (info.total_chunks + grid * FO_RUN_DIV - 1u) / (grid * FO_RUN_DIV);
+  p.run_chunks = run < 1u ? 1u : (run > FO_RUN_MAX ? FO_RUN_MAX : run);
   kernel<<<grid, kThreads, dynamic_smem, s>>>(p);
   return cudaGetLastError();
 }

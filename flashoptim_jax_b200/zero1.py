@@ -215,6 +215,11 @@ class Zero1Optimizer:
         # leaves of one param group share one config object, so per-step scalars are derived once per group
         interned: Dict[Any, Dict[str, Any]] = {}
         self.configs = [interned.setdefault(tuple(sorted(c.items(), key=lambda kv: kv[0])), c) for c in self.configs]
+        self._group_configs: List[Dict[str, Any]] = []
+        for c in self.configs:
+            if not any(c is g for g in self._group_configs):
+                self._group_configs.append(c)
+        self._group_id = [next(i for i, g in enumerate(self._group_configs) if g is c) for c in self.configs]
         for c in self.configs:
             if c["quantize"] and c["group_size"] != 32:
                 raise ValueError("Zero1Optimizer shards on 32-element group boundaries: group_size must be 32")
@@ -396,6 +401,37 @@ class Zero1Optimizer:
         self._static_work = [(w, leaf, b, sl) for w, (leaf, b, sl) in zip(work, meta)]
         return work
 
+    def _run(self, tag: Tuple[Any, ...], pick: Callable[[int, int, int], bool], peers=None, grad_peers=None,
+             mc_param: int = 0, mc_grad: int = 0) -> int:
+        """Step kernels for the segments `pick(leaf, bucket, slice)` selects.  With the default step function the
+        descriptor tables of a selection are built once (tag names the selection) and only the hyper-parameters
+        are refreshed per step; an injected step function gets the list of LeafWork as before."""
+        if self._step_fn is not eng.launch:
+            work = self.local_work()
+            items = [w for w, (_, leaf, b, sl) in zip(work, self._static_work) if pick(leaf, b, sl)]
+            if not items:
+                return 0
+            if peers is None and grad_peers is None and not mc_param and not mc_grad:
+                return self._step_fn(self.opt_code, items)
+            return self._step_fn(self.opt_code, items, peers, grad_peers, mc_param, mc_grad)
+        if getattr(self, "_static_work", None) is None:
+            self.local_work()
+        plans = self.__dict__.setdefault("_plans", {})
+        key = (tag, peers is not None, grad_peers is not None, bool(mc_param), bool(mc_grad))
+        plan = plans.get(key)
+        if plan is None:
+            chosen = [(w, self._group_id[leaf]) for w, leaf, b, sl in self._static_work if pick(leaf, b, sl)]
+            plan = plans[key] = eng.PreparedLaunch(self.opt_code, [w for w, _ in chosen], [g for _, g in chosen],
+                                                   peers, grad_peers, mc_param, mc_grad) if chosen else None
+        if plan is None:
+            return 0
+        count_before = torch.tensor(self.count, dtype=torch.int32)
+        hypers = {}
+        for gid, config in enumerate(self._group_configs):
+            lr = utils._resolve_learning_rate(config["learning_rate"], count_before)
+            hypers[gid] = self._hyper(config, lr, self.count + 1)
+        return plan.run(hypers)
+
     def _slices(self) -> List[Tuple[int, int]]:
         """(bucket, slice) pairs in the order the collectives are issued."""
         return [(b, sl) for b, layout in enumerate(self.buckets) for sl in range(layout.n_slices)]
@@ -429,10 +465,6 @@ class Zero1Optimizer:
         """Slice by slice: the kernels of slice s run while the reduce-scatter of slice s+1 is in flight, and
         each all-gather is queued as soon as its slice is updated (NCCL serialises them behind the
         reduce-scatters on its own stream).  Device-side ordering only; the host never waits."""
-        work = self.local_work()
-        per_slice: Dict[Tuple[int, int], List[eng.LeafWork]] = {}
-        for w, (_, _, b, sl) in zip(work, self._static_work):
-            per_slice.setdefault((b, sl), []).append(w)
         order = self._slices()
         rs = []
         for b, sl in order:
@@ -441,9 +473,7 @@ class Zero1Optimizer:
         ag = []
         for handle, (b, sl) in zip(rs, order):
             handle.wait()  # the compute stream waits for this slice's gradients
-            items = per_slice.get((b, sl))
-            if items:
-                self._step_fn(self.opt_code, items)
+            self._run(("slice", b, sl), lambda _leaf, wb, wsl, b=b, sl=sl: wb == b and wsl == sl)
             full, piece = self._ag_args(b, sl)
             mine = full[self.rank * piece:(self.rank + 1) * piece]
             ag.append(dist.all_gather_into_tensor(full, mine, group=self.group, async_op=True))
@@ -464,8 +494,6 @@ class Zero1Optimizer:
             for dst, src in zip(mine, leaves):
                 dst.copy_(as_tensor(src).reshape(dst.shape), non_blocking=True)
             return self.step()
-        work = self.local_work()  # one item per leaf on a single rank
-        by_leaf: Dict[int, eng.LeafWork] = {leaf: w for w, (_, leaf, _, _) in zip(work, self._static_work)}
         total = sum(t.numel() * t.element_size() for t in mine)
         main = torch.cuda.current_stream(self.device)
         if getattr(self, "_copy_stream", None) is None:
@@ -486,9 +514,8 @@ class Zero1Optimizer:
                 done = torch.cuda.Event()
                 done.record(copier)
             main.wait_event(done)
-            items = [by_leaf[i] for i in group if i in by_leaf]
-            if items:
-                self._step_fn(self.opt_code, items)
+            chosen = frozenset(group)  # every segment of these leaves (a leaf that straddles slices has several)
+            self._run(("leaves", tuple(group)), lambda leaf, _b, _sl: leaf in chosen)
             group = []
 
         for i in order:
@@ -501,25 +528,43 @@ class Zero1Optimizer:
         self.count += 1
         return self.params
 
-    def step(self, grads: Any = None) -> Any:
+    ALL_PHASES = ("reduce_scatter", "step", "all_gather")
+
+    def step(self, grads: Any = None, phases: Tuple[str, ...] = ALL_PHASES) -> Any:
         """One optimizer step.  `grads` (optional) is copied into the flat gradient buffers;
-        leave it out when backward already wrote into `self.grads`.  Returns `self.params`."""
+        leave it out when backward already wrote into `self.grads`.  Returns `self.params`.
+
+        `phases` is for measurement: leaving "reduce_scatter" out steps on this rank's own gradients,
+        leaving "all_gather" out keeps the updated slice local (the replicas then disagree; the state
+        is of no further use).  The default runs the whole ZeRO-1 step."""
+        unknown = set(phases) - set(self.ALL_PHASES)
+        if unknown or "step" not in phases:
+            raise ValueError(f"phases must contain 'step' and only names of {self.ALL_PHASES}, got {phases}")
+        do_rs, do_ag = "reduce_scatter" in phases, "all_gather" in phases
         if grads is not None:
             leaves, treedef = pytree.tree_flatten(grads)
             if treedef != self.treedef:
                 raise ValueError(f"{self.name} gradients must match parameter structure")
             for mine, theirs in zip(pytree.tree_leaves(self.grads), leaves):
-                mine.copy_(as_tensor(theirs).to(mine.dtype).reshape(mine.shape))
+                theirs = as_tensor(theirs)
+                if theirs.dtype != mine.dtype and theirs.element_size() > mine.element_size():
+                    # the flat gradient buffers (and the reduce-scatter) have the parameters' dtype
+                    raise TypeError(f"{self.name}: a {theirs.dtype} gradient would be narrowed to the {mine.dtype} gradient "
+                                    "buffer of its leaf; cast it yourself or write into `.grads` directly")
+                mine.copy_(theirs.to(mine.dtype).reshape(mine.shape))
         if self._pipelined():
+            if not (do_rs and do_ag):
+                raise ValueError("the sliced pipeline runs whole steps only")
             self._step_pipelined()
             self.count += 1
             return self.params
-        if self.fused_reduce_scatter:
-            dist.all_reduce(self._token, group=self.group)  # every rank's gradients are complete before any kernel reads them
-        else:
-            self.reduce_scatter_grads()
+        if do_rs:
+            if self.fused_reduce_scatter:
+                dist.all_reduce(self._token, group=self.group)  # every rank's gradients are complete before any kernel reads them
+            else:
+                self.reduce_scatter_grads()
         with self._clip_context():
-            return self._launch_and_gather()
+            return self._launch_and_gather(do_rs, do_ag)
 
     def _clip_context(self):
         """Global-norm clipping for the launches of this step: the squares of this rank's slices (padding is
@@ -531,25 +576,26 @@ class Zero1Optimizer:
             dist.all_reduce(sq, group=self.group)
         return eng.grad_clip(sq, self.max_grad_norm)
 
-    def _launch_and_gather(self) -> Any:
+    def _launch_and_gather(self, do_rs: bool = True, do_ag: bool = True) -> Any:
         if self.fused_allgather or self.fused_reduce_scatter:
-            work = self.local_work()
             for b in range(len(self.buckets)):
-                items = [w for w, (_, _, wb, _) in zip(work, self._static_work) if wb == b]
-                if items:
-                    self._step_fn(self.opt_code, items, self.peer_offsets[b] if self.fused_allgather else None,
-                                  self.peer_grad_offsets[b] if self.fused_reduce_scatter else None,
-                                  self.mc_param_offsets[b], self.mc_grad_offsets[b])
+                self._run(("bucket", b), lambda _leaf, wb, _sl, b=b: wb == b,
+                          self.peer_offsets[b] if (self.fused_allgather and do_ag) else None,
+                          self.peer_grad_offsets[b] if (self.fused_reduce_scatter and do_rs) else None,
+                          self.mc_param_offsets[b] if do_ag else 0, self.mc_grad_offsets[b] if do_rs else 0)
             self.count += 1
             if self.fused_allgather:
                 # all ranks' kernels are complete: their stores into this replica, their reads of these gradients
                 dist.all_reduce(self._token, group=self.group)
-            else:
+            elif do_ag:
                 self.all_gather_params()  # a collective, hence also the barrier that protects the gradients
+            elif self.fused_reduce_scatter and do_rs:
+                dist.all_reduce(self._token, group=self.group)
             return self.params
-        self._step_fn(self.opt_code, self.local_work())
+        self._run(("all",), lambda _leaf, _b, _sl: True)
         self.count += 1
-        self.all_gather_params()
+        if do_ag:
+            self.all_gather_params()
         return self.params
 
     # ---- checkpoint / export -------------------------------------------------------------------------
