@@ -998,7 +998,8 @@ FO_DEVI float sign_of(float x);
 
 template <int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
 __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base,
-                                        const float one, const float* lut_mw, const Peers& peers, const Clip* clip);
+                                        const float one, const float* lut_mw, const Peers& peers, const Clip* clip,
+                                        const uint32_t n_limit);
 
 // Second half of a hot chunk: update, split, requantize, store.  Each stage runs its packed
 // shortcut unconditionally.
@@ -1010,7 +1011,8 @@ __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const in
 // The stored bits are those of the IEEE path in every case.
 template <bool REPAIR, int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
 FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base, const Piece& at, const float one,
-                        bool rare, Unpacked& u, const float* lut_mw, const Peers& peers, const Clip* clip) {
+                        bool rare, Unpacked& u, const float* lut_mw, const Peers& peers, const Clip* clip,
+                        const int n_valid = kPiece, const bool group_valid = true) {
   using namespace fast2;
   const float2 one2 = sp(one);
   float2 (&g)[4] = u.g;
@@ -1180,11 +1182,43 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
         // no new first moment of the warp differs from zero: look whether the whole piece is at rest
         if (__all_sync(0xFFFFFFFFu, am_lane == 0.0f) && zero_chunk<OPT, PDT, ECC_BITS>(h.flags, h.wd, h.decay, gdt, one, at.grad, at.param, at.ecc, at.mu, at.nu, at.msc, at.vsc)) return;
       }
-      warm_chunk<OPT, PDT, ECC_BITS, STATE, AUX>(L, h, gdt, base, one, lut_mw, peers, clip);
+      warm_chunk<OPT, PDT, ECC_BITS, STATE, AUX>(L, h, gdt, base, one, lut_mw, peers, clip, 0xFFFFFFFFu);
       return;
     }
   }
   // ---- stores ---------------------------------------------------------------------------------------------
+  if constexpr (REPAIR) {
+    // the ragged end of a leaf (repairing pass only): the piece that straddles the end stores its
+    // valid elements one by one, pieces beyond it store nothing; a group's scale is stored by the
+    // lanes of a group that has an element at all
+    if (n_valid < kPiece) {
+      for (int j = 0; j < n_valid; ++j) {
+        const float2 t = theta[j >> 1];
+        if constexpr (PDT == FO_F32) {
+          ((float*)at.param)[j] = (j & 1) ? t.y : t.x;
+        } else {
+          ((unsigned short*)at.param)[j] = (unsigned short)(nw[j >> 1] >> (16 * (j & 1)));
+          const uint32_t ew[4] = {ecc_out.x, ecc_out.y, ecc_out.z, ecc_out.w};
+          if constexpr (ECC_BITS == 16) ((unsigned short*)at.ecc)[j] = (unsigned short)(ew[j >> 1] >> (16 * (j & 1)));
+          if constexpr (ECC_BITS == 8) ((unsigned char*)at.ecc)[j] = (unsigned char)(ew[j >> 2] >> (8 * (j & 3)));
+        }
+        if constexpr (STATE == FO_STATE_FULL) {
+          ((float*)at.mu)[j] = (j & 1) ? m[j >> 1].y : m[j >> 1].x;
+          if constexpr (OPT == FO_OPT_ADAM) ((float*)at.nu)[j] = (j & 1) ? v[j >> 1].y : v[j >> 1].x;
+        } else if constexpr (STATE == FO_STATE_QUANT) {
+          ((unsigned char*)at.mu)[j] = (unsigned char)(((j & 4) ? mq.y : mq.x) >> (8 * (j & 3)));
+          if constexpr (OPT == FO_OPT_ADAM) ((unsigned char*)at.nu)[j] = (unsigned char)(((j & 4) ? vq.y : vq.x) >> (8 * (j & 3)));
+        }
+      }
+      if constexpr (STATE == FO_STATE_QUANT) {
+        if (group_valid) {
+          *(__half*)at.msc = __float2half_rn(am);
+          if constexpr (OPT == FO_OPT_ADAM) *(__half*)at.vsc = __float2half_rn(av);
+        }
+      }
+      return;
+    }
+  }
   if constexpr (PDT == FO_F32) {
     const float4 lo = make_float4(theta[0].x, theta[0].y, theta[1].x, theta[1].y);
     const float4 hi = make_float4(theta[2].x, theta[2].y, theta[3].x, theta[3].y);
@@ -1230,18 +1264,77 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
   }
 }
 
+// words of eight consecutive elements of which only the first n_valid exist (the rest read as zero)
+template <int BYTES>
+FO_DEVI void masked_words(const void* src, const int n_valid, uint32_t (&w)[2 * BYTES]) {
+#pragma unroll
+  for (int k = 0; k < 2 * BYTES; ++k) w[k] = 0u;
+  for (int j = 0; j < n_valid; ++j) {
+    if constexpr (BYTES == 4) w[j] = ((const uint32_t*)src)[j];
+    if constexpr (BYTES == 2) w[j >> 1] |= (uint32_t)((const unsigned short*)src)[j] << (16 * (j & 1));
+    if constexpr (BYTES == 1) w[j >> 2] |= (uint32_t)((const unsigned char*)src)[j] << (8 * (j & 3));
+  }
+}
+template <int OPT, int PDT, int ECC_BITS, int STATE>
+__device__ __noinline__ void masked_load(const Piece& at, const int gdt, const int n_valid, Raw<OPT, PDT, ECC_BITS, STATE>& r) {
+  uint32_t w4[8], w2[4], w1[2];
+  if constexpr (PDT == FO_F32) {
+    masked_words<4>(at.param, n_valid, w4);
+    r.p0 = make_uint4(w4[0], w4[1], w4[2], w4[3]); r.p1 = make_uint4(w4[4], w4[5], w4[6], w4[7]);
+  } else {
+    masked_words<2>(at.param, n_valid, w2);
+    r.p0 = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+  }
+  if constexpr (ECC_BITS == 16) { masked_words<2>(at.ecc, n_valid, w2); r.e = make_uint4(w2[0], w2[1], w2[2], w2[3]); }
+  if constexpr (ECC_BITS == 8) { masked_words<1>(at.ecc, n_valid, w1); r.e.x = w1[0]; r.e.y = w1[1]; }
+  if constexpr (STATE == FO_STATE_QUANT) {
+    masked_words<1>(at.mu, n_valid, w1); r.mq = make_uint2(w1[0], w1[1]);
+    if constexpr (OPT == FO_OPT_ADAM) { masked_words<1>(at.nu, n_valid, w1); r.vq = make_uint2(w1[0], w1[1]); }
+  } else if constexpr (STATE == FO_STATE_FULL) {
+    masked_words<4>(at.mu, n_valid, w4);
+    r.m0 = make_uint4(w4[0], w4[1], w4[2], w4[3]); r.m1 = make_uint4(w4[4], w4[5], w4[6], w4[7]);
+    if constexpr (OPT == FO_OPT_ADAM) {
+      masked_words<4>(at.nu, n_valid, w4);
+      r.v0 = make_uint4(w4[0], w4[1], w4[2], w4[3]); r.v1 = make_uint4(w4[4], w4[5], w4[6], w4[7]);
+    }
+  }
+  if (gdt == FO_F32) {
+    masked_words<4>(at.grad, n_valid, w4);
+    r.g0 = make_uint4(w4[0], w4[1], w4[2], w4[3]); r.g1 = make_uint4(w4[4], w4[5], w4[6], w4[7]);
+  } else {
+    masked_words<2>(at.grad, n_valid, w2);
+    r.g0 = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+  }
+}
+
 // Second chance for a warp whose first pass met a value outside a shortcut's range: the same
 // packed arithmetic from a fresh load, with per-lane IEEE repairs.  About twice the cost of a
 // first pass for that warp, against about seven times for the scalar IEEE path.
+// Also the path of a leaf's ragged last chunk: elements from n_limit on do not exist; they read as
+// zeros (flashoptim_jax/quantization.py:20-26) and nothing is stored for them.  Warps that lie wholly
+// beyond the end return at once.  (Not with peer replicas: their stores are whole vectors.)
 template <int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
 __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base,
-                                        const float one, const float* lut_mw, const Peers& peers, const Clip* clip) {
+                                        const float one, const float* lut_mw, const Peers& peers, const Clip* clip,
+                                        const uint32_t n_limit) {
+  const uint32_t i0 = base + threadIdx.x * kPiece;
+  if ((i0 & ~255u) >= n_limit) return;  // the warp's first element: the same answer in all its lanes
+  const int n_valid = i0 >= n_limit ? 0 : (n_limit - i0 < (uint32_t)kPiece ? (int)(n_limit - i0) : kPiece);
+  const bool group_valid = (i0 & ~31u) < n_limit;
+  const Piece at = piece_at<PDT, ECC_BITS, STATE>(L, gdt, i0);
   Raw<OPT, PDT, ECC_BITS, STATE> raw;
-  hot_load<OPT, PDT, ECC_BITS, STATE>(L, gdt, base + threadIdx.x * kPiece, raw);
+  if (n_valid == kPiece) {
+    hot_load<OPT, PDT, ECC_BITS, STATE>(L, gdt, i0, raw);
+  } else {
+    masked_load<OPT, PDT, ECC_BITS, STATE>(at, gdt, n_valid, raw);
+    if constexpr (STATE == FO_STATE_QUANT) {
+      raw.msc = group_valid ? *(const __half*)at.msc : __float2half(0.0f);
+      if constexpr (OPT == FO_OPT_ADAM) raw.vsc = group_valid ? *(const __half*)at.vsc : __float2half(0.0f);
+    }
+  }
   Unpacked u;
   hot_unpack<true, OPT, PDT, ECC_BITS, STATE>(raw, gdt, lut_mw, one, u);
   if (AUX && peers.ng > 0) {
-    const uint32_t i0 = base + threadIdx.x * kPiece;
     merge_peer_grads<true>(u.g, gdt, peers, [&](int r, uint4& w0, uint4& w1) {
       const char* g = (const char*)L.grad + peers.gdelta[r];
       if (gdt == FO_F32) {
@@ -1253,8 +1346,7 @@ __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const in
     });
   }
   if (AUX && clip->active) clip_grads<true>(u.g, gdt, *clip);
-  const Piece at = piece_at<PDT, ECC_BITS, STATE>(L, gdt, base + threadIdx.x * kPiece);
-  hot_finish<true, OPT, PDT, ECC_BITS, STATE, AUX>(L, h, gdt, base, at, one, false, u, lut_mw, peers, clip);
+  hot_finish<true, OPT, PDT, ECC_BITS, STATE, AUX>(L, h, gdt, base, at, one, false, u, lut_mw, peers, clip, n_valid, group_valid);
 }
 
 // One block's run of consecutive whole chunks [ch, hot_end) of a leaf, for the kernel without peer or
@@ -1564,8 +1656,18 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
         hot_finish<false, OPT, PDT, ECC_BITS, STATE, AUX>(L, h, p.grad_dtype, base, at, p.one, rare, u, lut_mw, p.peers, AUX ? &clip : nullptr);
       }
     }
-    for (; ch < end; ch += grid)
-      cold_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, (unsigned long long)ch * kChunk, lut_m, lut_v, p.peers, clip);
+    // what is left of the leaf in this run: its ragged last chunk, or all of a leaf the straight-line path
+    // does not take.  An aligned leaf under ordinary hyper-parameters goes through the repairing pass with
+    // a limit (vector accesses, masked at the end); the scalar path keeps unaligned leaves, the CPU-path
+    // parameter hand-back and peer replicas.
+    const bool vector_ok = leaf_is_hot<OPT>(p, l) && hyper_ok &&
+                           (!AUX || (p.peers.n == 0 && p.peers.ng == 0 && p.peers.mc_pdelta == 0 && p.peers.mc_gdelta == 0));
+    for (; ch < end; ch += grid) {
+      if (vector_ok)
+        warm_chunk<OPT, PDT, ECC_BITS, STATE, AUX>(L, h, p.grad_dtype, ch * (uint32_t)kChunk, p.one, lut_mw, p.peers, AUX ? &clip : nullptr, (uint32_t)L.n);
+      else
+        cold_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, (unsigned long long)ch * kChunk, lut_m, lut_v, p.peers, clip);
+    }
     c = first + ch;
   }
   }
