@@ -43,9 +43,11 @@ _KINDS = (("quant", 0), ("full", 1), ("generic", 3))
 _SHAPES = {("adam", 0): (512, 1), ("lion", 0): (768, 1)}
 
 
-def _units(shapes=None) -> List[Tuple[str, str, List[str]]]:
+def _units(shapes=None, ffi_dir: str | None = None) -> List[Tuple[str, str, List[str]]]:
     shapes = _SHAPES if shapes is None else shapes
     units = [(name, name + ".cu", []) for name in ("fo_api", "fo_codec", "fo_selftest", "fo_norm")]
+    if ffi_dir is not None:
+        units.append(("fo_ffi", "fo_ffi.cc", ["-x", "cu", f"-I{ffi_dir}"]))
 
     def step_unit(oname: str, omacro: str, kname: str, kind: int, aux: int | None):
         suffix = "" if aux is None else ("_aux" if aux else "_plain")
@@ -68,6 +70,18 @@ def _units(shapes=None) -> List[Tuple[str, str, List[str]]]:
     return units
 
 
+def ffi_include_dir() -> str | None:
+    """Directory of jaxlib's XLA FFI headers (xla/ffi/api/ffi.h), or None when jax is not installed.
+    The jax.ffi shim (csrc/fo_ffi.cc) is compiled into the library only when this resolves."""
+    try:
+        import jax.ffi  # noqa: PLC0415
+
+        path = jax.ffi.include_dir()
+    except Exception:  # jax absent, or too old to have jax.ffi
+        return None
+    return path if os.path.exists(os.path.join(path, "xla", "ffi", "api", "ffi.h")) else None
+
+
 def _nvcc() -> str:
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
@@ -79,7 +93,7 @@ def _sources_digest(extra: List[str], units=None) -> str:
     h = hashlib.sha256()
     for root in (CSRC, os.path.join(os.path.dirname(HERE), "include")):
         for name in sorted(os.listdir(root)):
-            if name.endswith((".cu", ".cuh", ".h")):
+            if name.endswith((".cu", ".cuh", ".h", ".cc")):
                 with open(os.path.join(root, name), "rb") as f:
                     h.update(name.encode())
                     h.update(f.read())
@@ -93,7 +107,7 @@ def build_native(force: bool = False, jobs: int | None = None, extra_flags: List
     """Compile every CUDA source for sm_100a and link the shared object; returns its path.
     `shapes` overrides the block shapes of the step slices ({(optimizer, aux): (threads, blocks per SM)})."""
     extra = list(extra_flags or [])
-    units = _units(shapes)
+    units = _units(shapes, ffi_include_dir())
     os.makedirs(OBJ_DIR, exist_ok=True)
     os.makedirs(os.path.dirname(lib_path), exist_ok=True)
     stamp = lib_path + ".digest"

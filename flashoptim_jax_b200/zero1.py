@@ -622,6 +622,198 @@ class Zero1Optimizer:
                 if mine is not None:
                     mine.copy_(entry[name])
 
+    # -- unsharded state in the reference's layout, assembled on the device ----------------------------------
+
+    _STREAMS = ("ecc", "mu", "mu_scales", "nu", "nu_scales")
+
+    def _gather_stream(self, b: int, name: str) -> Optional[torch.Tensor]:
+        """The flat buffer of one state stream of bucket b, assembled from all ranks' slices with one
+        all-gather per slice, on the device the state lives on (no host copy).  Element i of the result belongs
+        to position i of the bucket's flat parameter buffer (i // 32 for the group scales).  None when no leaf
+        of the bucket has the stream; mixed dtypes inside a bucket (param groups that differ in
+        master_weight_bits) are not handled here."""
+        layout = self.buckets[b]
+        mine = [(seg, getattr(self.state[(b, s)], name)) for s, seg in enumerate(layout.segments[self.rank])]
+        # every rank must agree on dtype and presence without talking: derive both from the configs
+        kinds = set()
+        for leaf in layout.leaves:
+            c = self.configs[leaf]
+            has_ecc = layout.dtype in (torch.bfloat16, torch.float16) and c["master_weight_bits"] in (24, 32)
+            quant, mom = c["quantize"], self._uses_momentum(c)
+            if name == "ecc":
+                kinds.add((torch.int8 if c["master_weight_bits"] == 24 else torch.int16) if has_ecc else None)
+            elif name in ("mu", "nu"):
+                present = mom and (name == "mu" or self.opt_code == _lib.FO_OPT_ADAM)
+                kinds.add(None if not present else ((torch.int8 if name == "mu" else torch.uint8) if quant else torch.float32))
+            else:
+                present = mom and quant and (name == "mu_scales" or self.opt_code == _lib.FO_OPT_ADAM)
+                kinds.add(torch.float16 if present else None)
+        if kinds == {None}:
+            return None
+        if len(kinds) != 1:
+            raise NotImplementedError("state_dict(): leaves of one dtype bucket differ in how they store " + name)
+        dtype = kinds.pop()
+        per = 32 if name.endswith("scales") else 1
+        piece, world = layout.piece // per, self.world_size
+        full = torch.zeros(layout.n_slices * world * piece, dtype=dtype, device=self.device)
+        for seg, t in mine:
+            at = flat_position(layout, self.rank, seg.offset) // per
+            full[at:at + t.numel()].copy_(t)
+        raw = full.view(torch.uint8)  # bytes travel: every backend carries uint8, not every one int16 / fp16
+        width = full.element_size()
+        for sl in range(layout.n_slices):
+            _all_gather_inplace(raw[sl * world * piece * width:(sl + 1) * world * piece * width], piece * width, self.group, world)
+        return full
+
+    def state_dict(self) -> Dict[str, Any]:
+        """The optimizer state in the reference's checkpoint form (flashoptim_jax/adamw.py:639-644, lion.py:234-239,
+        sgd.py:314-319 over utils.py:377-407): {"count", "mu", ["nu",] "ecc"}, each tree serialised leaf by leaf as
+        {"kind": "quantized", "values", "scales"} or {"kind": "array", "value"}.  Collective: every rank calls it and
+        every rank gets the whole state; the slices travel device to device (one all-gather per state stream)."""
+        from .quantization import QuantizedArray
+
+        n_leaves = len(self.shapes)
+        ecc: List[Any] = [None] * n_leaves
+        mu: List[Any] = [None] * n_leaves
+        nu: List[Any] = [None] * n_leaves
+        for b, layout in enumerate(self.buckets):
+            flat = {name: self._gather_stream(b, name) for name in self._STREAMS}
+            for leaf, start, n in zip(layout.leaves, layout.starts, layout.sizes):
+                shape, groups = self.shapes[leaf], -(-n // 32)
+                take = lambda name: None if flat[name] is None else (  # noqa: E731
+                    flat[name][start // 32:start // 32 + groups] if name.endswith("scales") else flat[name][start:start + n].view(shape)).clone()
+                sentinel = lambda: torch.zeros((), dtype=torch.int32, device=self.device)  # noqa: E731
+                ecc[leaf] = take("ecc") if flat["ecc"] is not None else sentinel()
+                for vals, scales, out in (("mu", "mu_scales", mu), ("nu", "nu_scales", nu)):
+                    if flat[vals] is None:
+                        out[leaf] = sentinel()
+                    elif flat[scales] is not None:
+                        out[leaf] = QuantizedArray(values=take(vals), scales=take(scales))
+                    else:
+                        out[leaf] = take(vals)
+        sd = {"count": torch.tensor(self.count, dtype=torch.int32), "mu": utils._tree_state_dict(self.treedef.unflatten(mu)),
+              "ecc": utils._tree_state_dict(self.treedef.unflatten(ecc))}
+        if self.opt_code == _lib.FO_OPT_ADAM:
+            sd["nu"] = utils._tree_state_dict(self.treedef.unflatten(nu))
+        return sd
+
+    def load_state_dict(self, sd: Dict[str, Any]) -> None:
+        """Inverse of state_dict(), for any world size: every rank copies the slices it owns out of the
+        unsharded trees (which may live on the host or on any device)."""
+        from .quantization import QuantizedArray
+
+        trees = {name: pytree.tree_leaves(utils._tree_from_state_dict(sd[name]), is_leaf=lambda x: isinstance(x, QuantizedArray))
+                 for name in ("mu", "nu", "ecc") if name in sd}
+        for name, leaves in trees.items():
+            if len(leaves) != len(self.shapes):
+                raise ValueError(f"{self.name} state trees must match parameter structure")
+        self.count = int(sd["count"])
+        for (b, s), st in self.state.items():
+            seg = self.buckets[b].segments[self.rank][s]
+            glo, ghi = seg.lo // 32, -(-seg.hi // 32)
+
+            def put(dst, src, lo, hi):
+                if dst is None:
+                    return
+                src = as_tensor(src).reshape(-1)
+                if src.dtype != dst.dtype or src.numel() < hi:
+                    raise ValueError(f"{self.name} state of leaf {seg.leaf} does not fit this optimizer's layout")
+                dst.copy_(src[lo:hi])
+
+            if st.ecc is not None:
+                put(st.ecc, trees["ecc"][seg.leaf], seg.lo, seg.hi)
+            for vals, scales, key in ((st.mu, st.mu_scales, "mu"), (st.nu, st.nu_scales, "nu")):
+                if vals is None:
+                    continue
+                leaf = trees[key][seg.leaf]
+                if isinstance(leaf, QuantizedArray):
+                    put(vals, leaf.values, seg.lo, seg.hi)
+                    put(scales, leaf.scales, glo, ghi)
+                else:
+                    put(vals, leaf, seg.lo, seg.hi)
+
+    def master_weights(self) -> Any:
+        """reconstruct_weights for the sharded optimizer (flashoptim_jax/compression.py:124-126, README "export"):
+        the fp32 master weights as a tree like `params`.  Collective: the ECC slices are all-gathered on the
+        device, then every rank reconstructs (the reconstruction kernel, one pass over parameter + ECC)."""
+        from .compression import reconstruct_leaf
+
+        out: List[Any] = [None] * len(self.shapes)
+        param_leaves = pytree.tree_leaves(self.params)
+        for b, layout in enumerate(self.buckets):
+            ecc = self._gather_stream(b, "ecc")
+            for leaf, start, n in zip(layout.leaves, layout.starts, layout.sizes):
+                p = param_leaves[leaf]
+                out[leaf] = p.to(torch.float32) if ecc is None else reconstruct_leaf(p, ecc[start:start + n].view(self.shapes[leaf]))
+        return self.treedef.unflatten(out)
+
+    def set_master_weights(self, fp32_params: Any) -> Any:
+        """set_fp32_params for the sharded optimizer (flashoptim_jax/compression.py:129-146, README "import"):
+        every rank splits the slices it owns into stored parameter + ECC (the split kernel), then the updated
+        parameters are all-gathered.  The moments are left as they are.  Returns `self.params`."""
+        from .compression import split_leaf
+
+        leaves, treedef = pytree.tree_flatten(fp32_params)
+        if treedef != self.treedef:
+            raise ValueError("fp32_params and param_template must have matching tree structure")
+        for (b, s), st in self.state.items():
+            layout = self.buckets[b]
+            seg = layout.segments[self.rank][s]
+            at = flat_position(layout, self.rank, seg.offset)
+            src = as_tensor(leaves[seg.leaf]).reshape(-1)[seg.lo:seg.hi].to(device=self.device, dtype=torch.float32)
+            mwb = self.configs[seg.leaf]["master_weight_bits"] if st.ecc is not None else None
+            lp, ecc = split_leaf(src, narrow_dtype=layout.dtype, master_weight_bits=mwb)
+            self.flat_params[b][at:at + (seg.hi - seg.lo)].copy_(lp)
+            if st.ecc is not None:
+                st.ecc.copy_(ecc)
+        self.all_gather_params()
+        return self.params
+
+    # -- per-rank files -----------------------------------------------------------------------------------------
+
+    SHARD_FORMAT = 1
+
+    def save_shards(self, directory: str) -> str:
+        """Writes this rank's slice of the state to `directory` (every rank calls it; no communication):
+        `shard_<rank>_of_<world>.pt` holds a header (format number, optimizer, step count, the table of
+        segments with their leaf paths and element ranges) and the slice's tensors on the host.  Reload
+        with load_shards on the same world size, or convert with state_dict() / load_state_dict() to move to
+        another."""
+        import os as _os
+
+        _os.makedirs(directory, exist_ok=True)
+        path = _os.path.join(directory, f"shard_{self.rank:05d}_of_{self.world_size:05d}.pt")
+        segments = []
+        for (b, s), st in sorted(self.state.items()):
+            seg = self.buckets[b].segments[self.rank][s]
+            segments.append({"bucket": b, "index": s, "leaf": seg.leaf, "path": "/".join(str(x) for x in self.paths[seg.leaf]),
+                             "lo": seg.lo, "hi": seg.hi, "tensors": {k: v.detach().cpu() for k, v in st._asdict().items() if v is not None}})
+        torch.save({"format": self.SHARD_FORMAT, "optimizer": self.name, "count": self.count, "world_size": self.world_size,
+                    "rank": self.rank, "leaf_shapes": [list(x) for x in self.shapes], "segments": segments}, path)
+        return path
+
+    def load_shards(self, directory: str) -> None:
+        import os as _os
+
+        path = _os.path.join(directory, f"shard_{self.rank:05d}_of_{self.world_size:05d}.pt")
+        if not _os.path.exists(path):
+            raise FileNotFoundError(f"{path}: no shard for rank {self.rank} of {self.world_size} (saved with another world size? "
+                                    "use state_dict() / load_state_dict() to re-shard)")
+        blob = torch.load(path, map_location="cpu", weights_only=False)
+        if blob.get("format") != self.SHARD_FORMAT or blob["optimizer"] != self.name:
+            raise ValueError(f"{path} is not a format-{self.SHARD_FORMAT} shard of {self.name}")
+        if [list(x) for x in self.shapes] != blob["leaf_shapes"]:
+            raise ValueError(f"{path} was saved for a different parameter tree")
+        for entry in blob["segments"]:
+            key = (entry["bucket"], entry["index"])
+            seg = self.buckets[key[0]].segments[self.rank][key[1]]
+            if (entry["leaf"], entry["lo"], entry["hi"]) != (seg.leaf, seg.lo, seg.hi):
+                raise ValueError(f"segment {key} of {path} does not match this layout")
+            for name, mine in self.state[key]._asdict().items():
+                if mine is not None:
+                    mine.copy_(entry["tensors"][name])
+        self.count = int(blob["count"])
+
     def gather_state(self, dst: int = 0) -> Optional[Dict[str, Any]]:
         """Assemble the reference's unsharded state on rank `dst`: {"count", "mu", "nu", "ecc"} trees with
         the layout tx.init() gives (QuantizedArray leaves, 0-d int32 sentinels)."""

@@ -95,11 +95,23 @@ def _worker(rank, world, port, kind, hp, out):
         state = z.gather_state(dst=0)
         local = z.local_state_dict()
         z.load_local_state_dict(local)  # round trip of the per-rank shard
+        sd = z.state_dict()  # collective: the reference's checkpoint form, on every rank
+        shard_dir = os.path.join(os.path.dirname(out), "shards")
+        z.save_shards(shard_dir)
+        fresh = Zero1Optimizer(kind, _make_params(), step_fn=oracle_step_fn, n_slices=3 if kind == "adamw" else None, **hp)
+        fresh.load_shards(shard_dir)
+        same = fresh.count == z.count and all(
+            (a is None and b is None) or torch.equal(a, b) for k in z.state for a, b in zip(z.state[k], fresh.state[k]))
+        again = Zero1Optimizer(kind, _make_params(), step_fn=oracle_step_fn, **hp)  # another slicing of the same buckets
+        again.load_state_dict(sd)
+        sd2 = again.state_dict()
         if rank == 0:
-            from flashoptim_jax_b200 import tree
+            from flashoptim_jax_b200 import tree, utils
 
+            flat = lambda d: [x for name in ("mu", "nu", "ecc") if name in d for x in tree.tree_leaves(utils._tree_from_state_dict(d[name]))]  # noqa: E731
             torch.save({"params": tree.tree_leaves(z.params), "state": tree.tree_leaves(state), "count": z.count,
-                        "segments": len(local["segments"])}, out)
+                        "segments": len(local["segments"]), "state_dict": flat(sd), "state_dict_again": flat(sd2),
+                        "shards_round_trip": same, "sd_count": int(sd["count"])}, out)
     finally:
         dist.destroy_process_group()
 
@@ -130,6 +142,33 @@ def test_two_ranks_match_one_rank_bit_for_bit(tmp_path, kind, hp):
     assert len(got["state"]) == len(want_state)
     for a, b in zip(got["state"], want_state):
         assert a.dtype == b.dtype and a.shape == b.shape and torch.equal(a, b)
+    # the device-side gather gives the unsharded optimizer's state dict, also after re-sharding; per-rank files round-trip
+    from flashoptim_jax_b200 import utils
+
+    want_sd = single.state_dict()
+    want_flat = [x for name in ("mu", "nu", "ecc") if name in want_sd for x in tree.tree_leaves(utils._tree_from_state_dict(want_sd[name]))]
+    assert got["sd_count"] == 3 and got["shards_round_trip"]
+    for key in ("state_dict", "state_dict_again"):
+        assert len(got[key]) == len(want_flat)
+        for a, b in zip(got[key], want_flat):
+            assert a.dtype == b.dtype and a.shape == b.shape and torch.equal(a, b)
+
+
+def test_state_dict_has_the_reference_checkpoint_form():
+    z = _run("adamw", dict(learning_rate=1e-3), steps=1)
+    sd = z.state_dict()
+    assert set(sd) == {"count", "mu", "nu", "ecc"} and int(sd["count"]) == 1
+    for name in ("mu", "nu", "ecc"):
+        assert set(sd[name]) == {"treedef", "leaves"} and len(sd[name]["leaves"]) == 8
+    assert sd["mu"]["leaves"][0]["kind"] == "quantized" and set(sd["mu"]["leaves"][0]) == {"kind", "values", "scales"}
+    kinds = {leaf["kind"] for leaf in sd["ecc"]["leaves"]}
+    assert kinds == {"array"}
+    other = Zero1Optimizer("adamw", _make_params(), step_fn=oracle_step_fn, learning_rate=1e-3)
+    other.load_state_dict(sd)
+    assert other.count == 1 and all((a is None and b is None) or torch.equal(a, b) for k in z.state for a, b in zip(z.state[k], other.state[k]))
+    with pytest.raises(ValueError):
+        bad = dict(sd, mu={"treedef": sd["mu"]["treedef"], "leaves": sd["mu"]["leaves"][:-1]})
+        other.load_state_dict(bad)
 
 
 def test_gathered_state_has_the_reference_layout():
