@@ -139,6 +139,25 @@ def sq_norm_of(tensors: List[torch.Tensor], out: Optional[torch.Tensor] = None, 
 # ---- per-step scalars on the device (graph-capturable steps) ---------------------------------------
 
 
+def mean_sq_norm(grad_slice: torch.Tensor, mean_out: torch.Tensor, peer_grad_offsets: List[int], out: torch.Tensor,
+                 accumulate: bool) -> torch.Tensor:
+    """mean_out <- this rank's slice of the gradient averaged over the ranks (own value, then the same elements
+    `peer_grad_offsets` bytes away in the peers' buffers), and the sum of its squares into `out` (a one-element
+    float64 tensor), in one sweep over NVLink (fo_mean_sq_norm)."""
+    device = grad_slice.device
+    if grad_slice.numel() != mean_out.numel() or grad_slice.dtype != mean_out.dtype:
+        raise ValueError("mean_sq_norm: slice and output differ")
+    ws = _workspaces.get(device.index)
+    if ws is None:
+        ws = _workspaces[device.index] = torch.empty(_lib.FO_SQ_NORM_WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+    peers = np.asarray(peer_grad_offsets, dtype=np.int64)
+    with torch.cuda.device(device):
+        _lib.check(_lib.lib().fo_mean_sq_norm(grad_slice.data_ptr(), mean_out.data_ptr(), grad_slice.numel(), DTYPE_CODE[grad_slice.dtype],
+                                             peers.ctypes.data if len(peers) else None, len(peers), int(accumulate), out.data_ptr(),
+                                             ws.data_ptr(), stream_ptr(device)))
+    return out
+
+
 def step_scalars(count: torch.Tensor, learning_rate: Any, b1: float, b2: float, write_count: bool) -> torch.Tensor:
     """float32[3] = {lr, 1 - b1^(count+1), 1 - b2^(count+1)} formed on the device from the device counter
     (adamw.py:510, 526-528); `learning_rate` is a number or a 0-d float32 CUDA tensor.  With `write_count`

@@ -27,7 +27,7 @@ FO_SELFTEST_GROUP_DIV, FO_SELFTEST_CODE_TABLES, FO_SELFTEST_RCP, FO_SELFTEST_PAC
 EXPORTS = (
     "fo_step", "fo_quantize_momentum", "fo_dequantize_momentum", "fo_quantize_variance",
     "fo_dequantize_variance", "fo_split", "fo_reconstruct", "fo_selftest", "fo_selftest_static", "fo_version",
-    "fo_status_string", "fo_last_error", "fo_sq_norm", "fo_step_scalars", "fo_step_scalars_schedule",
+    "fo_status_string", "fo_last_error", "fo_sq_norm", "fo_mean_sq_norm", "fo_step_scalars", "fo_step_scalars_schedule",
 )
 FO_SQ_NORM_WORKSPACE_BYTES = 16384
 
@@ -113,6 +113,8 @@ def lib() -> ctypes.CDLL:
     cdll.fo_selftest_static.argtypes = [i32, ctypes.c_int64, ctypes.POINTER(ctypes.c_uint64), ctypes.c_uint32, vp]
     cdll.fo_sq_norm.restype = ctypes.c_int
     cdll.fo_sq_norm.argtypes = [ctypes.POINTER(FoArray), ctypes.c_uint32, i32, i32, vp, vp, vp]
+    cdll.fo_mean_sq_norm.restype = ctypes.c_int
+    cdll.fo_mean_sq_norm.argtypes = [vp, vp, ctypes.c_uint64, i32, vp, ctypes.c_uint32, i32, vp, vp, vp]
     cdll.fo_step_scalars.restype = ctypes.c_int
     cdll.fo_step_scalars.argtypes = [vp, vp, ctypes.c_float, ctypes.c_float, ctypes.c_float, vp, vp, vp]
     cdll.fo_step_scalars_schedule.restype = ctypes.c_int

@@ -60,15 +60,19 @@ static DevHyper make_dev_hyper(const FoHyper& h, int opt) {
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// SM count of the device that is current on the calling thread (cached per device ordinal)
+// SM count of the device that is current on the calling thread (cached per device ordinal; atomics,
+// so that concurrent first calls from several threads are well defined: they store the same number)
 static int sm_count_of_current_device() {
-  static int cache[64] = {0};
+  static std::atomic<int> cache[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -1;
-  if (dev >= 0 && dev < 64 && cache[dev] > 0) return cache[dev];
+  if (dev >= 0 && dev < 64) {
+    const int known = cache[dev].load(std::memory_order_acquire);
+    if (known > 0) return known;
+  }
   int sms = 0;
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
-  if (dev >= 0 && dev < 64) cache[dev] = sms;
+  if (dev >= 0 && dev < 64) cache[dev].store(sms, std::memory_order_release);
   return sms;
 }
 

@@ -80,6 +80,66 @@ __global__ void __launch_bounds__(kThreads) sq_norm_partial(const __grid_constan
   }
 }
 
+// reduce-scatter by peer loads, the mean written out, its squares summed (see fo_mean_sq_norm)
+struct MeanParams {
+  const void* grad;
+  void* mean_out;
+  unsigned long long n;
+  long long gdelta[kMaxPeers];
+  int32_t n_peers;
+  int32_t dtype;
+};
+
+__global__ void __launch_bounds__(kThreads) mean_sq_norm_partial(const __grid_constant__ MeanParams p, double* partials) {
+  __shared__ double warp_sums[kThreads / 32];
+  double acc = 0.0;
+  const float ranks = (float)(p.n_peers + 1);
+  const unsigned long long pieces = p.n / kPiece;
+  for (unsigned long long q = (unsigned long long)blockIdx.x * kThreads + threadIdx.x; q < pieces; q += (unsigned long long)gridDim.x * kThreads) {
+    const unsigned long long i0 = q * kPiece;
+    const size_t off = (size_t)i0 * (p.dtype == FO_F32 ? 4u : 2u);
+    uint4 w0, w1 = make_uint4(0u, 0u, 0u, 0u);
+    w0 = __ldcs((const uint4*)((const char*)p.grad + off));
+    if (p.dtype == FO_F32) w1 = __ldcs((const uint4*)((const char*)p.grad + off) + 1);
+    float2 g[4];
+    grad_pairs(w0, w1, p.dtype, g);
+    for (int r = 0; r < p.n_peers; ++r) {
+      const char* src = (const char*)p.grad + p.gdelta[r] + off;
+      uint4 v0 = __ldcs((const uint4*)src), v1 = make_uint4(0u, 0u, 0u, 0u);
+      if (p.dtype == FO_F32) v1 = __ldcs((const uint4*)src + 1);
+      float2 pg[4];
+      grad_pairs(v0, v1, p.dtype, pg);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) { g[k].x = fadd(g[k].x, pg[k].x); g[k].y = fadd(g[k].y, pg[k].y); }
+    }
+    float s = 0.0f;
+    uint32_t packed[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float a = fdiv(g[k].x, ranks), b = fdiv(g[k].y, ranks);
+      if (p.dtype == FO_BF16) { packed[k] = pack2<FO_BF16>(a, b); unpack2<FO_BF16>(packed[k], a, b); }
+      if (p.dtype == FO_F16) { packed[k] = pack2<FO_F16>(a, b); unpack2<FO_F16>(packed[k], a, b); }
+      g[k].x = a; g[k].y = b;
+      s = __fmaf_rn(b, b, __fmaf_rn(a, a, s));
+    }
+    if (p.dtype == FO_F32) {
+      __stcs((float4*)((char*)p.mean_out + off), make_float4(g[0].x, g[0].y, g[1].x, g[1].y));
+      __stcs((float4*)((char*)p.mean_out + off) + 1, make_float4(g[2].x, g[2].y, g[3].x, g[3].y));
+    } else {
+      __stcs((uint4*)((char*)p.mean_out + off), make_uint4(packed[0], packed[1], packed[2], packed[3]));
+    }
+    acc += (double)s;
+  }
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < kThreads / 32; ++w) t += warp_sums[w];
+    partials[blockIdx.x] = t;
+  }
+}
+
 __global__ void sq_norm_final(const double* partials, int n, double* out, int accumulate) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
   double s = accumulate ? *out : 0.0;
@@ -173,6 +233,35 @@ extern "C" int fo_sq_norm(const FoArray* arrays, uint32_t n_arrays, int32_t dtyp
     ++count;
   }
   return flush();
+}
+
+extern "C" int fo_mean_sq_norm(const void* grad, void* mean_out, uint64_t n, int32_t dtype, const int64_t* peer_grad_offsets,
+                               uint32_t n_peers, int32_t accumulate, double* out, void* workspace, void* cuda_stream) {
+  if (out == nullptr || workspace == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_mean_sq_norm: null out / workspace");
+  if (dtype < FO_F32 || dtype > FO_F16) return fail(FO_ERR_INVALID_ARG, "fo_mean_sq_norm: bad dtype %d", dtype);
+  if (n_peers > (uint32_t)kMaxPeers) return fail(FO_ERR_TOO_LARGE, "fo_mean_sq_norm: %u peers, at most %d", n_peers, kMaxPeers);
+  if (n_peers > 0 && peer_grad_offsets == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_mean_sq_norm: n_peers without peer_grad_offsets");
+  if (n > 0 && (grad == nullptr || mean_out == nullptr)) return fail(FO_ERR_INVALID_ARG, "fo_mean_sq_norm: null grad / mean_out");
+  if (n % kPiece != 0 || ((uintptr_t)grad & 15u) != 0 || ((uintptr_t)mean_out & 15u) != 0)
+    return fail(FO_ERR_INVALID_ARG, "fo_mean_sq_norm: n must be a multiple of %d and the pointers 16-byte aligned", kPiece);
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return fail(FO_ERR_CUDA, "fo_mean_sq_norm: cannot query the current device");
+  MeanParams p;
+  memset(&p, 0, sizeof(p));
+  p.grad = grad; p.mean_out = mean_out; p.n = n; p.n_peers = (int32_t)n_peers; p.dtype = dtype;
+  for (uint32_t r = 0; r < n_peers; ++r) p.gdelta[r] = (long long)peer_grad_offsets[r];
+  double* partials = static_cast<double*>(workspace);
+  unsigned long long want = (n / kPiece + kThreads - 1) / kThreads;
+  unsigned int grid = (unsigned int)(sms * kNormBlocksPerSm);
+  if (grid > kNormMaxBlocks) grid = kNormMaxBlocks;
+  if ((unsigned long long)grid > want) grid = (unsigned int)want;
+  if (grid > 0) mean_sq_norm_partial<<<grid, kThreads, 0, stream>>>(p, partials);
+  sq_norm_final<<<1, 32, 0, stream>>>(partials, (int)grid, out, accumulate);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(FO_ERR_CUDA, "fo_mean_sq_norm: launch failed: %s", cudaGetErrorString(e));
+  return FO_OK;
 }
 
 extern "C" int fo_step_scalars(const int32_t* count, const float* lr_dev, float lr_const, float b1, float b2, float* out3,

@@ -223,57 +223,76 @@ __global__ void selftest_code_tables(unsigned long long* out) {
   tally(bad, out);
 }
 
+// Is (which, arg) a sweep this library has?  Checked before anything is queued on the stream.
+static int validate_sweep(const char* who, int32_t which, int64_t arg) {
+  switch (which) {
+    case FO_SELFTEST_SQRT: case FO_SELFTEST_SOFTSIGN: case FO_SELFTEST_GROUP_DIV: case FO_SELFTEST_CODE_TABLES:
+    case FO_SELFTEST_RCP: case FO_SELFTEST_PACKED:
+      return FO_OK;
+    case FO_SELFTEST_RECONSTRUCT:
+    case FO_SELFTEST_SPLIT: {
+      const int pdt = (int)(arg / 100), eb = (int)(arg % 100);
+      if ((pdt == FO_BF16 || pdt == FO_F16) && (eb == 8 || eb == 16)) return FO_OK;
+      return fail(FO_ERR_INVALID_ARG, "%s: arg %lld names no (dtype, ecc) pair", who, (long long)arg);
+    }
+    default: return fail(FO_ERR_INVALID_ARG, "%s: unknown test %d", who, which);
+  }
+}
+
+// The one dispatch table of the sweeps, shared by both entry points: launches sweep `which` with its
+// mismatch counters at `d` (zeroed by the caller).  (which, arg) has passed validate_sweep.
+static void launch_sweep(int32_t which, int64_t arg, unsigned long long* d, cudaStream_t s) {
+  const int grid = 148 * 8, block = 256;
+  volatile float one_src = 1.0f;  // a run-time 1.0f, as the step kernels receive it
+  const float one = one_src;
+  switch (which) {
+    case FO_SELFTEST_SQRT: selftest_sqrt<<<grid, block, 0, s>>>(one, d); return;
+    case FO_SELFTEST_SOFTSIGN: selftest_softsign<<<grid, block, 0, s>>>(one, d); return;
+    case FO_SELFTEST_GROUP_DIV:
+      selftest_group_div<<<grid, block, 0, s>>>(one, (unsigned long long)(arg > 0 ? arg : 1) * 1000000ull, d);
+      return;
+    case FO_SELFTEST_CODE_TABLES: selftest_code_tables<<<64, block, 0, s>>>(d); return;
+    case FO_SELFTEST_RCP: selftest_rcp<<<grid, block, 0, s>>>(d); return;
+    case FO_SELFTEST_PACKED: selftest_packed<<<grid, block, 0, s>>>(one, 1000000000ull, d); return;
+    case FO_SELFTEST_RECONSTRUCT:
+    case FO_SELFTEST_SPLIT: {
+      const int pdt = (int)(arg / 100), eb = (int)(arg % 100);
+#define X(P, E)                                                                                  \
+  if (pdt == P && eb == E) {                                                                     \
+    if (which == FO_SELFTEST_RECONSTRUCT) selftest_reconstruct<P, E><<<grid, block, 0, s>>>(one, d); \
+    else selftest_split<P, E><<<grid, block, 0, s>>>(one, d);                                    \
+    return;                                                                                      \
+  }
+      X(FO_BF16, 8) X(FO_BF16, 16) X(FO_F16, 8) X(FO_F16, 16)
+#undef X
+      return;
+    }
+    default: return;
+  }
+}
+
 }  // namespace fo
 
 using namespace fo;
 
 extern "C" int fo_selftest(int32_t which, int64_t arg, uint64_t* mismatches, void* cuda_stream) {
   if (mismatches == nullptr) return fail(FO_ERR_INVALID_ARG, "fo_selftest: null result pointer");
+  int rc = validate_sweep("fo_selftest", which, arg);
+  if (rc != FO_OK) return rc;
   cudaStream_t s = (cudaStream_t)cuda_stream;
   unsigned long long* d = nullptr;
   // the only allocation in the library: a test-only counter, freed before returning
   cudaError_t e = cudaMalloc(&d, 4 * sizeof(unsigned long long));
   if (e != cudaSuccess) return fail(FO_ERR_CUDA, "fo_selftest: %s", cudaGetErrorString(e));
   cudaMemsetAsync(d, 0, 4 * sizeof(unsigned long long), s);
-  const int grid = 148 * 8, block = 256;
-  volatile float one_src = 1.0f;  // a run-time 1.0f, as the step kernels receive it
-  const float one = one_src;
-  int rc = FO_OK;
-  switch (which) {
-    case FO_SELFTEST_SQRT: selftest_sqrt<<<grid, block, 0, s>>>(one, d); break;
-    case FO_SELFTEST_SOFTSIGN: selftest_softsign<<<grid, block, 0, s>>>(one, d); break;
-    case FO_SELFTEST_GROUP_DIV:
-      selftest_group_div<<<grid, block, 0, s>>>(one, (unsigned long long)(arg > 0 ? arg : 1) * 1000000ull, d);
-      break;
-    case FO_SELFTEST_CODE_TABLES: selftest_code_tables<<<64, block, 0, s>>>(d); break;
-    case FO_SELFTEST_RCP: selftest_rcp<<<grid, block, 0, s>>>(d); break;
-    case FO_SELFTEST_PACKED: selftest_packed<<<grid, block, 0, s>>>(one, 1000000000ull, d); break;
-    case FO_SELFTEST_RECONSTRUCT:
-    case FO_SELFTEST_SPLIT: {
-      const int pdt = (int)(arg / 100), eb = (int)(arg % 100);
-      bool ok = false;
-#define X(P, E)                                                                              \
-  if (pdt == P && eb == E) {                                                                 \
-    ok = true;                                                                               \
-    if (which == FO_SELFTEST_RECONSTRUCT) selftest_reconstruct<P, E><<<grid, block, 0, s>>>(one, d); \
-    else selftest_split<P, E><<<grid, block, 0, s>>>(one, d);                                     \
-  }
-      X(FO_BF16, 8) X(FO_BF16, 16) X(FO_F16, 8) X(FO_F16, 16)
-#undef X
-      if (!ok) rc = fail(FO_ERR_INVALID_ARG, "fo_selftest: arg %lld names no (dtype, ecc) pair", (long long)arg);
-      break;
-    }
-    default: rc = fail(FO_ERR_INVALID_ARG, "fo_selftest: unknown test %d", which);
-  }
-  if (rc == FO_OK) {
-    e = cudaGetLastError();
-    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
-    unsigned long long h[4] = {0, 0, 0, 0};
-    if (e == cudaSuccess) e = cudaMemcpy(h, d, sizeof(h), cudaMemcpyDeviceToHost);
-    if (e != cudaSuccess) rc = fail(FO_ERR_CUDA, "fo_selftest: %s", cudaGetErrorString(e));
-    // arg selects which counter of a multi-counter test is reported (FO_SELFTEST_RCP: 0 in use, 1 one step, 2 two steps)
-    *mismatches = ((which == FO_SELFTEST_RCP || which == FO_SELFTEST_PACKED) && arg >= 0 && arg < 3) ? h[arg] : h[0];
-  }
+  launch_sweep(which, arg, d, s);
+  e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  unsigned long long h[4] = {0, 0, 0, 0};
+  if (e == cudaSuccess) e = cudaMemcpy(h, d, sizeof(h), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) rc = fail(FO_ERR_CUDA, "fo_selftest: %s", cudaGetErrorString(e));
+  // arg selects which counter of a multi-counter test is reported (FO_SELFTEST_RCP: 0 in use, 1 one step, 2 two steps)
+  *mismatches = ((which == FO_SELFTEST_RCP || which == FO_SELFTEST_PACKED) && arg >= 0 && arg < 3) ? h[arg] : h[0];
   cudaFree(d);
   return rc;
 }
@@ -315,37 +334,6 @@ static int static_counters_address(unsigned long long** out) {
   return FO_OK;
 }
 
-// dispatch of one sweep onto counters at `d` (used by fo_selftest_static only)
-static int launch_sweep(int32_t which, int64_t arg, unsigned long long* d, cudaStream_t s) {
-  const int grid = 148 * 8, block = 256;
-  volatile float one_src = 1.0f;
-  const float one = one_src;
-  switch (which) {
-    case FO_SELFTEST_SQRT: selftest_sqrt<<<grid, block, 0, s>>>(one, d); return FO_OK;
-    case FO_SELFTEST_SOFTSIGN: selftest_softsign<<<grid, block, 0, s>>>(one, d); return FO_OK;
-    case FO_SELFTEST_GROUP_DIV:
-      selftest_group_div<<<grid, block, 0, s>>>(one, (unsigned long long)(arg > 0 ? arg : 1) * 1000000ull, d);
-      return FO_OK;
-    case FO_SELFTEST_CODE_TABLES: selftest_code_tables<<<64, block, 0, s>>>(d); return FO_OK;
-    case FO_SELFTEST_RCP: selftest_rcp<<<grid, block, 0, s>>>(d); return FO_OK;
-    case FO_SELFTEST_PACKED: selftest_packed<<<grid, block, 0, s>>>(one, 1000000000ull, d); return FO_OK;
-    case FO_SELFTEST_RECONSTRUCT:
-    case FO_SELFTEST_SPLIT: {
-      const int pdt = (int)(arg / 100), eb = (int)(arg % 100);
-#define X(P, E)                                                                                  \
-  if (pdt == P && eb == E) {                                                                     \
-    if (which == FO_SELFTEST_RECONSTRUCT) selftest_reconstruct<P, E><<<grid, block, 0, s>>>(one, d); \
-    else selftest_split<P, E><<<grid, block, 0, s>>>(one, d);                                    \
-    return FO_OK;                                                                                \
-  }
-      X(FO_BF16, 8) X(FO_BF16, 16) X(FO_F16, 8) X(FO_F16, 16)
-#undef X
-      return fail(FO_ERR_INVALID_ARG, "fo_selftest_static: arg %lld names no (dtype, ecc) pair", (long long)arg);
-    }
-    default: return fail(FO_ERR_INVALID_ARG, "fo_selftest_static: unknown test %d", which);
-  }
-}
-
 }  // namespace fo
 
 extern "C" int fo_selftest_static(int32_t which, int64_t arg, uint64_t* counters, uint32_t n_counters, void* cuda_stream) {
@@ -354,15 +342,16 @@ extern "C" int fo_selftest_static(int32_t which, int64_t arg, uint64_t* counters
   if (n_counters > FO_SELFTEST_STATIC_MAX_COUNTERS)
     return fail(FO_ERR_TOO_LARGE, "fo_selftest_static: %u counters asked for, the static scratch holds %d", n_counters,
                 FO_SELFTEST_STATIC_MAX_COUNTERS);
+  int rc = validate_sweep("fo_selftest_static", which, arg);  // before the shared array is touched
+  if (rc != FO_OK) return rc;
   cudaStream_t s = (cudaStream_t)cuda_stream;
   unsigned long long* d = nullptr;
-  int rc = static_counters_address(&d);
+  rc = static_counters_address(&d);
   if (rc != FO_OK) return rc;
   // the array keeps what the previous call left: counters must start from zero
   cudaError_t e = cudaMemsetAsync(d, 0, FO_SELFTEST_STATIC_MAX_COUNTERS * sizeof(unsigned long long), s);
   if (e != cudaSuccess) return fail(FO_ERR_CUDA, "fo_selftest_static: cudaMemsetAsync: %s", cudaGetErrorString(e));
-  rc = launch_sweep(which, arg, d, s);
-  if (rc != FO_OK) return rc;
+  launch_sweep(which, arg, d, s);
   e = cudaGetLastError();
   unsigned long long h[FO_SELFTEST_STATIC_MAX_COUNTERS] = {0};
   if (e == cudaSuccess) e = cudaMemcpyAsync(h, d, sizeof(h), cudaMemcpyDeviceToHost, s);

@@ -25,6 +25,8 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include "fo_math.cuh"
 
 namespace fo {
@@ -1794,12 +1796,18 @@ cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStre
   const bool switch_sum = p_in.peers.mc_gdelta != 0 && p_in.grad_dtype != FO_F32;
   const int ring_bytes = switch_sum ? kSwitchBatch * 16 * kThreads : 0;
   auto kernel = step_kernel<OPT, PDT, ECC_BITS, STATE, AUX>;
-  static int static_smem = -1;  // the same on every device
+  // Two caches, per instantiation of this function (one kernel each): the kernel's static shared memory
+  // (the same on every device) and whether a device's copy of the function has been opted in above
+  // 48 KB.  Atomics: concurrent first calls may both query and both set, which is harmless (same
+  // values, idempotent calls), and no call ever reads a half-written entry.
+  static std::atomic<int> static_smem_cache{-1};
+  int static_smem = static_smem_cache.load(std::memory_order_acquire);
   if (static_smem < 0) {
     cudaFuncAttributes attr;
     cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
     if (e != cudaSuccess) return e;
     static_smem = (int)attr.sharedSizeBytes;
+    static_smem_cache.store(static_smem, std::memory_order_release);
   }
   // as many stages as fit beside the tables with min_blocks(OPT) blocks on an SM; when the peers'
   // gradient pieces make a stage too large for two of them, with one block on an SM
@@ -1815,16 +1823,16 @@ cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStre
   if (stages > max_stages) stages = max_stages;
   if (stages < (aux ? 2 : kPlainStages)) return cudaErrorInvalidConfiguration;
   const int dynamic_smem = stages * per_stage + ring_bytes;
-  static bool opted_in[64] = {};  // per device ordinal: the opt-in above 48 KB belongs to the device's copy of the function
+  static std::atomic<bool> opted_in[64];  // per device ordinal (zero-initialised)
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  if (dev < 0 || dev >= 64 || !opted_in[dev]) {
+  if (dev < 0 || dev >= 64 || !opted_in[dev].load(std::memory_order_acquire)) {
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPerSm - kSmemReservedPerBlock - static_smem);
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return e;
-    if (dev >= 0 && dev < 64) opted_in[dev] = true;
+    if (dev >= 0 && dev < 64) opted_in[dev].store(true, std::memory_order_release);
   }
   StepParams p = p_in;
   p.stages = stages;

@@ -179,8 +179,10 @@ class Zero1Optimizer:
                 clip the (averaged) gradients at this global norm, as optax.clip_by_global_norm in front
                 of the optimizer does (examples/train_gpt2_pretrain.py:56-70): every rank sums the squares
                 of its reduce-scattered slice on the device, the sums are all-reduced, and the step kernel
-                rescales the gradients as it loads them.  Needs the reduce-scattered gradients in memory,
-                so not together with fused_reduce_scatter.
+                rescales the gradients as it loads them.  Together with fused_reduce_scatter the sweep that
+                sums the squares is also the reduce-scatter: it reads the peers' slices over NVLink, leaves the
+                averaged slice in local memory for the step and its squares in the sum (fo_mean_sq_norm), so
+                the gradients still cross the links once.
     """
 
     def __init__(self, optimizer: str, params: Any, *, group=None, step_fn: Optional[StepFn] = None,
@@ -238,11 +240,16 @@ class Zero1Optimizer:
             n_slices = 1
         self.max_grad_norm = None if max_grad_norm is None else float(max_grad_norm)
         if self.max_grad_norm is not None:
-            if self.fused_reduce_scatter:
-                raise ValueError("max_grad_norm needs the reduce-scattered gradients: fused_reduce_scatter must be off")
             if device.type != "cuda":
                 raise ValueError("max_grad_norm needs CUDA tensors")
             n_slices = 1  # the norm is known only after the last reduce-scatter: nothing to pipeline
+        # Who reads the peers' gradients: the step kernel itself, or, when the step clips by the global norm (whose
+        # value needs the whole averaged gradient first), the norm sweep, which leaves this rank's averaged
+        # slice in grad_shards for the step.
+        self._rs_in_step = self.fused_reduce_scatter and self.max_grad_norm is None
+        self._rs_in_norm = self.fused_reduce_scatter and self.max_grad_norm is not None
+        if self._rs_in_norm and use_switch:
+            raise ValueError("max_grad_norm with fused_reduce_scatter reads the peers point to point: use_switch must be off")
         self.use_switch = use_switch
         self.peer_offsets: List[List[int]] = []
         self.peer_grad_offsets: List[List[int]] = []
@@ -271,7 +278,7 @@ class Zero1Optimizer:
             self.flat_grads.append(flat_g)
             # one rank owns everything: the "scattered" gradient is the flat buffer itself
             # (nor is there a scattered copy when the kernel reads the peers' gradients itself)
-            own_shard = self.world_size > 1 and not self.fused_reduce_scatter
+            own_shard = self.world_size > 1 and not self._rs_in_step
             self.grad_shards.append(torch.zeros(layout.shard, dtype=dtype, device=device) if own_shard else flat_g)
         self.params = self.treedef.unflatten(param_views)
         self.grads = self.treedef.unflatten(grad_views)
@@ -571,7 +578,13 @@ class Zero1Optimizer:
         zero), summed over the ranks."""
         if self.max_grad_norm is None:
             return contextlib.nullcontext()
-        sq = eng.sq_norm_of(list(self.grad_shards))
+        if self._rs_in_norm:
+            sq = torch.zeros(1, dtype=torch.float64, device=self.device)
+            for b, layout in enumerate(self.buckets):
+                mine = self.flat_grads[b][self.rank * layout.shard:(self.rank + 1) * layout.shard]
+                eng.mean_sq_norm(mine, self.grad_shards[b], self.peer_grad_offsets[b], sq, accumulate=b > 0)
+        else:
+            sq = eng.sq_norm_of(list(self.grad_shards))
         if self.world_size > 1:
             dist.all_reduce(sq, group=self.group)
         return eng.grad_clip(sq, self.max_grad_norm)
@@ -581,7 +594,7 @@ class Zero1Optimizer:
             for b in range(len(self.buckets)):
                 self._run(("bucket", b), lambda _leaf, wb, _sl, b=b: wb == b,
                           self.peer_offsets[b] if (self.fused_allgather and do_ag) else None,
-                          self.peer_grad_offsets[b] if (self.fused_reduce_scatter and do_rs) else None,
+                          self.peer_grad_offsets[b] if (self._rs_in_step and do_rs) else None,
                           self.mc_param_offsets[b] if do_ag else 0, self.mc_grad_offsets[b] if do_rs else 0)
             self.count += 1
             if self.fused_allgather:
@@ -589,7 +602,7 @@ class Zero1Optimizer:
                 dist.all_reduce(self._token, group=self.group)
             elif do_ag:
                 self.all_gather_params()  # a collective, hence also the barrier that protects the gradients
-            elif self.fused_reduce_scatter and do_rs:
+            elif self._rs_in_step and do_rs:
                 dist.all_reduce(self._token, group=self.group)
             return self.params
         self._run(("all",), lambda _leaf, _b, _sl: True)

@@ -202,6 +202,19 @@ typedef struct FoArray {
 int fo_sq_norm(const FoArray* arrays, uint32_t n_arrays, int32_t dtype, int32_t accumulate, double* out,
                void* workspace, void* cuda_stream);
 
+/* Reduce-scatter and norm in one sweep, for ZeRO-1 steps that clip by the global norm: this rank's
+ * slice of the averaged gradient is needed twice (for the norm of the whole averaged gradient, then
+ * for the step), but should cross NVLink once.  grad points at the slice inside this rank's copy of
+ * the gradient buffer; the same elements of peer r lie peer_grad_offsets[r] bytes away (peer-mapped
+ * memory, as for FoStepDesc.peer_grad_offsets).  mean_out[i] = RN_g((g_own[i] + g_peer0[i] + ...) /
+ * (n_peers + 1)): fp32 sum in that order, one rounding to the gradient dtype, the value the step
+ * kernel's own averaging produces (the reference's pmean, examples/train_gpt2_pretrain.py:429); the sum of
+ * mean_out[i]^2 is added to / stored in *out as fo_sq_norm does.  n must be a multiple of 8 and both
+ * pointers 16-byte aligned (a ZeRO-1 slice is).  The caller orders the ranks around the call like around a
+ * fused reduce-scatter. */
+int fo_mean_sq_norm(const void* grad, void* mean_out, uint64_t n, int32_t dtype, const int64_t* peer_grad_offsets,
+                    uint32_t n_peers, int32_t accumulate, double* out, void* workspace, void* cuda_stream);
+
 /* Codecs on fp32 arrays; n elements, scales has ceil(n/group_size) fp16 entries.
  * scale_floor selects the guard of FO_FLAG_SCALE_FLOOR.
  *   fo_quantize_momentum   flashoptim_jax/quantization.py:37-46

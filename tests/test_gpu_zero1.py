@@ -371,3 +371,58 @@ def test_checkpoint_export_and_import_on_the_device(tmp_path):
     for k in z.state:
         for a, b in zip(z.state[k], other.state[k]):
             assert (a is None and b is None) or torch.equal(a, b)
+
+
+def _clip_worker(rank, world, port, out, own_grads):
+    import torch
+    import torch.distributed as dist
+
+    from flashoptim_jax_b200 import tree
+    from flashoptim_jax_b200.zero1 import Zero1Optimizer
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        z = Zero1Optimizer("adamw", _params(dev), fused_allgather=True, fused_reduce_scatter=True, max_grad_norm=0.05, **HP)
+        for t in range(3):
+            z.step(_grads(t + (100 * rank if own_grads else 0), dev))
+        torch.cuda.synchronize()
+        state = z.gather_state(dst=0)
+        if rank == 0:
+            torch.save({"params": [p.cpu() for p in tree.tree_leaves(z.params)], "state": [s.cpu() for s in tree.tree_leaves(state)]}, out)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("own_grads", [False, True], ids=["equal-grads", "own-grads"])
+def test_two_ranks_clip_by_global_norm_with_the_fused_reduce_scatter(tmp_path, own_grads):
+    """Clipping together with the reduce-scatter by peer loads: the sweep that sums the squares also forms this
+    rank's averaged slice.  The result is the one-rank clipped step on the mean gradient, bit for bit (the
+    norm is a sum of doubles in another order: equal to the last place of the float it is rounded to here)."""
+    import torch
+    import torch.multiprocessing as mp
+
+    from flashoptim_jax_b200 import tree
+    from flashoptim_jax_b200.zero1 import Zero1Optimizer
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    dev = torch.device("cuda", 0)
+    single = Zero1Optimizer("adamw", _params(dev), max_grad_norm=0.05, **HP)
+    for t in range(3):
+        g0 = _grads(t, dev)
+        if own_grads:
+            g1 = _grads(t + 100, dev)
+            g0 = tree.tree_map(lambda a, b: ((a.float() + b.float()) * 0.5).to(a.dtype), g0, g1)
+        single.step(g0)
+    want_p = [p.cpu() for p in tree.tree_leaves(single.params)]
+    want_s = [s.cpu() for s in tree.tree_leaves(single.gather_state())]
+    out = str(tmp_path / "r0.pt")
+    mp.spawn(_clip_worker, args=(2, _free_port(), out, own_grads), nprocs=2, join=True)
+    got = torch.load(out, weights_only=False)
+    for a, b in zip(got["params"], want_p):
+        assert torch.equal(a, b)
+    for a, b in zip(got["state"], want_s):
+        assert a.dtype == b.dtype and torch.equal(a, b)
