@@ -353,6 +353,21 @@ def parity_check(zero, device):
         return D.LeafArrays(arr(zero.flat_params[b], at + lo, at + hi), arr(st.ecc, lo, hi), arr(st.mu, lo, hi), arr(st.mu_scales, glo, ghi),
                             arr(st.nu, lo, hi), arr(st.nu_scales, glo, ghi)), D.to_numpy(zero.flat_grads[b][at + lo:at + hi])
 
+    def mean_as_the_kernel_forms_it(g):
+        """Equal gradients on all ranks: the fused reduce-scatter adds them in fp32 (own value first, then the
+        peers), divides by the rank count and rounds once to the gradient dtype.  k * g is exact for 16-bit
+        gradients (k <= 8), so the mean is g itself; an fp32 sum of fp32 values rounds at every addition from
+        the third on, and the last place of the mean can differ from g's."""
+        if zero.world_size <= 2 or g.dtype != np.float32:
+            return g
+        acc = g.copy()
+        for _ in range(zero.world_size - 1):
+            acc = (acc + g).astype(np.float32)
+        return (acc / np.float32(zero.world_size)).astype(np.float32)
+
+    if zero.world_size > 2 and not zero.fused_reduce_scatter:
+        # NCCL's order of additions is its own: fp32 buckets cannot be predicted to the bit
+        samples = [x for x in samples if zero.buckets[x[0]].dtype != torch.float32]
     before = [snap(*x) for x in samples]
     count = zero.count + 1
     zero.step()
@@ -366,7 +381,7 @@ def parity_check(zero, device):
         st = zero.state[(b, s)]
         state = C.STATE_NONE if st.mu is None else (C.STATE_QUANT if config["quantize"] else C.STATE_FULL)
         opt = {_lib.FO_OPT_ADAM: C.ADAM, _lib.FO_OPT_LION: C.LION, _lib.FO_OPT_SGD: C.SGD}[zero.opt_code]
-        D.oracle_step(opt, grad, leaf, state, 32, hp)
+        D.oracle_step(opt, mean_as_the_kernel_forms_it(grad), leaf, state, 32, hp)
         got, _ = snap(b, s, lo, hi)
         elements += hi - lo
         for f in leaf.fields():
@@ -578,6 +593,8 @@ def run_ours(args):
     parity = None
     if not args.no_parity:
         parity = parity_check(zero, device)
+        if parity.get("detail"):
+            print(f"rank {rank}: parity mismatches: {parity['detail']}", file=sys.stderr)
         if world > 1:
             t = torch.tensor([parity["mismatches"], parity["elements"], parity["leaves"]], device=device, dtype=torch.int64)
             dist.all_reduce(t)

@@ -144,7 +144,11 @@ typedef struct FoStepDesc {
    * step (fo_sq_norm writes it; with sharded gradients the caller adds the ranks' sums first).
    * With norm = (float)sqrt(*grad_sq_norm): gradients are used as they are if norm < max_grad_norm,
    * else each is replaced by RN_g(RN_g(g / RN_g(norm)) * RN_g(max_grad_norm)), RN_g = rounding to
-   * grad_dtype.  Applied after the averaging over peers.  NULL: no clipping. */
+   * grad_dtype.  Applied after the averaging over peers.  NULL: no clipping.
+   * The sum of squares is the caller's: fo_sq_norm forms it exactly (fp32 squares, fp64 sums), where
+   * optax sums every leaf in the leaf's own dtype; for 16-bit gradients the two norms, and with them
+   * the clip / no-clip decision right at the threshold and the divisor, can differ by places of that
+   * dtype.  The element-wise rescaling is optax's bit for bit given the same sum. */
   const double* grad_sq_norm;
   float max_grad_norm;
   uint32_t reserved2;
