@@ -147,6 +147,10 @@ WORKLOADS = {
     "llama3_8b": (llama3_8b_shapes, "adamw", LLAMA_HP, 1e-4, 0.0),
     "llama3_8b_div64": (small_shapes, "adamw", LLAMA_HP, 1e-4, 0.0),
     "adamw_leaf_64m": (one_leaf_shapes, "adamw", LLAMA_HP, 1e-4, 0.0),
+    # the same single leaf under the other kernels (24-bit master weights), for their profiles
+    "adamw24_leaf_64m": (one_leaf_shapes, "adamw", dict(LLAMA_HP, master_weight_bits=24), 1e-4, 0.0),
+    "lion_leaf_64m": (one_leaf_shapes, "lion", dict(learning_rate=1e-4, b1=0.9, b2=0.99, weight_decay=1e-2, master_weight_bits=24), 1e-4, 0.0),
+    "sgdw_leaf_64m": (one_leaf_shapes, "sgdw", dict(learning_rate=1e-2, momentum=0.9, weight_decay=1e-2, master_weight_bits=24), 1e-4, 0.0),
     "resnet50": (resnet50_shapes, "sgdw", dict(learning_rate=0.1, momentum=0.9, weight_decay=1e-4, master_weight_bits=24,
                                                param_groups=[{"params": _no_decay, "weight_decay": 0.0}]), 1e-3, 0.0),
     "gpt2_small": (gpt2_small_shapes, "adamw", dict(learning_rate=1e-3, b1=0.9, b2=0.999, eps=1e-8, weight_decay=1e-2,

@@ -56,6 +56,8 @@ def _units(shapes=None, ffi_dir: str | None = None) -> List[Tuple[str, str, List
         shape = shapes.get((oname, aux))
         if shape is not None and kind != 3:
             flags += [f"-DFO_THREADS={shape[0]}", f"-DFO_MIN_BLOCKS_ADAM={shape[1]}", f"-DFO_MIN_BLOCKS_MOMENTUM={shape[1]}"]
+            if len(shape) > 2:
+                flags.append(f"-DFO_PLAIN_STAGES={shape[2]}")
         units.append((f"fo_step_{oname}_{kname}{suffix}", "fo_step_inst.cu", flags))
 
     for oname, omacro in _OPTS:

@@ -1000,8 +1000,7 @@ FO_DEVI float sign_of(float x);
 
 template <int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
 __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base,
-                                        const float one, const float* lut_mw, const Peers& peers, const Clip* clip,
-                                        const uint32_t n_limit);
+                                        const float one, const float* lut_mw, const Peers& peers, const Clip* clip);
 
 // Second half of a hot chunk: update, split, requantize, store.  Each stage runs its packed
 // shortcut unconditionally.
@@ -1011,7 +1010,7 @@ __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const in
 // REPAIR = true (warm_chunk): the lane that holds such a value (exact zeros are the common case:
 // untouched rows, padding, zero gradients) redoes that stage with IEEE operations, then stores.
 // The stored bits are those of the IEEE path in every case.
-template <bool REPAIR, int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
+template <bool REPAIR, int OPT, int PDT, int ECC_BITS, int STATE, bool AUX, bool MASKED = false>
 FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base, const Piece& at, const float one,
                         bool rare, Unpacked& u, const float* lut_mw, const Peers& peers, const Clip* clip,
                         const int n_valid = kPiece, const bool group_valid = true) {
@@ -1184,13 +1183,13 @@ FO_DEVI void hot_finish(const DevLeaf& L, const Hyp& h, const int gdt, const uin
         // no new first moment of the warp differs from zero: look whether the whole piece is at rest
         if (__all_sync(0xFFFFFFFFu, am_lane == 0.0f) && zero_chunk<OPT, PDT, ECC_BITS>(h.flags, h.wd, h.decay, gdt, one, at.grad, at.param, at.ecc, at.mu, at.nu, at.msc, at.vsc)) return;
       }
-      warm_chunk<OPT, PDT, ECC_BITS, STATE, AUX>(L, h, gdt, base, one, lut_mw, peers, clip, 0xFFFFFFFFu);
+      warm_chunk<OPT, PDT, ECC_BITS, STATE, AUX>(L, h, gdt, base, one, lut_mw, peers, clip);
       return;
     }
   }
   // ---- stores ---------------------------------------------------------------------------------------------
-  if constexpr (REPAIR) {
-    // the ragged end of a leaf (repairing pass only): the piece that straddles the end stores its
+  if constexpr (REPAIR && MASKED) {
+    // the ragged end of a leaf (ragged_chunk only): the piece that straddles the end stores its
     // valid elements one by one, pieces beyond it store nothing; a group's scale is stored by the
     // lanes of a group that has an element at all
     if (n_valid < kPiece) {
@@ -1309,14 +1308,12 @@ __device__ __noinline__ void masked_load(const Piece& at, const int gdt, const i
   }
 }
 
-// Second chance for a warp whose first pass met a value outside a shortcut's range: the same
-// packed arithmetic from a fresh load, with per-lane IEEE repairs.  About twice the cost of a
-// first pass for that warp, against about seven times for the scalar IEEE path.
-// Also the path of a leaf's ragged last chunk: elements from n_limit on do not exist; they read as
+// The repairing pass with a limit, for a leaf's ragged last chunk and for leaves shorter than a chunk
+// (called from the tail kernel only): elements from n_limit on do not exist; they read as
 // zeros (flashoptim_jax/quantization.py:20-26) and nothing is stored for them.  Warps that lie wholly
 // beyond the end return at once.  (Not with peer replicas: their stores are whole vectors.)
 template <int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
-__device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base,
+__device__ __noinline__ void ragged_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base,
                                         const float one, const float* lut_mw, const Peers& peers, const Clip* clip,
                                         const uint32_t n_limit) {
   const uint32_t i0 = base + threadIdx.x * kPiece;
@@ -1348,7 +1345,34 @@ __device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const in
     });
   }
   if (AUX && clip->active) clip_grads<true>(u.g, gdt, *clip);
-  hot_finish<true, OPT, PDT, ECC_BITS, STATE, AUX>(L, h, gdt, base, at, one, false, u, lut_mw, peers, clip, n_valid, group_valid);
+  hot_finish<true, OPT, PDT, ECC_BITS, STATE, AUX, true>(L, h, gdt, base, at, one, false, u, lut_mw, peers, clip, n_valid, group_valid);
+}
+
+// Second chance for a warp whose first pass met a value outside a shortcut's range: the same
+// packed arithmetic from a fresh load, with per-lane IEEE repairs.  About twice the cost of a
+// first pass for that warp, against about seven times for the scalar IEEE path.
+template <int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
+__device__ __noinline__ void warm_chunk(const DevLeaf& L, const Hyp& h, const int gdt, const uint32_t base,
+                                        const float one, const float* lut_mw, const Peers& peers, const Clip* clip) {
+  Raw<OPT, PDT, ECC_BITS, STATE> raw;
+  hot_load<OPT, PDT, ECC_BITS, STATE>(L, gdt, base + threadIdx.x * kPiece, raw);
+  Unpacked u;
+  hot_unpack<true, OPT, PDT, ECC_BITS, STATE>(raw, gdt, lut_mw, one, u);
+  if (AUX && peers.ng > 0) {
+    const uint32_t i0 = base + threadIdx.x * kPiece;
+    merge_peer_grads<true>(u.g, gdt, peers, [&](int r, uint4& w0, uint4& w1) {
+      const char* g = (const char*)L.grad + peers.gdelta[r];
+      if (gdt == FO_F32) {
+        w0 = __ldcs((const uint4*)((const float*)g + i0));
+        w1 = __ldcs((const uint4*)((const float*)g + i0) + 1);
+      } else {
+        w0 = __ldcs((const uint4*)((const unsigned short*)g + i0));
+      }
+    });
+  }
+  if (AUX && clip->active) clip_grads<true>(u.g, gdt, *clip);
+  const Piece at = piece_at<PDT, ECC_BITS, STATE>(L, gdt, base + threadIdx.x * kPiece);
+  hot_finish<true, OPT, PDT, ECC_BITS, STATE, AUX>(L, h, gdt, base, at, one, false, u, lut_mw, peers, clip);
 }
 
 // One block's run of consecutive whole chunks [ch, hot_end) of a leaf, for the kernel without peer or
@@ -1501,6 +1525,63 @@ FO_DEVI bool leaf_is_hot(const StepParams& p, int l) {
 #endif
 }
 
+// The chunks [ch, end) of leaf l that the straight-line path does not take.  An aligned leaf under
+// ordinary hyper-parameters goes through the repairing pass with a limit (vector accesses, masked at
+// the leaf's end); the scalar path keeps unaligned leaves, the CPU-path parameter hand-back and peer
+// replicas.  Out of line and fed by reference to the kernel's parameters, so that the persistent loop's
+// register allocation does not see it.
+template <int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
+__device__ __noinline__ void leaf_tail(const StepParams& p, const int l, uint32_t ch, const uint32_t end, const float* lut_all,
+                                       const Clip* clip) {
+  const DevLeaf& L = p.leaf[l];
+  const Hyp h = load_hyper<OPT>(p.hyper[p.hyper_of[l]]);
+  const float* lut_m = lut_all;
+  const float* lut_v = lut_all + 256;
+  const float* lut_mw = lut_all + 512 + (STATE == FO_STATE_QUANT ? (threadIdx.x & (kLutCopies - 1)) : 0);
+  bool hyper_ok = (h.flags & FO_FLAG_LP_DELTA) == 0;  // as in the kernel: what the straight-line arithmetic may take
+  if constexpr (OPT == FO_OPT_ADAM) hyper_ok = hyper_ok && (h.flags & kFlagTameAdam) != 0;
+  const bool vector_ok = leaf_is_hot<OPT>(p, l) && hyper_ok &&
+                         (!AUX || (p.peers.n == 0 && p.peers.ng == 0 && p.peers.mc_pdelta == 0 && p.peers.mc_gdelta == 0));
+  Clip none;
+  none.active = false; none.div_ok = true; none.n_g = 1.0f; none.rcp_n = 1.0f; none.m_g = 1.0f;
+  for (; ch < end; ++ch) {
+    if (vector_ok)
+      ragged_chunk<OPT, PDT, ECC_BITS, STATE, AUX>(L, h, p.grad_dtype, ch * (uint32_t)kChunk, p.one, lut_mw, p.peers, clip, (uint32_t)L.n);
+    else
+      cold_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, (unsigned long long)ch * kChunk, lut_m, lut_v, p.peers, clip != nullptr ? *clip : none);
+  }
+}
+
+// Second walk over the runs of this block, for what the straight-line loop of step_kernel skipped.
+template <int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
+__device__ __noinline__ void block_tails(const StepParams& p, const float* lut_all) {
+  const Clip clip = load_clip(AUX ? p.sq_norm : nullptr, p.max_norm, p.grad_dtype);
+  const uint32_t total = p.first_block[p.n_leaves];
+  for (uint32_t run0 = blockIdx.x * p.run_chunks; run0 < total; run0 += gridDim.x * p.run_chunks) {
+    uint32_t c = run0;
+    const uint32_t c_hi = min(total, run0 + p.run_chunks);
+    int l_first = 0;
+    for (int l_end = p.n_leaves; l_end - l_first > 1;) {
+      const int mid = (l_first + l_end) >> 1;
+      if (p.first_block[mid] <= c) l_first = mid; else l_end = mid;
+    }
+    for (int l = l_first; l < p.n_leaves && c < c_hi; ++l) {
+      const uint32_t first = p.first_block[l];
+      const uint32_t next = min(p.first_block[l + 1], c_hi);
+      if (c >= next) continue;
+      const uint32_t end = next - first;
+      uint32_t ch = c - first;
+      const uint32_t flags = p.hyper[p.hyper_of[l]].dyn != nullptr ? load_hyper<OPT>(p.hyper[p.hyper_of[l]]).flags : p.hyper[p.hyper_of[l]].flags;
+      bool hyper_ok = (flags & FO_FLAG_LP_DELTA) == 0;
+      if constexpr (OPT == FO_OPT_ADAM) hyper_ok = hyper_ok && (flags & kFlagTameAdam) != 0;
+      const uint32_t hot_end = (leaf_is_hot<OPT>(p, l) && hyper_ok) ? min(end, (uint32_t)(p.leaf[l].n / kChunk)) : 0u;
+      if (ch < hot_end) ch = hot_end;  // those were done
+      if (ch < end) leaf_tail<OPT, PDT, ECC_BITS, STATE, AUX>(p, l, ch, end, lut_all, AUX ? &clip : nullptr);
+      c = next;
+    }
+  }
+}
+
 // Persistent grid.  The chunks of all leaves form one sequence (first_block[] gives each leaf's
 // first position in it) and block b takes positions b, b + grid, b + 2*grid, ...: at any moment
 // the blocks work on neighbouring chunks, which keeps the DRAM pages they stream from few.
@@ -1512,8 +1593,12 @@ FO_DEVI bool leaf_is_hot(const StepParams& p, int l) {
 // norm; the plain one carries none of that code or state.
 template <int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
 __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const __grid_constant__ StepParams p) {
-  __shared__ float lut_m[256], lut_v[256];
-  __shared__ float lut_m_wide[STATE == FO_STATE_QUANT ? 256 * kLutCopies : 1];
+  // one array for the three tables, so that the out-of-line paths need one pointer: [0, 256) momentum,
+  // [256, 512) second moment, [512, 512 + 256 * kLutCopies) the interleaved momentum copies
+  __shared__ float lut_all[512 + (STATE == FO_STATE_QUANT ? 256 * kLutCopies : 1)];
+  float* const lut_m = lut_all;
+  float* const lut_v = lut_all + 256;
+  float* const lut_m_wide = lut_all + 512;
   if constexpr (STATE == FO_STATE_QUANT) {
     build_luts(lut_m, lut_v);
     build_wide_lut(lut_m, lut_m_wide);
@@ -1658,21 +1743,27 @@ __global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_kernel(const _
         hot_finish<false, OPT, PDT, ECC_BITS, STATE, AUX>(L, h, p.grad_dtype, base, at, p.one, rare, u, lut_mw, p.peers, AUX ? &clip : nullptr);
       }
     }
-    // what is left of the leaf in this run: its ragged last chunk, or all of a leaf the straight-line path
-    // does not take.  An aligned leaf under ordinary hyper-parameters goes through the repairing pass with
-    // a limit (vector accesses, masked at the end); the scalar path keeps unaligned leaves, the CPU-path
-    // parameter hand-back and peer replicas.
-    const bool vector_ok = leaf_is_hot<OPT>(p, l) && hyper_ok &&
-                           (!AUX || (p.peers.n == 0 && p.peers.ng == 0 && p.peers.mc_pdelta == 0 && p.peers.mc_gdelta == 0));
-    for (; ch < end; ch += grid) {
-      if (vector_ok)
-        warm_chunk<OPT, PDT, ECC_BITS, STATE, AUX>(L, h, p.grad_dtype, ch * (uint32_t)kChunk, p.one, lut_mw, p.peers, AUX ? &clip : nullptr, (uint32_t)L.n);
-      else
-        cold_chunk<OPT, PDT, ECC_BITS, STATE>(L, h, p.grad_dtype, (unsigned long long)ch * kChunk, lut_m, lut_v, p.peers, clip);
-    }
+    ch = end;  // the rest of the leaf in this run is taken after the loop (block_tails)
     c = first + ch;
   }
   }
+  // What the loop left (ragged last chunks, leaves the straight-line path does not take) is the work of
+  // step_tail_kernel, a launch of its own: measured on the 80-register Lion / SGD kernels, a call to
+  // that code from this kernel, inside the leaf loop or after it, cost a quarter of their throughput
+  // (spills in the loop, no uniform registers).
+}
+
+// The same walk over the same runs for what step_kernel skipped; launched after it with the same grid
+// when the leaf table has a ragged end, an unaligned leaf or hyper-parameters outside the shortcuts'
+// range (the launcher looks).
+template <int OPT, int PDT, int ECC_BITS, int STATE, bool AUX>
+__global__ void __launch_bounds__(kThreads, min_blocks(OPT)) step_tail_kernel(const __grid_constant__ StepParams p) {
+  __shared__ float lut_all[512 + (STATE == FO_STATE_QUANT ? 256 * kLutCopies : 1)];
+  if constexpr (STATE == FO_STATE_QUANT) {
+    build_luts(lut_all, lut_all + 256);
+    build_wide_lut(lut_all, lut_all + 512);
+  }
+  block_tails<OPT, PDT, ECC_BITS, STATE, AUX>(p, lut_all);
 }
 
 // ---- any group size (1..1024): one block per tile of whole groups, group maxima through
@@ -1850,7 +1941,25 @@ cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStre
   unsigned int run = (info.total_chunks + grid * FO_RUN_DIV - 1u) / (grid * FO_RUN_DIV);
   p.run_chunks = run < 1u ? 1u : (run > FO_RUN_MAX ? FO_RUN_MAX : run);
   kernel<<<grid, kThreads, dynamic_smem, s>>>(p);
-  return cudaGetLastError();
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  // is there anything the straight-line loop leaves?  (device-resident scalars can move Adam's
+  // hyper-parameters out of the shortcuts' range at run time: then the tail kernel looks for itself)
+  bool need_tails = false;
+  for (int l = 0; l < p.n_leaves && !need_tails; ++l) {
+    const DevHyper& h = p.hyper[p.hyper_of[l]];
+    bool ok = (h.flags & FO_FLAG_LP_DELTA) == 0 && p.aligned[l] != 0;
+    if (OPT == FO_OPT_ADAM) ok = ok && (h.flags & kFlagTameAdam) != 0 && h.dyn == nullptr;
+    need_tails = !ok || p.leaf[l].n % (unsigned long long)kChunk != 0;
+  }
+#ifdef FO_NAIVE_MATH
+  need_tails = true;
+#endif
+  if (need_tails) {
+    step_tail_kernel<OPT, PDT, ECC_BITS, STATE, AUX><<<grid, kThreads, 0, s>>>(p);
+    e = cudaGetLastError();
+  }
+  return e;
 }
 template <int OPT, int PDT, int ECC_BITS>
 cudaError_t launch_step_generic(const StepParams& p, const LaunchInfo& info, cudaStream_t s) {
