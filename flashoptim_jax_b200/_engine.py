@@ -241,8 +241,8 @@ class PreparedLaunch:
             raise ValueError("peer_param_offsets and peer_grad_offsets must name the same peers")
         n_peers = max(len(self.peers), len(self.grad_peers))
         buckets: Dict[Tuple[Any, ...], List[Tuple[LeafWork, int]]] = {}
-        for w, gid in zip(work, group_ids):
-            buckets.setdefault(w.bucket, []).append((w, gid))
+        for i, (w, gid) in enumerate(zip(work, group_ids)):
+            buckets.setdefault(w.bucket, []).append((w, gid, i))
         self.calls: List[Dict[str, Any]] = []
         for key, items in buckets.items():
             dev_index, pdt, gdt, ecc_bits, state, group_size = key
@@ -250,18 +250,18 @@ class PreparedLaunch:
             while start < len(items):
                 slots: Dict[int, int] = {}
                 end = start
-                while end < len(items) and (items[end][1] in slots or len(slots) < _lib.FO_MAX_HYPERS):
+                while end < len(items) and (items[end][1] in slots or len(slots) < _lib.FO_MAX_HYPERS):  # noqa: E501
                     slots.setdefault(items[end][1], len(slots))
                     end += 1
                 part = items[start:end]
-                ws = [w for w, _ in part]
+                ws = [w for w, _, _ in part]
                 leaves = np.zeros(len(part), dtype=LEAF_DTYPE)
                 leaves["grad"] = [w.grad.data_ptr() for w in ws]
                 leaves["param"] = [w.param.data_ptr() for w in ws]
                 for name in ("ecc", "mu", "mu_scales", "nu", "nu_scales"):
                     leaves[name] = [_ptr(getattr(w, name)) for w in ws]
                 leaves["n"] = [w.param.numel() for w in ws]
-                leaves["hyper"] = [slots[gid] for _, gid in part]
+                leaves["hyper"] = [slots[gid] for _, gid, _ in part]
                 hypers = np.zeros(len(slots), dtype=HYPER_DTYPE)
                 desc = _lib.FoStepDesc(
                     struct_size=ctypes.sizeof(_lib.FoStepDesc), opt=opt, param_dtype=pdt, grad_dtype=gdt, ecc_bits=ecc_bits,
@@ -273,8 +273,15 @@ class PreparedLaunch:
                 desc.mc_param_offset, desc.mc_grad_offset = int(mc_param_offset), int(mc_grad_offset)
                 self.calls.append({"key": key, "desc": desc, "leaves": leaves, "hypers": hypers, "slots": list(slots.items()),
                                    "device": torch.device("cuda", dev_index), "n_params": int(leaves["n"].sum()),
+                                   "index": np.asarray([i for _, _, i in part], dtype=np.int64),
                                    "keep": ws})  # the tensors stay alive as long as their addresses are in the tables
                 start = end
+
+    def set_grads(self, grad_ptrs: np.ndarray, keep: List[torch.Tensor]) -> None:
+        """New gradient buffers for the same leaves (addresses in the order of the work list this was built from)."""
+        for call in self.calls:
+            call["leaves"]["grad"] = grad_ptrs[call["index"]]
+        self._grads_alive = keep
 
     def run(self, hyper_of_group: Dict[int, Tuple[Any, ...]]) -> int:
         lib = _lib.lib()
@@ -293,6 +300,82 @@ class PreparedLaunch:
             with torch.cuda.device(device), _observed(call["key"], call["n_params"]):
                 _lib.check(lib.fo_step(ctypes.byref(desc), stream_ptr(device)))
         return len(self.calls)
+
+
+class DonatedStepCache:
+    """The functional tx.step for callers that donate their buffers and hand each step's outputs to the
+    next: the parameter and state tensors are then the same objects step after step, and only the gradients
+    and the scalars change.  After one step through the general path this remembers the prepared launch of
+    that step, keyed on the identity and the addresses of every tensor of the returned trees; a later call
+    whose trees consist of exactly those tensors skips the per-leaf host work (path normalisation, param-group
+    matching, validation, table building: about 12 us per leaf) and replays the launch with new gradient
+    addresses and hyper-parameter values.  Anything else (other tensors, other gradient dtypes, non-contiguous
+    gradients) falls back to the general path, which then re-primes the cache."""
+
+    def __init__(self):
+        self.entry = None
+
+    @staticmethod
+    def _tensors(params: Any, state_trees: List[Any]) -> List[torch.Tensor]:
+        out = list(pytree.tree_leaves(params))
+        for tree in state_trees:
+            for leaf in pytree.tree_leaves(tree, is_leaf=_is_quantized_leaf):
+                if isinstance(leaf, QuantizedArray):
+                    out.append(leaf.values)
+                    out.append(leaf.scales)
+                else:
+                    out.append(leaf)
+        return out
+
+    def remember(self, opt: int, work: List[LeafWork], configs: List[Dict[str, Any]], params_out: Any, state_trees_out: List[Any]) -> None:
+        groups: List[Dict[str, Any]] = []
+        gids = []
+        for c in configs:
+            for i, g in enumerate(groups):
+                if g is c or g == c:
+                    gids.append(i)
+                    break
+            else:
+                groups.append(c)
+                gids.append(len(groups) - 1)
+        tensors = self._tensors(params_out, state_trees_out)
+        if not all(isinstance(t, torch.Tensor) for t in tensors):
+            self.entry = None
+            return
+        self.entry = {
+            "plan": PreparedLaunch(opt, work, gids), "groups": groups, "ids": [id(t) for t in tensors],
+            "treedef": pytree.tree_structure(params_out),
+            "ptrs": [t.data_ptr() for t in tensors], "alive": tensors, "params": params_out, "state": state_trees_out,
+            "grad_spec": [(w.grad.dtype, w.grad.shape, w.grad.device) for w in work],
+        }
+
+    def replay(self, params: Any, state_trees: List[Any], grads: Any, hyper_of_group) -> Optional[Tuple[Any, List[Any]]]:
+        """Runs the remembered launch if (params, state) are the remembered tensors; returns (params, state trees)
+        or None.  `hyper_of_group(config)` gives the hyper-parameter tuple of a param group for this step."""
+        e = self.entry
+        if e is None:
+            return None
+        if pytree.tree_structure(params) != e["treedef"]:
+            return None
+        tensors = self._tensors(params, state_trees)
+        if len(tensors) != len(e["ids"]):
+            return None
+        for t, i, ptr in zip(tensors, e["ids"], e["ptrs"]):
+            if id(t) != i or t.data_ptr() != ptr:
+                return None
+        g_leaves = pytree.tree_leaves(grads)
+        spec = e["grad_spec"]
+        if len(g_leaves) != len(spec):
+            return None
+        ptrs = np.empty(len(spec), dtype=np.uint64)
+        for k, (g, (dtype, shape, device)) in enumerate(zip(g_leaves, spec)):
+            if not isinstance(g, torch.Tensor) or g.dtype != dtype or g.shape != shape or g.device != device or not g.is_contiguous():
+                return None
+            ptrs[k] = g.data_ptr()
+        plan = e["plan"]
+        plan.set_grads(ptrs, g_leaves)
+        plan.run({gid: hyper_of_group(config) for gid, config in enumerate(e["groups"])})
+        return e["params"], e["state"]
 
 
 def launch(opt: int, work: List[LeafWork], peer_param_offsets: Optional[List[int]] = None,

@@ -83,9 +83,18 @@ def _make_adam_transform(learning_rate, b1, b2, eps, weight_decay, quantize, mas
         new_state = FlashAdamState(count=count, mu=treedef.unflatten(new_m), nu=treedef.unflatten(new_v), ecc=treedef.unflatten(new_e))
         return treedef.unflatten(new_p), new_state
 
+    cache = eng.DonatedStepCache()
+
     def step_fn(params: Any, state: FlashAdamState, grads: Any):
         old_count = as_tensor(state.count, dtype=torch.int32).cpu()
         count = int(old_count) + 1  # adamw.py:510
+        if donate:
+            hit = cache.replay(params, [state.ecc, state.mu, state.nu], grads, lambda config: adam_hyper(
+                config, utils._resolve_learning_rate(config["learning_rate"], old_count), count, decoupled_weight_decay))
+            if hit is not None:
+                ecc_t, mu_t, nu_t = hit[1]
+                return hit[0], FlashAdamState(count=torch.tensor(count, dtype=torch.int32), mu=mu_t, nu=nu_t, ecc=ecc_t)
+        configs: List[Dict[str, Any]] = []
         param_pl, grad_leaves, (ecc_leaves, mu_leaves, nu_leaves), treedef = eng.flatten_step_inputs(
             name, params, grads, [state.ecc, state.mu, state.nu])
         work: List[eng.LeafWork] = []
@@ -97,11 +106,15 @@ def _make_adam_transform(learning_rate, b1, b2, eps, weight_decay, quantize, mas
             hyper = adam_hyper(config, lr, count, decoupled_weight_decay)
             w, p_out, e_out, m_out, v_out = eng.make_work(leaf, g, e, m, v, config, hyper, donate, has_nu=True)
             work.append(w)
+            configs.append(config)
             new_p.append(p_out); new_e.append(e_out); new_m.append(m_out); new_v.append(v_out)
         eng.launch(_lib.FO_OPT_ADAM, work)
         new_state = FlashAdamState(count=torch.tensor(count, dtype=torch.int32), mu=treedef.unflatten(new_m),
                                    nu=treedef.unflatten(new_v), ecc=treedef.unflatten(new_e))
-        return treedef.unflatten(new_p), new_state
+        new_params = treedef.unflatten(new_p)
+        if donate:
+            cache.remember(_lib.FO_OPT_ADAM, work, configs, new_params, [new_state.ecc, new_state.mu, new_state.nu])
+        return new_params, new_state
 
     return utils.FlashOptimizer(init=init_fn, step=capturable_step_fn if capturable else step_fn)
 

@@ -87,8 +87,17 @@ def _make_sgd_transform(learning_rate, momentum, dampening, weight_decay, nester
         eng.launch(_lib.FO_OPT_SGD, work)
         return treedef.unflatten(new_p), FlashSGDState(count=count, mu=treedef.unflatten(new_m), ecc=treedef.unflatten(new_e))
 
+    cache = eng.DonatedStepCache()
+
     def step_fn(params: Any, state: FlashSGDState, grads: Any):
         old_count = as_tensor(state.count, dtype=torch.int32).cpu()
+        if donate:
+            hit = cache.replay(params, [state.ecc, state.mu], grads, lambda config: sgd_hyper(
+                config, utils._resolve_learning_rate(config["learning_rate"], old_count), decoupled_weight_decay))
+            if hit is not None:
+                ecc_t, mu_t = hit[1]
+                return hit[0], FlashSGDState(count=torch.tensor(int(old_count) + 1, dtype=torch.int32), mu=mu_t, ecc=ecc_t)
+        configs = []
         param_pl, grad_leaves, (ecc_leaves, mu_leaves), treedef = eng.flatten_step_inputs(
             name, params, grads, [state.ecc, state.mu])
         work, new_p, new_e, new_m = [], [], [], []
@@ -103,11 +112,15 @@ def _make_sgd_transform(learning_rate, momentum, dampening, weight_decay, nester
             w, p_out, e_out, m_out, _ = eng.make_work(leaf, g, e, m, None, config, hyper, donate, has_nu=False,
                                                       use_momentum=use_momentum)
             work.append(w)
+            configs.append(config)
             new_p.append(p_out); new_e.append(e_out); new_m.append(m_out)
         eng.launch(_lib.FO_OPT_SGD, work)
         new_state = FlashSGDState(count=torch.tensor(int(old_count) + 1, dtype=torch.int32),
                                   mu=treedef.unflatten(new_m), ecc=treedef.unflatten(new_e))
-        return treedef.unflatten(new_p), new_state
+        new_params = treedef.unflatten(new_p)
+        if donate:
+            cache.remember(_lib.FO_OPT_SGD, work, configs, new_params, [new_state.ecc, new_state.mu])
+        return new_params, new_state
 
     return utils.FlashOptimizer(init=init_fn, step=capturable_step_fn if capturable else step_fn)
 

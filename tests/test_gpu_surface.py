@@ -223,3 +223,47 @@ def test_step_argument_checks():
     # float64 grads are accepted (upcast rule of the reference: everything goes through fp32)
     p2, s2 = tx.step(params, state, {"a": torch.ones(64, dtype=torch.float64, device="cuda"), "b": torch.ones(3, device="cuda")})
     assert p2["a"].dtype == torch.bfloat16 and int(s2.count) == 1 and int(state.count) == 0
+
+
+@pytest.mark.gpu
+def test_donated_steps_replayed_from_the_prepared_launch_equal_plain_steps():
+    """With donate=True the second and later steps on the same tensors replay a prepared launch (only gradient
+    addresses and scalars are refreshed); new tensor objects, a new gradient dtype or a non-contiguous gradient
+    fall back to the general path.  Whatever the route, the results are those of the non-donating steps."""
+    import torch
+
+    import flashoptim_jax_b200 as fo
+    from flashoptim_jax_b200 import tree
+
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev).manual_seed(3)
+
+    def make():
+        g = torch.Generator(device=dev).manual_seed(5)
+        return {"w": (torch.randn((300, 70), device=dev, generator=g) * 0.02).to(torch.bfloat16),
+                "b": torch.zeros(70, device=dev), "v": [(torch.randn(5000, device=dev, generator=g) * 0.02).to(torch.bfloat16)]}
+
+    groups = [{"params": "b", "weight_decay": 0.0}]
+    fast = fo.flash_adamw(learning_rate=lambda c: 1e-3 / (1.0 + float(c)), master_weight_bits=32, param_groups=groups, donate=True)
+    plain = fo.flash_adamw(learning_rate=lambda c: 1e-3 / (1.0 + float(c)), master_weight_bits=32, param_groups=groups, donate=False)
+    pf, pp = make(), make()
+    sf, sp = fast.init(pf), plain.init(pp)
+    for t in range(8):
+        grads = tree.tree_map(lambda p: (torch.randn(p.shape, device=dev, generator=gen) * 1e-3).to(p.dtype), pp)
+        if t == 4:  # another gradient dtype for the 16-bit leaves: the prepared launch does not fit
+            grads = tree.tree_map(lambda g: g.float(), grads)
+        if t == 5:  # new tensor objects for the same values
+            pf = tree.tree_map(lambda x: x.clone(), pf)
+        if t == 6:  # a non-contiguous gradient
+            wide = torch.zeros((300, 140), device=dev, dtype=torch.bfloat16)
+            wide[:, ::2] = grads["w"]
+            grads = dict(grads, w=wide[:, ::2])
+        pf, sf = fast.step(pf, sf, grads)
+        pp, sp = plain.step(pp, sp, grads)
+    torch.cuda.synchronize()
+    assert int(sf.count) == int(sp.count) == 8
+    for a, b in zip(tree.tree_leaves(pf), tree.tree_leaves(pp)):
+        assert torch.equal(a, b)
+    for name in ("mu", "nu", "ecc"):
+        for a, b in zip(tree.tree_leaves(getattr(sf, name)), tree.tree_leaves(getattr(sp, name))):
+            assert a.dtype == b.dtype and torch.equal(a, b)
