@@ -36,9 +36,10 @@ if ROOT not in sys.path:
 METRIC = "optimizer-step params/sec"
 UNIT = "params/s"
 
-# DRAM bytes per parameter seen by one profiler capture of the bf16 / int16-ECC AdamW kernel on the
-# 2^26-element leaf (904.3 MB per 67,108,864 parameters); traffic is proportional to the parameter count
-NCU_DRAM_BYTES_PER_PARAM = 13.47
+# DRAM bytes per parameter (dram__bytes_read.sum + dram__bytes_write.sum) of one profiler capture of each
+# kernel on a 2^26-element bf16 leaf with bf16 gradients, keyed by (optimizer, ECC bits); traffic is
+# proportional to the parameter count.  AdamW / int16 ECC: 917.4 MB per 67,108,864 parameters.
+NCU_DRAM_BYTES_PER_PARAM = {("adamw", 16): 13.67, ("adamw", 8): 11.62, ("lion", 8): 9.56, ("sgdw", 8): 9.54}
 
 
 def bytes_per_param(optimizer: str, param_bytes: int, ecc_bits: int, grad_bytes: int) -> float:
@@ -585,9 +586,9 @@ def run_ours(args):
         psize = 4 if bucket[1] == 0 else 2
         bpp = bytes_per_param(optimizer, psize, bucket[3], 4 if bucket[2] == 0 else 2)
         achieved = n_par * bpp / (avg_ms * 1e-3) / 1e9
-        headline = optimizer == "adamw" and bucket[1] == 1 and bucket[3] == 16
+        captured = NCU_DRAM_BYTES_PER_PARAM.get((optimizer, bucket[3])) if bucket[1] == 1 and bucket[2] == 1 else None
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "traffic": NCU_DRAM_BYTES_PER_PARAM * n_par if headline else None,
+                    "traffic": captured * n_par if captured is not None else None,
                     "kernel": f"step_kernel<{optimizer}, {'f32' if bucket[1] == 0 else ('bf16' if bucket[1] == 1 else 'f16')}, ecc{bucket[3]}, quant>",
                     "params_per_launch": n_par, "avg_launch_ms": avg_ms, "launches_timed": len(pool[top]),
                     "algorithmic_bytes_per_param": bpp, "peak_source": peak_src}

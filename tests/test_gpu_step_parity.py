@@ -112,8 +112,15 @@ def test_many_steps_exercise_bias_correction_and_saturation():
             H.assert_leaf_equal(dev.to_host(), ref, f"opt {opt} ecc {ecc_bits} after 100 steps")
 
 
-def test_extreme_values_take_the_guarded_paths():
+@pytest.mark.parametrize("opt,conv,hp_kw", [
+    (C.ADAM, O.FUSED, dict(lr=1e-3, wd=1e-2)),
+    (C.LION, O.FUSED, dict(lr=1e-4, wd=1e-2, b2=0.99)),
+    (C.LION, O.UNFUSED, dict(lr=1e-4, wd=1e-2, b2=0.99)),
+    (C.SGD, O.FUSED, dict(lr=1e-2, wd=1e-2, momentum=0.9)),
+], ids=["adam", "lion-fused", "lion-unfused", "sgd"])
+def test_extreme_values_take_the_guarded_paths(opt, conv, hp_kw):
     # zeros, subnormals, huge and tiny gradients and weights: exercises every fallback of the shortcuts
+    # (scattered exact zeros also give Lion interpolations that are exactly zero, whose sign is zero)
     import torch
 
     rng = np.random.default_rng(11)
@@ -124,17 +131,17 @@ def test_extreme_values_take_the_guarded_paths():
     p32[::7] = 0.0
     for pdt, ecc_bits in ((1, 8), (1, 16), (2, 16), (0, 0)):
         pnp = (np.clip(p32, -1e3, 1e3) if pdt == 2 else p32).astype(H.NP_OF_CODE[pdt])  # keep fp16 finite
-        ref = H.fresh_leaf(pnp, C.ADAM, C.STATE_QUANT, ecc_bits)
+        ref = H.fresh_leaf(pnp, opt, C.STATE_QUANT, ecc_bits)
         dev = ref.copy().to_device()
         for t in range(1, 4):
             g32 = np.ldexp(rng.normal(0, 1, n), rng.integers(-140, 12, n)).astype(np.float32)  # |m| stays below the fp16 scale range
             g32[::5] = 0.0
             g32[64:128] = 0.0  # whole groups of zeros
-            hp = H.hyper_tuple(C.ADAM, O.FUSED, t, lr=1e-3, wd=1e-2)
-            H.oracle_step(C.ADAM, g32, ref, C.STATE_QUANT, 32, hp)
-            H.abi_step(C.ADAM, [H.to_torch(g32)], [dev], C.STATE_QUANT, 32, [hp], [0], pdt, 0, ecc_bits)
+            hp = H.hyper_tuple(opt, conv, t, **hp_kw)
+            H.oracle_step(opt, g32, ref, C.STATE_QUANT, 32, hp)
+            H.abi_step(opt, [H.to_torch(g32)], [dev], C.STATE_QUANT, 32, [hp], [0], pdt, 0, ecc_bits)
             torch.cuda.synchronize()
-            H.assert_leaf_equal(dev.to_host(), ref, f"extreme pdt {pdt} ecc {ecc_bits} step {t}")
+            H.assert_leaf_equal(dev.to_host(), ref, f"extreme opt {opt} pdt {pdt} ecc {ecc_bits} step {t}")
 
 
 def test_untamed_hyper_parameters_use_ieee_divisions():
