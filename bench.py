@@ -565,6 +565,9 @@ def run_ours(args):
                                     "note": "each rank's kernel on its own slice with its own gradients, no collective; aggregate over ranks"}
         ag_ms = median(timed(lambda: zero.step(phases=("step", "all_gather")), args.steps, 3))
         legs["step_and_allgather"] = {"ms_per_step": ag_ms, "value": total_params / (ag_ms * 1e-3), "unit": UNIT}
+        rs_ms = median(timed(lambda: zero.step(phases=("reduce_scatter", "step")), args.steps, 3))
+        legs["reducescatter_and_step"] = {"ms_per_step": rs_ms, "value": total_params / (rs_ms * 1e-3), "unit": UNIT,
+                                          "note": "replicas are left stale by this leg and gathered again after it"}
         legs["full_step"] = {"ms_per_step": ms_per_step, "value": value, "unit": UNIT}
         zero.all_gather_params()  # the replicas agree again
         barrier()
