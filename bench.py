@@ -24,6 +24,7 @@ import argparse
 import json
 import math
 import os
+import random
 import subprocess
 import sys
 import threading
@@ -662,6 +663,150 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+SQUARE_SIZES = (256, 512, 1024, 2048, 4096, 8192, 16384)
+SQUARE_HP = {"adamw": dict(learning_rate=1e-3, b1=0.9, b2=0.999, eps=1e-8, weight_decay=1e-2),
+             "lion": dict(learning_rate=1e-4, b1=0.9, b2=0.99, weight_decay=1e-2),
+             "sgdw": dict(learning_rate=1e-2, momentum=0.9, weight_decay=1e-2)}
+
+
+def percentile(xs, q):
+    xs = sorted(xs)
+    return xs[min(len(xs) - 1, int(math.ceil(q * len(xs))) - 1)]
+
+
+def square_graph_samples(optimizer, hparams, n, k, n_samples, device, gen, rng):
+    """The same case through the functional surface with the step's scalars formed on the device
+    (capturable=True): k calls of tx.step captured in one CUDA graph, one replay per sample."""
+    import torch
+
+    import flashoptim_jax_b200 as fo
+
+    factory = {"adamw": fo.flash_adamw, "lion": fo.flash_lion, "sgdw": fo.flash_sgdw}[optimizer]
+    lr = torch.tensor(float(hparams["learning_rate"]), dtype=torch.float32, device=device)
+    tx = factory(**dict(hparams, learning_rate=lr), donate=True, capturable=True)
+    params = {"w": make_param((n, n), "bf16", device, gen)}
+    grads = {"w": torch.empty_like(params["w"])}
+    fill_grad(grads["w"], 1e-3, 1e-4, gen)
+    state = tx.init(params)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):  # eager once: moves the counter to the device, loads the kernels
+        for _ in range(5):
+            params, state = tx.step(params, state, grads)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(k):
+            params, state = tx.step(params, state, grads)
+    samples = []
+    for it in range(-1, n_samples):
+        fill_grad(grads["w"], 10.0 ** rng.uniform(-4.0, -1.0), 1e-4, gen)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= 0:
+            samples.append(e0.elapsed_time(e1) / k)
+    del graph
+    return samples
+
+
+def run_square_sweep(args):
+    """The square-matrix sweep of the reference's step benchmark (examples/benchmark_square_step_all.sh:7-12,
+    examples/benchmark_step.py:144-157): one bf16 N x N parameter, N = 256 .. 16384, under flash_adamw / flash_lion /
+    flash_sgdw with 24- and 32-bit master weights; bf16 gradients N(0, sigma) with sigma log-uniform in
+    [1e-4, 1e-1] redrawn for every sample and 0.01 % of the entries scaled by 100.  Protocol as the reference's:
+    5 warm-up steps, then samples of k back-to-back steps between synchronisations, CUDA events around the k
+    steps, median and 95th percentile over the samples; 100 timed steps per case.  One JSON line: the headline
+    value is the largest AdamW case with 32-bit master weights, every case is listed under "sweep"."""
+    quiet_stdout()
+    import torch
+
+    from flashoptim_jax_b200 import tree as pytree
+    from flashoptim_jax_b200.zero1 import Zero1Optimizer
+
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise SystemExit("the square sweep is a single-GPU workload")
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    k, n_samples = 10, 10
+    rng = random.Random(7)
+    sampler = ClockSampler(0)
+    sampler.start()
+    sweep, launches = [], 0
+    for optimizer in ("adamw", "lion", "sgdw"):
+        for mwb in (24, 32):
+            for n in SQUARE_SIZES:
+                gen = torch.Generator(device=device)
+                gen.manual_seed(n + mwb)
+                hparams = dict(SQUARE_HP[optimizer], master_weight_bits=mwb)
+                zero = Zero1Optimizer(optimizer, {"w": make_param((n, n), "bf16", device, gen)}, **hparams)
+                g = zero.grads["w"]
+                samples = []
+                for it in range(-1, n_samples):  # sample -1: the warm-up steps
+                    fill_grad(g, 10.0 ** rng.uniform(-4.0, -1.0), 1e-4, gen)
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(5 if it < 0 else k):
+                        zero.step()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    if it >= 0:
+                        samples.append(e0.elapsed_time(e1) / k)
+                        launches += k
+                bpp = bytes_per_param(optimizer, 2, 8 if mwb == 24 else 16, 2)
+                ms = median(samples)
+                case = {"optimizer": "flash_" + optimizer, "n": n, "master_weight_bits": mwb, "params": n * n,
+                        "ms_per_step": ms, "ms_per_step_p95": percentile(samples, 0.95), "params_per_s": n * n / (ms * 1e-3),
+                        "gb_per_s": n * n * bpp / (ms * 1e-3) / 1e9, "frac_of_peak": n * n * bpp / (ms * 1e-3) / 1e9 / peak,
+                        "l2_resident": n * n * bpp < 126e6}
+                if not args.no_parity:
+                    chk = parity_check(zero, device)
+                    case["parity_mismatches"] = chk["mismatches"]
+                    if chk.get("detail"):
+                        print(f"{optimizer} {n} mwb {mwb}: parity mismatches: {chk['detail']}", file=sys.stderr)
+                del zero, g
+                torch.cuda.empty_cache()
+                graph_samples = square_graph_samples(optimizer, hparams, n, k, n_samples, device, gen, rng)
+                launches += k * n_samples
+                case["cuda_graph"] = {"ms_per_step": median(graph_samples), "ms_per_step_p95": percentile(graph_samples, 0.95),
+                                      "params_per_s": n * n / (median(graph_samples) * 1e-3)}
+                sweep.append(case)
+                torch.cuda.empty_cache()
+    clocks = sampler.stop()
+    head = next(c for c in sweep if c["optimizer"] == "flash_adamw" and c["master_weight_bits"] == 32 and c["n"] == SQUARE_SIZES[-1])
+    emit({
+        "metric": METRIC, "value": head["params_per_s"], "unit": UNIT, "n_gpus": 1, "steps": k * n_samples, "warmup": 5,
+        "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "square_sweep", "headline": "flash_adamw, 16384 x 16384 bf16, 32-bit master weights",
+                   "sizes": list(SQUARE_SIZES), "optimizers": ["flash_adamw", "flash_lion", "flash_sgdw"], "master_weight_bits": [24, 32],
+                   "hparams": SQUARE_HP, "grad_dtype": "bf16", "grad_sigma": "log-uniform in [1e-4, 1e-1] per sample", "grad_outliers": 1e-4,
+                   "protocol": f"5 warm-up steps, {n_samples} samples of {k} back-to-back steps, median and p95 over the samples; "
+                               "cuda_graph: the same k steps as one captured graph of tx.step calls (scalars formed on the device)",
+                   "l2": "cases marked l2_resident touch less than the 126 MB L2 per step and run from it (no flush): their GB/s is "
+                         "not an HBM figure; the others exceed L2"},
+        "roofline": {"bound": "hbm", "achieved": head["gb_per_s"], "peak": peak, "unit": "GB/s", "frac": head["frac_of_peak"],
+                     "traffic": NCU_DRAM_BYTES_PER_PARAM[("adamw", 16)] * head["params"], "kernel": "step_kernel<adamw, bf16, ecc16, quant>",
+                     "params_per_launch": head["params"], "avg_launch_ms": head["ms_per_step"], "peak_source": peak_src,
+                     "algorithmic_bytes_per_param": bytes_per_param("adamw", 2, 16, 2)},
+        "cpu_baseline": None, "e2e": None, "gpu_launches": launches, "clocks": clocks,
+        "parity_check": None if args.no_parity else {"cases": len(sweep), "mismatches": sum(c["parity_mismatches"] for c in sweep),
+                                                     "against": "C oracle (reference's fused-kernel text), bit for bit, one step after each case's timed steps"},
+        "sweep": sweep,
+    })
+
+
+
 def measure_public_api(optimizer, hparams, params, zero, args, sigma, outliers):
     """The same step through the public surface, tx.init / tx.step with donated buffers (what a user of the
     reference's API calls), host cost of flattening and table building included."""
@@ -751,7 +896,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the median region is reported")
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="llama3_8b")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["square_sweep"], default="llama3_8b")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (used for profiler captures)")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of one more step after the timed region")
@@ -773,6 +918,8 @@ def main():
     args.repeats = max(1, args.repeats)
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "square_sweep":
+        run_square_sweep(args)
     else:
         run_ours(args)
 

@@ -1939,22 +1939,39 @@ cudaError_t launch_step(const StepParams& p_in, const LaunchInfo& info, cudaStre
 #define FO_RUN_MAX 192u
 #endif
   unsigned int run = (info.total_chunks + grid * FO_RUN_DIV - 1u) / (grid * FO_RUN_DIV);
+  // is there anything the straight-line loop leaves (a ragged end, a misaligned leaf, hyper-parameters
+  // outside the shortcuts' range)?  Device-resident scalars can move Adam's hyper-parameters out of that
+  // range at run time: then the tail kernel is launched to look for itself.
+  bool dynamic = false;
+  int tails = 0;  // leaves with work for the tail kernel
+  for (int l = 0; l < p.n_leaves; ++l) {
+    const DevHyper& h = p.hyper[p.hyper_of[l]];
+    bool ok = (h.flags & FO_FLAG_LP_DELTA) == 0 && p.aligned[l] != 0;
+    if (OPT == FO_OPT_ADAM) {
+      ok = ok && (h.flags & kFlagTameAdam) != 0;
+      dynamic = dynamic || h.dyn != nullptr;
+    }
+    if (!ok || p.leaf[l].n % (unsigned long long)kChunk != 0) ++tails;
+  }
+#ifdef FO_NAIVE_MATH
+  tails = p.n_leaves;
+#endif
+  const bool ragged = tails > 0;
+  // A launch of at most FO_RUN_WHOLE chunks per block with next to no tail work is dealt out as one run
+  // per block: it lasts tens of microseconds, a second fill and drain of the pipeline per block shows
+  // (4 M parameters: 31 -> 24 us), and an uneven count of short runs per block costs more than it
+  // spreads.  (With many ragged leaves in the table the short runs stay: they spread the tail kernel's
+  // work, which follows the same runs, over four times as many blocks.)
+#ifndef FO_RUN_WHOLE
+#define FO_RUN_WHOLE 32u
+#endif
+  const unsigned int share = (info.total_chunks + grid - 1u) / grid;
+  if (share <= FO_RUN_WHOLE && tails <= 4) run = share;
   p.run_chunks = run < 1u ? 1u : (run > FO_RUN_MAX ? FO_RUN_MAX : run);
   kernel<<<grid, kThreads, dynamic_smem, s>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  // is there anything the straight-line loop leaves?  (device-resident scalars can move Adam's
-  // hyper-parameters out of the shortcuts' range at run time: then the tail kernel looks for itself)
-  bool need_tails = false;
-  for (int l = 0; l < p.n_leaves && !need_tails; ++l) {
-    const DevHyper& h = p.hyper[p.hyper_of[l]];
-    bool ok = (h.flags & FO_FLAG_LP_DELTA) == 0 && p.aligned[l] != 0;
-    if (OPT == FO_OPT_ADAM) ok = ok && (h.flags & kFlagTameAdam) != 0 && h.dyn == nullptr;
-    need_tails = !ok || p.leaf[l].n % (unsigned long long)kChunk != 0;
-  }
-#ifdef FO_NAIVE_MATH
-  need_tails = true;
-#endif
+  const bool need_tails = ragged || dynamic;
   if (need_tails) {
     step_tail_kernel<OPT, PDT, ECC_BITS, STATE, AUX><<<grid, kThreads, 0, s>>>(p);
     e = cudaGetLastError();
