@@ -316,16 +316,20 @@ class DonatedStepCache:
         self.entry = None
 
     @staticmethod
-    def _tensors(params: Any, state_trees: List[Any]) -> List[torch.Tensor]:
-        out = list(pytree.tree_leaves(params))
+    def _tensors(params: Any, state_trees: List[Any]) -> Tuple[List[torch.Tensor], List[Any]]:
+        """Every tensor of the trees in flattening order, and the trees' structural signature."""
+        out, sig = pytree.tree_leaves_and_signature(params)
+        sig.append(len(out))
         for tree in state_trees:
-            for leaf in pytree.tree_leaves(tree, is_leaf=_is_quantized_leaf):
+            leaves, s = pytree.tree_leaves_and_signature(tree, is_leaf=_is_quantized_leaf)
+            sig.append(s)
+            for leaf in leaves:
                 if isinstance(leaf, QuantizedArray):
                     out.append(leaf.values)
                     out.append(leaf.scales)
                 else:
                     out.append(leaf)
-        return out
+        return out, sig
 
     def remember(self, opt: int, work: List[LeafWork], configs: List[Dict[str, Any]], params_out: Any, state_trees_out: List[Any]) -> None:
         groups: List[Dict[str, Any]] = []
@@ -338,13 +342,13 @@ class DonatedStepCache:
             else:
                 groups.append(c)
                 gids.append(len(groups) - 1)
-        tensors = self._tensors(params_out, state_trees_out)
+        tensors, sig = self._tensors(params_out, state_trees_out)
         if not all(isinstance(t, torch.Tensor) for t in tensors):
             self.entry = None
             return
         self.entry = {
             "plan": PreparedLaunch(opt, work, gids), "groups": groups, "ids": [id(t) for t in tensors],
-            "treedef": pytree.tree_structure(params_out),
+            "sig": sig,
             "ptrs": [t.data_ptr() for t in tensors], "alive": tensors, "params": params_out, "state": state_trees_out,
             "grad_spec": [(w.grad.dtype, w.grad.shape, w.grad.device) for w in work],
         }
@@ -355,10 +359,8 @@ class DonatedStepCache:
         e = self.entry
         if e is None:
             return None
-        if pytree.tree_structure(params) != e["treedef"]:
-            return None
-        tensors = self._tensors(params, state_trees)
-        if len(tensors) != len(e["ids"]):
+        tensors, sig = self._tensors(params, state_trees)
+        if len(tensors) != len(e["ids"]) or sig != e["sig"]:
             return None
         for t, i, ptr in zip(tensors, e["ids"], e["ptrs"]):
             if id(t) != i or t.data_ptr() != ptr:

@@ -121,8 +121,53 @@ def tree_flatten_with_path(tree: Any, is_leaf: Optional[Callable[[Any], bool]] =
     return out, treedef
 
 
+def _walk(x: Any, is_leaf: Optional[Callable[[Any], bool]], out: List[Any], sig: Optional[List[Any]]) -> None:
+    """The leaves of x in flattening order, without paths or TreeDef objects; `sig`, when given, receives one
+    entry per container in pre-order (kind with keys / type / length, and the number of leaves seen before
+    it): two trees have the same structure iff their leaf counts and these lists agree (a child slot whose
+    turn comes when the leaf count equals the next container's offset must be that container)."""
+    if is_leaf is not None and is_leaf(x):
+        out.append(x)
+    elif x is None:
+        if sig is not None:
+            sig.append((None, len(out)))
+    elif isinstance(x, dict):
+        try:
+            keys = sorted(x)
+        except TypeError:
+            keys = list(x)
+        if sig is not None:
+            sig.append(("dict", tuple(keys), len(out)))
+        for k in keys:
+            _walk(x[k], is_leaf, out, sig)
+    elif isinstance(x, tuple):
+        fields = getattr(type(x), "_fields", None)
+        if sig is not None:
+            sig.append((type(x) if fields is not None else "tuple", len(x), len(out)))
+        for v in x:
+            _walk(v, is_leaf, out, sig)
+    elif isinstance(x, list):
+        if sig is not None:
+            sig.append(("list", len(x), len(out)))
+        for v in x:
+            _walk(v, is_leaf, out, sig)
+    else:
+        out.append(x)
+
+
 def tree_leaves(tree: Any, is_leaf: Optional[Callable[[Any], bool]] = None) -> List[Any]:
-    return tree_flatten(tree, is_leaf)[0]
+    out: List[Any] = []
+    _walk(tree, is_leaf, out, None)
+    return out
+
+
+def tree_leaves_and_signature(tree: Any, is_leaf: Optional[Callable[[Any], bool]] = None) -> Tuple[List[Any], List[Any]]:
+    """Leaves plus a cheap structural signature (see _walk): equal signatures and leaf counts mean equal
+    tree structures.  For hot paths that re-check a structure on every call."""
+    out: List[Any] = []
+    sig: List[Any] = []
+    _walk(tree, is_leaf, out, sig)
+    return out, sig
 
 
 def tree_structure(tree: Any, is_leaf: Optional[Callable[[Any], bool]] = None) -> TreeDef:
