@@ -52,6 +52,29 @@ SMALL_CASES = [
 ]
 
 
+# Further cases through the other constructors and options of the public surface: (name, constructor,
+# keyword arguments, elements, parameter dtype, gradient dtype).
+VARIANT_CASES = [
+    ("adam_coupled_fused", "flash_adam", dict(learning_rate=1e-3, weight_decay=1e-2, master_weight_bits=24, fused=True), 1300, "bfloat16", "bfloat16"),
+    ("adam_coupled_unfused", "flash_adam", dict(learning_rate=1e-3, weight_decay=1e-2, master_weight_bits=32, fused=False), 1300, "bfloat16", "bfloat16"),
+    ("sgd_coupled_nesterov_fused", "flash_sgd", dict(learning_rate=1e-2, momentum=0.9, weight_decay=1e-2, nesterov=True, master_weight_bits=24, fused=True), 1111, "bfloat16", "bfloat16"),
+    ("sgd_coupled_nesterov_unfused", "flash_sgd", dict(learning_rate=1e-2, momentum=0.9, weight_decay=1e-2, nesterov=True, master_weight_bits=24, fused=False), 1111, "bfloat16", "bfloat16"),
+    ("sgdw_dampening_fused", "flash_sgdw", dict(learning_rate=1e-2, momentum=0.9, dampening=0.1, weight_decay=1e-2, master_weight_bits=32, fused=True), 999, "bfloat16", "bfloat16"),
+    ("sgdw_dampening_unfused", "flash_sgdw", dict(learning_rate=1e-2, momentum=0.9, dampening=0.1, weight_decay=1e-2, master_weight_bits=24, fused=False), 999, "float16", "bfloat16"),
+    ("sgdw_no_momentum", "flash_sgdw", dict(learning_rate=1e-2, momentum=0.0, weight_decay=1e-2, master_weight_bits=24), 700, "bfloat16", "bfloat16"),
+    ("adamw_full_state", "flash_adamw", dict(learning_rate=1e-3, weight_decay=1e-2, quantize=False, master_weight_bits=24), 600, "bfloat16", "bfloat16"),
+    ("lion_full_state", "flash_lion", dict(learning_rate=1e-4, weight_decay=1e-2, quantize=False, master_weight_bits=32), 600, "bfloat16", "bfloat16"),
+    ("sgdw_full_state", "flash_sgdw", dict(learning_rate=1e-2, momentum=0.9, weight_decay=1e-2, quantize=False, master_weight_bits=None), 600, "float32", "float32"),
+    ("adamw_group64_unfused", "flash_adamw", dict(learning_rate=1e-3, weight_decay=1e-2, group_size=64, master_weight_bits=24, fused=False), 1000, "bfloat16", "bfloat16"),
+    ("lion_group8_unfused", "flash_lion", dict(learning_rate=1e-4, weight_decay=1e-2, group_size=8, master_weight_bits=24, fused=False), 333, "bfloat16", "bfloat16"),
+    ("adamw_fp32_grads_fused", "flash_adamw", dict(learning_rate=1e-3, weight_decay=1e-2, master_weight_bits=24, fused=True), 2100, "bfloat16", "float32"),
+    ("adamw_fp16_grads_unfused", "flash_adamw", dict(learning_rate=1e-3, weight_decay=1e-2, master_weight_bits=32, fused=False), 2100, "float16", "float16"),
+    ("lion_betas_fused", "flash_lion", dict(learning_rate=3e-4, b1=0.95, b2=0.98, weight_decay=0.1, master_weight_bits=24, fused=True), 1500, "bfloat16", "bfloat16"),
+    ("adamw_betas_eps_fused", "flash_adamw", dict(learning_rate=3e-4, b1=0.8, b2=0.95, eps=1e-6, weight_decay=0.1, master_weight_bits=32, fused=True), 1500, "bfloat16", "bfloat16"),
+]
+NP_DTYPES = {"bfloat16": BF16, "float16": np.dtype(np.float16), "float32": np.dtype(np.float32)}
+
+
 def import_reference(path):
     """The reference package, unmodified, on top of the stand-in."""
     if not os.path.isdir(os.path.join(path, "flashoptim_jax")):
@@ -101,6 +124,37 @@ def small_case(ref, seed, n, dtype, mwb, opt, convention, steps=3):
     out.update(param=bits(params["x"]), mu=np.asarray(state.mu["x"].values), mu_scales=bits(state.mu["x"].scales))
     if opt == "adamw":
         out.update(nu=np.asarray(state.nu["x"].values), nu_scales=bits(state.nu["x"].scales))
+    ecc = np.asarray(state.ecc["x"])
+    if ecc.shape != ():
+        out["ecc"] = ecc
+    for k, v in out.items():
+        assert v.dtype != np.float64, k
+    return out
+
+
+def variant_case(ref, seed, factory, kwargs, n, dtype, grad_dtype, steps=3):
+    """Like small_case for any constructor / keyword arguments; a moment kept in full precision
+    (quantize=False) is stored as `mu_full` / `nu_full`, an absent one (momentum 0) not at all."""
+    rng = np.random.default_rng(seed)
+    p = rng.normal(0, 0.02, n).astype(np.float32).astype(NP_DTYPES[dtype])
+    grads = [rng.normal(0, 1e-3, n).astype(np.float32).astype(NP_DTYPES[grad_dtype]) for _ in range(steps)]
+    out = {"param0": bits(p), "grads": np.stack([bits(g) for g in grads])}
+    tx = getattr(ref, factory)(**kwargs)
+    params = {"x": p}
+    state = tx.init(params)
+    for g in grads:
+        params, state = tx.step(params, state, {"x": g})
+    assert int(state.count) == steps
+    out["param"] = bits(params["x"])
+    for name in ("mu", "nu"):
+        if not hasattr(state, name):
+            continue
+        m = getattr(state, name)["x"]
+        if hasattr(m, "values"):
+            out[name] = np.asarray(m.values)
+            out[name + "_scales"] = bits(m.scales)
+        elif np.asarray(m).shape != ():
+            out[name + "_full"] = np.asarray(m)
     ecc = np.asarray(state.ecc["x"])
     if ecc.shape != ():
         out["ecc"] = ecc
@@ -176,7 +230,7 @@ def main():
     ap.add_argument("--check", action="store_true")
     args = ap.parse_args()
     ref = import_reference(args.reference)
-    check_pow((0.9, 0.999), range(1, 11))
+    check_pow((0.9, 0.999, 0.8, 0.95), range(1, 11))
 
     bad = []
     cases = {}
@@ -186,6 +240,10 @@ def main():
         files[name + ".npz"] = small_case(ref, 1000 + i, n, dtype, mwb, opt, convention)
         cases[name] = {"n": n, "dtype": np.dtype(dtype).name, "master_weight_bits": mwb, "optimizer": opt,
                        "convention": convention}
+    variants = {}
+    for i, (name, factory, kwargs, n, dtype, grad_dtype) in enumerate(VARIANT_CASES):
+        files[f"variant_{name}.npz"] = variant_case(ref, 2000 + i, factory, kwargs, n, dtype, grad_dtype)
+        variants[name] = {"constructor": factory, "kwargs": kwargs, "n": n, "dtype": dtype, "grad_dtype": grad_dtype}
     files["codecs.npz"] = codec_vectors(ref)
     for fname, arrays in files.items():
         path = os.path.join(HERE, fname)
@@ -195,7 +253,7 @@ def main():
         else:
             with open(path, "wb") as f:
                 f.write(npz_bytes(arrays))
-    for fname, obj in (("cases.json", cases), ("config1_digests.json", config1_digests(ref))):
+    for fname, obj in (("cases.json", cases), ("variants.json", variants), ("config1_digests.json", config1_digests(ref))):
         path = os.path.join(HERE, fname)
         if args.check:
             if not os.path.exists(path) or json.load(open(path)) != obj:
@@ -205,7 +263,7 @@ def main():
                 json.dump(obj, f, indent=1)
     if bad:
         raise SystemExit("fixtures differ from the reference's output: " + ", ".join(bad))
-    print("checked" if args.check else "written", len(files) + 2, "fixtures")
+    print("checked" if args.check else "written", len(files) + 3, "fixtures")
 
 
 if __name__ == "__main__":

@@ -215,6 +215,83 @@ def test_python_surface_reproduces_golden(name, donate):
     H.assert_leaf_equal(got, want, name)
 
 
+VARIANTS = json.load(open(os.path.join(GOLD, "variants.json")))
+VARIANT_OPT = {"flash_adam": (C.ADAM, False), "flash_adamw": (C.ADAM, True), "flash_lion": (C.LION, True),
+               "flash_sgd": (C.SGD, False), "flash_sgdw": (C.SGD, True)}  # constructor -> (optimizer, decoupled weight decay)
+
+
+def _load_variant(name):
+    meta = VARIANTS[name]
+    z = np.load(os.path.join(GOLD, f"variant_{name}.npz"))
+    dt, gdt = NP_DT[meta["dtype"]], NP_DT[meta["grad_dtype"]]
+    view = lambda a, d: a.view(d) if d.itemsize == 2 else a  # noqa: E731
+    want = H.LeafArrays(view(z["param"], dt), z["ecc"] if "ecc" in z else None,
+                        z["mu"] if "mu" in z else (z["mu_full"] if "mu_full" in z else None),
+                        z["mu_scales"].view(np.float16) if "mu_scales" in z else None,
+                        z["nu"] if "nu" in z else (z["nu_full"] if "nu_full" in z else None),
+                        z["nu_scales"].view(np.float16) if "nu_scales" in z else None)
+    return meta, view(z["param0"], dt), [view(g, gdt) for g in z["grads"]], want
+
+
+@pytest.mark.parametrize("name", sorted(VARIANTS))
+def test_c_oracle_reproduces_variants(name):
+    """The other constructors and options of the reference's surface (coupled weight decay, Nesterov, dampening, no
+    momentum buffer, full-precision moments, other group sizes, betas and eps, fp32 / fp16 gradients)."""
+    meta, p0, grads, want = _load_variant(name)
+    kw = meta["kwargs"]
+    opt, decoupled = VARIANT_OPT[meta["constructor"]]
+    no_buffer = opt == C.SGD and kw.get("momentum", 0.0) == 0.0
+    state = C.STATE_NONE if no_buffer else (C.STATE_QUANT if kw.get("quantize", True) else C.STATE_FULL)
+    conv = O.FUSED if kw.get("fused", True) and not no_buffer else O.UNFUSED
+    ecc_bits = {None: 0, 24: 8, 32: 16}[kw["master_weight_bits"]] if p0.dtype.itemsize == 2 else 0
+    gs = kw.get("group_size", 32)
+    hyper = dict(lr=kw["learning_rate"], wd=kw.get("weight_decay", 0.0), decoupled=decoupled)
+    for k in ("b1", "b2", "eps", "momentum", "dampening", "nesterov"):
+        if k in kw:
+            hyper[k] = kw[k]
+    if opt == C.LION:
+        hyper.setdefault("b2", 0.99)
+        hyper.pop("decoupled")
+    if opt == C.SGD:
+        hyper.setdefault("momentum", 0.0)
+    leaf = H.fresh_leaf(p0, opt, state, ecc_bits, gs)
+    for t, g in enumerate(grads, 1):
+        H.oracle_step(opt, g, leaf, state, gs, H.hyper_tuple(opt, conv, t, **hyper))
+    H.assert_leaf_equal(leaf, want, name)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(VARIANTS))
+def test_python_surface_reproduces_variants(name):
+    """The same constructor calls on this package give the reference's bits."""
+    import torch
+
+    import flashoptim_jax_b200 as fo
+
+    meta, p0, grads, want = _load_variant(name)
+    tx = getattr(fo, meta["constructor"])(donate=True, **meta["kwargs"])
+    params = {"x": H.to_torch(p0)}
+    state = tx.init(params)
+    for g in grads:
+        params, state = tx.step(params, state, {"x": H.to_torch(g)})
+    torch.cuda.synchronize()
+    assert int(state.count) == len(grads)
+
+    def moment(name):
+        if not hasattr(state, name):
+            return None, None
+        m = getattr(state, name)["x"]
+        if isinstance(m, fo.QuantizedArray):
+            return H.to_numpy(m.values), H.to_numpy(m.scales)
+        return (None if m.dim() == 0 else H.to_numpy(m)), None
+
+    ecc = state.ecc["x"]
+    mu, mu_s = moment("mu")
+    nu, nu_s = moment("nu")
+    got = H.LeafArrays(H.to_numpy(params["x"]), None if ecc.dim() == 0 else H.to_numpy(ecc), mu, mu_s, nu, nu_s)
+    H.assert_leaf_equal(got, want, name)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("convention", ["fused", "unfused"])
 def test_config1_digests(convention):
