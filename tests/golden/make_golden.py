@@ -74,6 +74,33 @@ VARIANT_CASES = [
 ]
 NP_DTYPES = {"bfloat16": BF16, "float16": np.dtype(np.float16), "float32": np.dtype(np.float32)}
 
+# Nested pytrees with mixed dtypes and param groups (string, "a/b" path and tuple selectors; first match wins):
+# (name, constructor, keyword arguments, [(path, shape, dtype), ...]); gradients have each leaf's dtype.
+BLOCK_LEAVES = [(("attn", "kernel"), (96, 64), "bfloat16"), (("attn", "bias"), (64,), "bfloat16"),
+                (("ln", "scale"), (64,), "float32"), (("ln", "bias"), (64,), "float32"),
+                (("head", "kernel"), (64, 33), "bfloat16"), (("head", "bias"), (33,), "float32")]
+TREE_CASES = [
+    ("block_adamw_groups", "flash_adamw",
+     dict(learning_rate=1e-3, weight_decay=1e-2, master_weight_bits=24, fused=True,
+          param_groups=[{"params": ("head", "bias"), "learning_rate": 2e-3, "weight_decay": 0.0},
+                        {"params": "bias", "weight_decay": 0.0},
+                        {"params": "ln/scale", "weight_decay": 0.0, "learning_rate": 5e-4, "b2": 0.99},
+                        {"params": "head", "fused": False}]), BLOCK_LEAVES),
+    ("block_sgd_groups", "flash_sgd",
+     dict(learning_rate=1e-2, momentum=0.9, weight_decay=1e-3, master_weight_bits=32, fused=True,
+          param_groups=[{"params": "bias", "weight_decay": 0.0, "nesterov": True},
+                        {"params": "attn/kernel", "learning_rate": 5e-3, "dampening": 0.1}]), BLOCK_LEAVES),
+    ("block_lion_groups", "flash_lion",
+     dict(learning_rate=1e-4, weight_decay=1e-2, master_weight_bits=24, fused=False,
+          param_groups=[{"params": "ln", "weight_decay": 0.0, "b1": 0.95},
+                        {"params": ("attn", "kernel"), "fused": True}]), BLOCK_LEAVES),
+]
+
+
+def tuples_in(groups):
+    """JSON has no tuples: selectors stored as lists come back as tuples."""
+    return [{k: (tuple(v) if k == "params" and isinstance(v, list) else v) for k, v in g.items()} for g in groups]
+
 
 def import_reference(path):
     """The reference package, unmodified, on top of the stand-in."""
@@ -163,6 +190,58 @@ def variant_case(ref, seed, factory, kwargs, n, dtype, grad_dtype, steps=3):
     return out
 
 
+def nest(pairs):
+    tree = {}
+    for path, value in pairs:
+        node = tree
+        for key in path[:-1]:
+            node = node.setdefault(key, {})
+        node[path[-1]] = value
+    return tree
+
+
+def tree_case(ref, seed, factory, kwargs, leaves, steps=3):
+    """A nested pytree through the reference; arrays are stored under "<a/b>|<field>"."""
+    rng = np.random.default_rng(seed)
+    p0 = [(path, rng.normal(0, 0.02, shape).astype(np.float32).astype(NP_DTYPES[dt])) for path, shape, dt in leaves]
+    out = {}
+    for path, p in p0:
+        out["/".join(path) + "|param0"] = bits(p)
+    tx = getattr(ref, factory)(**dict(kwargs, param_groups=tuples_in(kwargs["param_groups"])))
+    params = nest(p0)
+    state = tx.init(params)
+    for t in range(steps):
+        g = [(path, rng.normal(0, 1e-3, shape).astype(np.float32).astype(NP_DTYPES[dt])) for path, shape, dt in leaves]
+        for path, a in g:
+            out["/".join(path) + f"|grad{t}"] = bits(a)
+        params, state = tx.step(params, state, nest(g))
+    assert int(state.count) == steps
+
+    def at(tree, path):
+        for key in path:
+            tree = tree[key]
+        return tree
+
+    for path, _, _ in leaves:
+        tag = "/".join(path)
+        out[tag + "|param"] = bits(at(params, path))
+        for name in ("mu", "nu"):
+            if not hasattr(state, name):
+                continue
+            m = at(getattr(state, name), path)
+            if hasattr(m, "values"):
+                out[f"{tag}|{name}"] = np.asarray(m.values)
+                out[f"{tag}|{name}_scales"] = bits(m.scales)
+            elif np.asarray(m).shape != ():
+                out[f"{tag}|{name}_full"] = np.asarray(m)
+        ecc = np.asarray(at(state.ecc, path))
+        if ecc.shape != ():
+            out[tag + "|ecc"] = ecc
+    for k, v in out.items():
+        assert v.dtype != np.float64, k
+    return out
+
+
 def config1_digests(ref):
     """Benchmark config 1: one 2048x2048 bf16 matrix N(0, 0.02), grads bf16 N(0, 1e-3), 10 AdamW steps,
     lr 1e-3, betas (0.9, 0.999), eps 1e-8, wd 1e-2, 24-bit master, seed 0; both texts of the reference."""
@@ -230,7 +309,7 @@ def main():
     ap.add_argument("--check", action="store_true")
     args = ap.parse_args()
     ref = import_reference(args.reference)
-    check_pow((0.9, 0.999, 0.8, 0.95), range(1, 11))
+    check_pow((0.9, 0.999, 0.8, 0.95, 0.99), range(1, 11))
 
     bad = []
     cases = {}
@@ -244,6 +323,11 @@ def main():
     for i, (name, factory, kwargs, n, dtype, grad_dtype) in enumerate(VARIANT_CASES):
         files[f"variant_{name}.npz"] = variant_case(ref, 2000 + i, factory, kwargs, n, dtype, grad_dtype)
         variants[name] = {"constructor": factory, "kwargs": kwargs, "n": n, "dtype": dtype, "grad_dtype": grad_dtype}
+    trees = {}
+    for i, (name, factory, kwargs, leaves) in enumerate(TREE_CASES):
+        files[f"tree_{name}.npz"] = tree_case(ref, 3000 + i, factory, kwargs, leaves)
+        trees[name] = {"constructor": factory, "kwargs": json.loads(json.dumps(kwargs)),
+                       "leaves": [[list(path), list(shape), dt] for path, shape, dt in leaves]}
     files["codecs.npz"] = codec_vectors(ref)
     for fname, arrays in files.items():
         path = os.path.join(HERE, fname)
@@ -253,7 +337,8 @@ def main():
         else:
             with open(path, "wb") as f:
                 f.write(npz_bytes(arrays))
-    for fname, obj in (("cases.json", cases), ("variants.json", variants), ("config1_digests.json", config1_digests(ref))):
+    for fname, obj in (("cases.json", cases), ("variants.json", variants), ("trees.json", trees),
+                       ("config1_digests.json", config1_digests(ref))):
         path = os.path.join(HERE, fname)
         if args.check:
             if not os.path.exists(path) or json.load(open(path)) != obj:
@@ -263,7 +348,7 @@ def main():
                 json.dump(obj, f, indent=1)
     if bad:
         raise SystemExit("fixtures differ from the reference's output: " + ", ".join(bad))
-    print("checked" if args.check else "written", len(files) + 3, "fixtures")
+    print("checked" if args.check else "written", len(files) + 4, "fixtures")
 
 
 if __name__ == "__main__":

@@ -292,6 +292,107 @@ def test_python_surface_reproduces_variants(name):
     H.assert_leaf_equal(got, want, name)
 
 
+TREES = json.load(open(os.path.join(GOLD, "trees.json")))
+
+
+def _tree_kwargs(meta):
+    kw = dict(meta["kwargs"])
+    kw["param_groups"] = [{k: (tuple(v) if k == "params" and isinstance(v, list) else v) for k, v in g.items()}
+                          for g in kw["param_groups"]]
+    return kw
+
+
+def _nest(pairs):
+    tree = {}
+    for path, value in pairs:
+        node = tree
+        for key in path[:-1]:
+            node = node.setdefault(key, {})
+        node[path[-1]] = value
+    return tree
+
+
+def _at(tree, path):
+    for key in path:
+        tree = tree[key]
+    return tree
+
+
+def _tree_leaf_want(z, tag, dt):
+    view = lambda a: a.view(dt) if dt.itemsize == 2 else a  # noqa: E731
+    get = lambda f: z[f"{tag}|{f}"] if f"{tag}|{f}" in z else None  # noqa: E731
+    scales = lambda f: None if get(f) is None else get(f).view(np.float16)  # noqa: E731
+    return H.LeafArrays(view(z[tag + "|param"]), get("ecc"), get("mu") if get("mu") is not None else get("mu_full"), scales("mu_scales"),
+                        get("nu") if get("nu") is not None else get("nu_full"), scales("nu_scales"))
+
+
+@pytest.mark.parametrize("name", sorted(TREES))
+def test_param_groups_resolved_as_the_reference_resolves_them(name):
+    """Nested pytrees with string, "a/b" and tuple selectors, first match wins, per-group learning rate, weight decay,
+    betas, Nesterov, dampening and `fused`: this package's group resolution feeding the C oracle leaf by leaf gives the
+    arrays the reference produced."""
+    from flashoptim_jax_b200 import utils
+
+    meta = TREES[name]
+    kw = _tree_kwargs(meta)
+    groups = kw.pop("param_groups")
+    z = np.load(os.path.join(GOLD, f"tree_{name}.npz"))
+    opt, decoupled = VARIANT_OPT[meta["constructor"]]
+    for path, _shape, dtype in meta["leaves"]:
+        path, dt, tag = tuple(path), NP_DT[dtype], "/".join(path)
+        p0 = z[tag + "|param0"].view(dt) if dt.itemsize == 2 else z[tag + "|param0"]
+        cfg = utils._group_config_for_path(path, p0, defaults=kw, param_groups=groups)
+        conv = O.FUSED if cfg.get("fused", True) else O.UNFUSED
+        ecc_bits = {None: 0, 24: 8, 32: 16}[cfg["master_weight_bits"]] if dt.itemsize == 2 else 0
+        hyper = dict(lr=cfg["learning_rate"], wd=cfg.get("weight_decay", 0.0), decoupled=decoupled)
+        for k in ("b1", "b2", "eps", "momentum", "dampening", "nesterov"):
+            if k in cfg:
+                hyper[k] = cfg[k]
+        if opt == C.LION:
+            hyper.setdefault("b2", 0.99)
+            hyper.pop("decoupled")
+        leaf = H.fresh_leaf(p0.reshape(-1), opt, C.STATE_QUANT, ecc_bits)
+        for t in range(3):
+            g = z[f"{tag}|grad{t}"]
+            H.oracle_step(opt, (g.view(dt) if dt.itemsize == 2 else g).reshape(-1), leaf, C.STATE_QUANT, 32, H.hyper_tuple(opt, conv, t + 1, **hyper))
+        want = _tree_leaf_want(z, tag, dt)
+        want.param, want.ecc, want.mu, want.nu = (None if a is None else a.reshape(-1) for a in (want.param, want.ecc, want.mu, want.nu))
+        H.assert_leaf_equal(leaf, want, f"{name} {tag}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(TREES))
+def test_python_surface_reproduces_trees(name):
+    import torch
+
+    import flashoptim_jax_b200 as fo
+
+    meta = TREES[name]
+    z = np.load(os.path.join(GOLD, f"tree_{name}.npz"))
+    leaves = [(tuple(path), NP_DT[dtype]) for path, _shape, dtype in meta["leaves"]]
+    view = lambda a, dt: a.view(dt) if dt.itemsize == 2 else a  # noqa: E731
+    tx = getattr(fo, meta["constructor"])(donate=True, **_tree_kwargs(meta))
+    params = _nest([(path, H.to_torch(view(z["/".join(path) + "|param0"], dt))) for path, dt in leaves])
+    state = tx.init(params)
+    for t in range(3):
+        grads = _nest([(path, H.to_torch(view(z["/".join(path) + f"|grad{t}"], dt))) for path, dt in leaves])
+        params, state = tx.step(params, state, grads)
+    torch.cuda.synchronize()
+    assert int(state.count) == 3
+    for path, dt in leaves:
+        tag = "/".join(path)
+        ecc = _at(state.ecc, path)
+        mom = {}
+        for field in ("mu", "nu"):
+            m = _at(getattr(state, field), path) if hasattr(state, field) else None
+            if isinstance(m, fo.QuantizedArray):
+                mom[field] = (H.to_numpy(m.values), H.to_numpy(m.scales))
+            else:
+                mom[field] = (None if m is None or m.dim() == 0 else H.to_numpy(m), None)
+        got = H.LeafArrays(H.to_numpy(_at(params, path)), None if ecc.dim() == 0 else H.to_numpy(ecc), *mom["mu"], *mom["nu"])
+        H.assert_leaf_equal(got, _tree_leaf_want(z, tag, dt), f"{name} {tag}")
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("convention", ["fused", "unfused"])
 def test_config1_digests(convention):
