@@ -239,7 +239,15 @@ def tree_case(ref, seed, factory, kwargs, leaves, steps=3):
             out[tag + "|ecc"] = ecc
     for k, v in out.items():
         assert v.dtype != np.float64, k
-    return out
+    # the checkpoint form of this state (flash_*_state_dict): kinds, dtypes and shapes of the serialized leaves in order
+    to_sd = getattr(ref, {"flash_adam": "flash_adamw", "flash_sgdw": "flash_sgd"}.get(factory, factory) + "_state_dict")
+    sd = to_sd(state)
+    layout = {"count": [str(np.asarray(sd["count"]).dtype), list(np.asarray(sd["count"]).shape)]}
+    for field in sorted(k for k in sd if k != "count"):
+        layout[field] = [{"kind": leaf["kind"],
+                          **{k: [str(np.asarray(v).dtype), list(np.asarray(v).shape)] for k, v in leaf.items() if k != "kind"}}
+                         for leaf in sd[field]["leaves"]]
+    return out, layout
 
 
 def config1_digests(ref):
@@ -325,9 +333,9 @@ def main():
         variants[name] = {"constructor": factory, "kwargs": kwargs, "n": n, "dtype": dtype, "grad_dtype": grad_dtype}
     trees = {}
     for i, (name, factory, kwargs, leaves) in enumerate(TREE_CASES):
-        files[f"tree_{name}.npz"] = tree_case(ref, 3000 + i, factory, kwargs, leaves)
+        files[f"tree_{name}.npz"], layout = tree_case(ref, 3000 + i, factory, kwargs, leaves)
         trees[name] = {"constructor": factory, "kwargs": json.loads(json.dumps(kwargs)),
-                       "leaves": [[list(path), list(shape), dt] for path, shape, dt in leaves]}
+                       "leaves": [[list(path), list(shape), dt] for path, shape, dt in leaves], "state_dict": layout}
     files["codecs.npz"] = codec_vectors(ref)
     for fname, arrays in files.items():
         path = os.path.join(HERE, fname)

@@ -391,6 +391,19 @@ def test_python_surface_reproduces_trees(name):
                 mom[field] = (None if m is None or m.dim() == 0 else H.to_numpy(m), None)
         got = H.LeafArrays(H.to_numpy(_at(params, path)), None if ecc.dim() == 0 else H.to_numpy(ecc), *mom["mu"], *mom["nu"])
         H.assert_leaf_equal(got, _tree_leaf_want(z, tag, dt), f"{name} {tag}")
+    # the checkpoint form: kinds, dtypes and shapes of the serialized leaves in the reference's order, and a round trip
+    stem = {"flash_adam": "flash_adamw", "flash_sgdw": "flash_sgd"}.get(meta["constructor"], meta["constructor"])
+    sd = getattr(fo, stem + "_state_dict")(state)
+    describe = lambda t: [str(t.dtype).replace("torch.", ""), list(t.shape)]  # noqa: E731
+    layout = {"count": describe(torch.as_tensor(sd["count"]))}
+    for field in sorted(k for k in sd if k != "count"):
+        layout[field] = [{"kind": leaf["kind"], **{k: describe(v) for k, v in leaf.items() if k != "kind"}} for leaf in sd[field]["leaves"]]
+    assert layout == meta["state_dict"]
+    back = getattr(fo, "load_" + stem + "_state_dict")(sd)
+    from flashoptim_jax_b200 import tree as pytree
+
+    for a, b in zip(pytree.tree_leaves(back), pytree.tree_leaves(state)):
+        assert torch.equal(torch.as_tensor(a), torch.as_tensor(b))
 
 
 @pytest.mark.gpu
