@@ -55,6 +55,37 @@ def test_fo_step_rejects_bad_descriptors_without_touching_a_gpu():
     assert lib.fo_step(ctypes.byref(d), None) == 0  # nothing to do
 
 
+def test_structural_signature_distinguishes_exactly_what_treedefs_distinguish():
+    """tree_leaves_and_signature is the cheap structure check of the donated-step cache: over random nestings of
+    dicts, lists, tuples and None, equal (leaf count, signature) must mean equal TreeDef and the other way round."""
+    import random
+
+    rnd = random.Random(0)
+
+    def grow(depth=0):
+        r = rnd.random()
+        if depth > 3 or r < 0.4:
+            return 0
+        if r < 0.5:
+            return None
+        if r < 0.7:
+            return [grow(depth + 1) for _ in range(rnd.randint(0, 3))]
+        if r < 0.85:
+            return tuple(grow(depth + 1) for _ in range(rnd.randint(0, 3)))
+        return {k: grow(depth + 1) for k in rnd.sample("abcd", rnd.randint(0, 3))}
+
+    by_sig, by_def = {}, {}
+    for _ in range(4000):
+        t = grow()
+        leaves, sig = tree.tree_leaves_and_signature(t)
+        assert leaves == tree.tree_flatten(t)[0] == tree.tree_leaves(t)
+        key, td = (len(leaves), repr(sig)), tree.tree_structure(t)
+        assert by_sig.setdefault(key, td) == td
+        assert by_def.setdefault(td, key) == key
+    assert len(by_sig) == len(by_def) > 500
+    assert tree.tree_leaves_and_signature([1, [2]])[1] != tree.tree_leaves_and_signature([[1], 2])[1]
+
+
 def test_pytree_flattening_follows_jax_rules():
     t = {"b": [1, (2, 3)], "a": {"z": 4, "y": None}, "c": fo.FlashOptimizer(init=5, step=6)}
     leaves, td = tree.tree_flatten(t)
