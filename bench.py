@@ -829,7 +829,35 @@ def measure_public_api(optimizer, hparams, params, zero, args, sigma, outliers):
             params, state = tx.step(params, state, grads)
         torch.cuda.synchronize()
         samples.append((time.perf_counter() - t0) / args.steps * 1e3)
-    return {"ms_per_step": median(samples), "all": samples, "note": "tx.step(params, state, grads) with donate=True, wall clock including the host side"}
+    out = {"ms_per_step": median(samples), "all": samples, "note": "tx.step(params, state, grads) with donate=True, wall clock including the host side"}
+    # the same steps with the scalars formed on the device, captured once as a CUDA graph and replayed
+    lr = torch.tensor(float(hparams["learning_rate"]), dtype=torch.float32, device=grads[next(iter(grads))].device)
+    tx = factory(**dict(hparams, learning_rate=lr), donate=True, capturable=True)
+    state = tx.init(params)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            params, state = tx.step(params, state, grads)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(args.steps):
+            params, state = tx.step(params, state, grads)
+    graph.replay()
+    torch.cuda.synchronize()
+    replays = []
+    for _ in range(args.repeats):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        replays.append(e0.elapsed_time(e1) / args.steps)
+    out["cuda_graph"] = {"ms_per_step": median(replays), "all": replays,
+                         "note": f"{args.steps} calls of tx.step(capturable=True) captured in one CUDA graph, one replay per sample, CUDA events"}
+    return out
 
 
 def measure_e2e(args, zero, device, ggen, world, barrier, total_params, sigma):
