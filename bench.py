@@ -153,6 +153,8 @@ WORKLOADS = {
     "adamw24_leaf_64m": (one_leaf_shapes, "adamw", dict(LLAMA_HP, master_weight_bits=24), 1e-4, 0.0),
     "lion_leaf_64m": (one_leaf_shapes, "lion", dict(learning_rate=1e-4, b1=0.9, b2=0.99, weight_decay=1e-2, master_weight_bits=24), 1e-4, 0.0),
     "sgdw_leaf_64m": (one_leaf_shapes, "sgdw", dict(learning_rate=1e-2, momentum=0.9, weight_decay=1e-2, master_weight_bits=24), 1e-4, 0.0),
+    # fp32 parameters and gradients (no ECC): the third kind of leaf the kernels take
+    "adamw_f32_leaf_64m": (lambda: {"w": ((8192, 8192), "f32")}, "adamw", dict(LLAMA_HP, master_weight_bits=None), 1e-4, 0.0),
     "resnet50": (resnet50_shapes, "sgdw", dict(learning_rate=0.1, momentum=0.9, weight_decay=1e-4, master_weight_bits=24,
                                                param_groups=[{"params": _no_decay, "weight_decay": 0.0}]), 1e-3, 0.0),
     "gpt2_small": (gpt2_small_shapes, "adamw", dict(learning_rate=1e-3, b1=0.9, b2=0.999, eps=1e-8, weight_decay=1e-2,
@@ -179,6 +181,8 @@ def make_param(shape, kind, device, gen):
         return (torch.randn(shape, device=device, generator=gen) * math.sqrt(2.0 / fan_in)).to(torch.bfloat16)
     if kind == "bf16_zeros":
         return torch.zeros(shape, device=device, dtype=torch.bfloat16)
+    if kind == "f32":
+        return torch.randn(shape, device=device, generator=gen) * 0.02
     if kind == "f32_ones":
         return torch.ones(shape, device=device, dtype=torch.float32)
     if kind == "f32_zeros":
