@@ -310,7 +310,10 @@ class DonatedStepCache:
     whose trees consist of exactly those tensors skips the per-leaf host work (path normalisation, param-group
     matching, validation, table building: about 12 us per leaf) and replays the launch with new gradient
     addresses and hyper-parameter values.  Anything else (other tensors, other gradient dtypes, non-contiguous
-    gradients) falls back to the general path, which then re-primes the cache."""
+    gradients) falls back to the general path, which then re-primes the cache.  A replayed step keeps the
+    param-group membership of the remembered call: selectors are functions of the path and of the leaf's
+    shape / dtype in every use the reference shows, and a selector that reads a leaf's *values* is not
+    re-evaluated while the same tensors come back."""
 
     def __init__(self):
         self.entry = None
