@@ -432,10 +432,16 @@ class Zero1Optimizer:
                                                    peers, grad_peers, mc_param, mc_grad) if chosen else None
         if plan is None:
             return 0
-        count_before = torch.tensor(self.count, dtype=torch.int32)
+        count_before = None
         hypers = {}
         for gid, config in enumerate(self._group_configs):
-            lr = utils._resolve_learning_rate(config["learning_rate"], count_before)
+            lr = config["learning_rate"]
+            if callable(lr):  # a schedule sees the pre-increment count as a tensor, as in the reference
+                if count_before is None:
+                    count_before = torch.tensor(self.count, dtype=torch.int32)
+                lr = utils._resolve_learning_rate(lr, count_before)
+            else:
+                lr = utils._resolve_learning_rate(lr, self.count)
             hypers[gid] = self._hyper(config, lr, self.count + 1)
         return plan.run(hypers)
 
@@ -455,11 +461,19 @@ class Zero1Optimizer:
         return self.flat_params[b][sl * slice_len:(sl + 1) * slice_len], layout.piece
 
     def reduce_scatter_grads(self) -> None:
+        if self.world_size == 1:
+            aliased = self.__dict__.get("_one_rank_alias")
+            if aliased is None:  # one rank: the "shard" normally is the flat buffer itself
+                aliased = self._one_rank_alias = all(s.data_ptr() == f.data_ptr() for s, f in zip(self.grad_shards, self.flat_grads))
+            if aliased:
+                return
         for b, sl in self._slices():
             out, full = self._rs_args(b, sl)
             _reduce_scatter_mean(out, full, self.group, self.world_size)
 
     def all_gather_params(self) -> None:
+        if self.world_size == 1:
+            return
         for b, sl in self._slices():
             full, piece = self._ag_args(b, sl)
             _all_gather_inplace(full, piece, self.group, self.world_size)
