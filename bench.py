@@ -746,8 +746,8 @@ def run_square_sweep(args):
     sampler = ClockSampler(0)
     sampler.start()
     sweep, launches = [], 0
-    primer = Zero1Optimizer("adamw", {"w": make_param((256, 256), "bf16", device, torch.Generator(device=device))}, **SQUARE_HP["adamw"])
-    for _ in range(50):  # first use of the library in this process: module loading, allocator and clocks
+    primer = Zero1Optimizer("adamw", {"w": make_param((4096, 4096), "bf16", device, torch.Generator(device=device))}, **SQUARE_HP["adamw"])
+    for _ in range(500):  # first use of the library in this process: module loading, allocator, and the clocks leave idle
         primer.step()
     torch.cuda.synchronize()
     del primer

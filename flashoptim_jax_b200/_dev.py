@@ -31,7 +31,13 @@ def require_cuda(t: torch.Tensor, what: str) -> None:
         )
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)  # the handle without a Stream object around it
+
+
 def stream_ptr(device: torch.device) -> int:
+    """Handle of torch's current stream on `device` (what every launch of this package runs on)."""
+    if _raw_stream is not None and device.index is not None:
+        return _raw_stream(device.index)
     return torch.cuda.current_stream(device).cuda_stream
 
 
