@@ -121,6 +121,9 @@ def tree_flatten_with_path(tree: Any, is_leaf: Optional[Callable[[Any], bool]] =
     return out, treedef
 
 
+_CONTAINERS = (dict, tuple, list)
+
+
 def _walk(x: Any, is_leaf: Optional[Callable[[Any], bool]], out: List[Any], sig: Optional[List[Any]]) -> None:
     """The leaves of x in flattening order, without paths or TreeDef objects; `sig`, when given, receives one
     entry per container in pre-order (kind with keys / type / length, and the number of leaves seen before
@@ -128,31 +131,35 @@ def _walk(x: Any, is_leaf: Optional[Callable[[Any], bool]], out: List[Any], sig:
     turn comes when the leaf count equals the next container's offset must be that container)."""
     if is_leaf is not None and is_leaf(x):
         out.append(x)
-    elif x is None:
+        return
+    if x is None:
         if sig is not None:
             sig.append((None, len(out)))
-    elif isinstance(x, dict):
+        return
+    if isinstance(x, dict):
         try:
             keys = sorted(x)
         except TypeError:
             keys = list(x)
         if sig is not None:
             sig.append(("dict", tuple(keys), len(out)))
-        for k in keys:
-            _walk(x[k], is_leaf, out, sig)
+        children = [x[k] for k in keys]
     elif isinstance(x, tuple):
-        fields = getattr(type(x), "_fields", None)
         if sig is not None:
-            sig.append((type(x) if fields is not None else "tuple", len(x), len(out)))
-        for v in x:
-            _walk(v, is_leaf, out, sig)
+            sig.append((type(x) if hasattr(type(x), "_fields") else "tuple", len(x), len(out)))
+        children = x
     elif isinstance(x, list):
         if sig is not None:
             sig.append(("list", len(x), len(out)))
-        for v in x:
-            _walk(v, is_leaf, out, sig)
+        children = x
     else:
         out.append(x)
+        return
+    for v in children:  # leaves are taken here, without a call of their own
+        if v is not None and not isinstance(v, _CONTAINERS) and (is_leaf is None or not is_leaf(v)):
+            out.append(v)
+        else:
+            _walk(v, is_leaf, out, sig)
 
 
 def tree_leaves(tree: Any, is_leaf: Optional[Callable[[Any], bool]] = None) -> List[Any]:
