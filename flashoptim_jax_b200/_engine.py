@@ -369,9 +369,11 @@ class DonatedStepCache:
         tensors, sig = self._tensors(params, state_trees)
         if len(tensors) != len(e["ids"]) or sig != e["sig"]:
             return None
-        for t, i, ptr in zip(tensors, e["ids"], e["ptrs"]):
-            if id(t) != i or t.data_ptr() != ptr:
+        try:  # the same objects at the same addresses (C-level loops: this check runs on every step)
+            if list(map(id, tensors)) != e["ids"] or list(map(torch.Tensor.data_ptr, tensors)) != e["ptrs"]:
                 return None
+        except TypeError:  # something that is not a tensor
+            return None
         g_leaves = pytree.tree_leaves(grads)
         spec = e["grad_spec"]
         if len(g_leaves) != len(spec):
