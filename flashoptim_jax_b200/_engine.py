@@ -543,14 +543,23 @@ def flush_copies() -> None:
 def flatten_step_inputs(name: str, params, grads, state_trees: List[Any]):
     """Flatten params / grads / state trees and check that they line up (adamw.py:511-519)."""
     _copies.pairs = []  # a step that failed half-way leaves nothing behind
-    grad_pl, grad_def = _tree_leaves_with_paths(grads)
     param_pl, treedef = _tree_leaves_with_paths(params)
+    # the usual case, all trees alike, is settled by the cheap structural signatures; anything else goes
+    # through the structure objects below, which tell the cases apart for the error messages
+    _, want = pytree.tree_leaves_and_signature(params)
+    grad_leaves, sig = pytree.tree_leaves_and_signature(grads)
+    alike = sig == want and len(grad_leaves) == len(param_pl)
     flat_states = []
-    for i, st in enumerate(state_trees):
-        leaves, st_def = pytree.tree_flatten(st, is_leaf=_is_quantized_leaf)
-        if st_def != treedef:
-            raise ValueError(f"{name} state trees must match parameter structure")
+    for st in state_trees:
+        leaves, sig = pytree.tree_leaves_and_signature(st, is_leaf=_is_quantized_leaf)
+        alike = alike and sig == want and len(leaves) == len(param_pl)
         flat_states.append(leaves)
+    if alike:
+        return param_pl, grad_leaves, flat_states, treedef
+    grad_pl, grad_def = _tree_leaves_with_paths(grads)
+    for st in state_trees:
+        if pytree.tree_structure(st, is_leaf=_is_quantized_leaf) != treedef:
+            raise ValueError(f"{name} state trees must match parameter structure")
     if grad_def != treedef:
         raise ValueError(f"{name} state trees must match parameter structure")
     if [p for p, _ in param_pl] != [p for p, _ in grad_pl]:

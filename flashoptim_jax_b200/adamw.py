@@ -99,11 +99,14 @@ def _make_adam_transform(learning_rate, b1, b2, eps, weight_decay, quantize, mas
             name, params, grads, [state.ecc, state.mu, state.nu])
         work: List[eng.LeafWork] = []
         new_p, new_e, new_m, new_v = [], [], [], []
+        resolve, hypers = utils.GroupResolver(defaults, param_groups), {}
         for (path, leaf), g, e, m, v in zip(param_pl, grad_leaves, ecc_leaves, mu_leaves, nu_leaves):
             leaf = as_tensor(leaf)
-            config = utils._group_config_for_path(path, leaf, defaults, param_groups)
-            lr = utils._resolve_learning_rate(config["learning_rate"], old_count)  # zero-based count (adamw.py:526)
-            hyper = adam_hyper(config, lr, count, decoupled_weight_decay)
+            config = resolve(path, leaf)
+            hyper = hypers.get(id(config))
+            if hyper is None:  # once per param group
+                lr = utils._resolve_learning_rate(config["learning_rate"], old_count)  # zero-based count (adamw.py:526)
+                hyper = hypers[id(config)] = adam_hyper(config, lr, count, decoupled_weight_decay)
             w, p_out, e_out, m_out, v_out = eng.make_work(leaf, g, e, m, v, config, hyper, donate, has_nu=True)
             work.append(w)
             configs.append(config)

@@ -82,11 +82,13 @@ def flash_lion(learning_rate=1e-4, b1: float = 0.9, b2: float = 0.99, weight_dec
         param_pl, grad_leaves, (ecc_leaves, mu_leaves), treedef = eng.flatten_step_inputs(
             name, params, grads, [state.ecc, state.mu])
         work, new_p, new_e, new_m = [], [], [], []
+        resolve, hypers = utils.GroupResolver(defaults, param_groups), {}
         for (path, leaf), g, e, m in zip(param_pl, grad_leaves, ecc_leaves, mu_leaves):
             leaf = as_tensor(leaf)
-            config = utils._group_config_for_path(path, leaf, defaults, param_groups)
-            lr = utils._resolve_learning_rate(config["learning_rate"], old_count)
-            hyper = lion_hyper(config, lr)
+            config = resolve(path, leaf)
+            hyper = hypers.get(id(config))
+            if hyper is None:  # once per param group
+                hyper = hypers[id(config)] = lion_hyper(config, utils._resolve_learning_rate(config["learning_rate"], old_count))
             w, p_out, e_out, m_out, _ = eng.make_work(leaf, g, e, m, None, config, hyper, donate, has_nu=False)
             work.append(w)
             configs.append(config)

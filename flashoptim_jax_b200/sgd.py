@@ -101,14 +101,17 @@ def _make_sgd_transform(learning_rate, momentum, dampening, weight_decay, nester
         param_pl, grad_leaves, (ecc_leaves, mu_leaves), treedef = eng.flatten_step_inputs(
             name, params, grads, [state.ecc, state.mu])
         work, new_p, new_e, new_m = [], [], [], []
+        resolve, hypers = utils.GroupResolver(defaults, param_groups), {}
         for (path, leaf), g, e, m in zip(param_pl, grad_leaves, ecc_leaves, mu_leaves):
             leaf = as_tensor(leaf)
-            config = utils._group_config_for_path(path, leaf, defaults, param_groups)
-            lr = utils._resolve_learning_rate(config["learning_rate"], old_count)
+            config = resolve(path, leaf)
             use_momentum = config["momentum"] > 0.0
             if use_momentum and not utils._has_state_leaf(m):
                 raise ValueError(f"{name}: momentum > 0 needs a momentum buffer in the state; re-run init()")
-            hyper = sgd_hyper(config, lr, decoupled_weight_decay)
+            hyper = hypers.get(id(config))
+            if hyper is None:  # once per param group
+                hyper = hypers[id(config)] = sgd_hyper(config, utils._resolve_learning_rate(config["learning_rate"], old_count),
+                                                       decoupled_weight_decay)
             w, p_out, e_out, m_out, _ = eng.make_work(leaf, g, e, m, None, config, hyper, donate, has_nu=False,
                                                       use_momentum=use_momentum)
             work.append(w)

@@ -83,6 +83,32 @@ def _group_config_for_path(path, leaf, defaults: Dict[str, Any], param_groups: O
     return config
 
 
+class GroupResolver:
+    """_group_config_for_path for all leaves of one step: the merged config of a group is built once and the same
+    dict is handed to each of its leaves, so that per-group work (hyper-parameter tuples) can be keyed on it."""
+
+    def __init__(self, defaults: Dict[str, Any], param_groups: Optional[List[ParamGroupSpec]]):
+        self.defaults, self.groups = defaults, list(param_groups or ())
+        for group in self.groups:
+            if "params" not in group:
+                raise ValueError("Each param group must define a 'params' matcher")
+        self._configs: Dict[int, Dict[str, Any]] = {}
+
+    def __call__(self, path, leaf) -> Dict[str, Any]:
+        index = -1
+        for i, group in enumerate(self.groups):
+            if _path_matches(path, leaf, group["params"]):
+                index = i
+                break
+        config = self._configs.get(index)
+        if config is None:
+            config = dict(self.defaults)
+            if index >= 0:
+                config.update({k: v for k, v in self.groups[index].items() if k != "params"})
+            self._configs[index] = config
+        return config
+
+
 # ---- validation (utils.py:157-266) ----------------------------------------------------------
 
 
