@@ -708,18 +708,34 @@ FO_DEVI bool unpack_master(const uint4& p0, const uint4& p1, const uint4& e_in, 
       for (int k = 0; k < 4; ++k) theta[k] = old_lp[k];
     } else {
       int e[8];
+      // The ECC halves / bytes go to fp32 by conversions that name the 16- or 8-bit part of the word
+      // (no sign extension first); the integers are needed by the repairs only.
+      float ef[8];
       if constexpr (ECC_BITS == 16) {
         const uint32_t w[4] = {e_in.x, e_in.y, e_in.z, e_in.w};
 #pragma unroll
-        for (int k = 0; k < 4; ++k) { e[2 * k] = (int)(short)(w[k] & 0xFFFFu); e[2 * k + 1] = (int)w[k] >> 16; }
+        for (int k = 0; k < 4; ++k) {
+          asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %2; cvt.rn.f32.s16 %0, lo; cvt.rn.f32.s16 %1, hi;}"
+              : "=f"(ef[2 * k]), "=f"(ef[2 * k + 1]) : "r"(w[k]));
+          if constexpr (REPAIR) { e[2 * k] = (int)(short)(w[k] & 0xFFFFu); e[2 * k + 1] = (int)w[k] >> 16; }
+        }
       } else {
         const uint32_t w[2] = {e_in.x, e_in.y};
 #pragma unroll
-        for (int k = 0; k < 8; ++k) e[k] = (int)(signed char)((w[k >> 2] >> (8 * (k & 3))) & 0xFFu);
+        for (int k = 0; k < 2; ++k) {
+          asm("{.reg .b8 b0, b1, b2, b3; .reg .s16 t; mov.b32 {b0, b1, b2, b3}, %4;"
+              " cvt.s16.s8 t, b0; cvt.rn.f32.s16 %0, t; cvt.s16.s8 t, b1; cvt.rn.f32.s16 %1, t;"
+              " cvt.s16.s8 t, b2; cvt.rn.f32.s16 %2, t; cvt.s16.s8 t, b3; cvt.rn.f32.s16 %3, t;}"
+              : "=f"(ef[4 * k]), "=f"(ef[4 * k + 1]), "=f"(ef[4 * k + 2]), "=f"(ef[4 * k + 3]) : "r"(w[k]));
+        }
+        if constexpr (REPAIR) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) e[k] = (int)(signed char)((w[k >> 2] >> (8 * (k & 3))) & 0xFFu);
+        }
       }
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        theta[k] = reconstruct_ordinary2<PDT, ECC_BITS>(old_lp[k], mk((float)e[2 * k], (float)e[2 * k + 1]), one2);
+        theta[k] = reconstruct_ordinary2<PDT, ECC_BITS>(old_lp[k], mk(ef[2 * k], ef[2 * k + 1]), one2);
       if constexpr (PDT == FO_BF16) {
         // a value too small for the exponent-field shortcut (zero included)
         if (!(minabs8(old_lp) >= fast::Ordinary<PDT>::kMin)) {
