@@ -71,7 +71,11 @@ VARIANT_CASES = [
     ("adamw_fp16_grads_unfused", "flash_adamw", dict(learning_rate=1e-3, weight_decay=1e-2, master_weight_bits=32, fused=False), 2100, "float16", "float16"),
     ("lion_betas_fused", "flash_lion", dict(learning_rate=3e-4, b1=0.95, b2=0.98, weight_decay=0.1, master_weight_bits=24, fused=True), 1500, "bfloat16", "bfloat16"),
     ("adamw_betas_eps_fused", "flash_adamw", dict(learning_rate=3e-4, b1=0.8, b2=0.95, eps=1e-6, weight_decay=0.1, master_weight_bits=32, fused=True), 1500, "bfloat16", "bfloat16"),
+    # a schedule instead of a number ("@name": see SCHEDULES): it sees the count before the increment
+    ("adamw_schedule_fused", "flash_adamw", dict(learning_rate="@halving", weight_decay=1e-2, master_weight_bits=24, fused=True), 900, "bfloat16", "bfloat16"),
+    ("sgdw_schedule_unfused", "flash_sgdw", dict(learning_rate="@halving", momentum=0.9, weight_decay=1e-2, master_weight_bits=24, fused=False), 900, "bfloat16", "bfloat16"),
 ]
+SCHEDULES = {"@halving": lambda count: 1e-3 * 0.5 ** int(count)}
 NP_DTYPES = {"bfloat16": BF16, "float16": np.dtype(np.float16), "float32": np.dtype(np.float32)}
 
 # Nested pytrees with mixed dtypes and param groups (string, "a/b" path and tuple selectors; first match wins):
@@ -166,7 +170,7 @@ def variant_case(ref, seed, factory, kwargs, n, dtype, grad_dtype, steps=3):
     p = rng.normal(0, 0.02, n).astype(np.float32).astype(NP_DTYPES[dtype])
     grads = [rng.normal(0, 1e-3, n).astype(np.float32).astype(NP_DTYPES[grad_dtype]) for _ in range(steps)]
     out = {"param0": bits(p), "grads": np.stack([bits(g) for g in grads])}
-    tx = getattr(ref, factory)(**kwargs)
+    tx = getattr(ref, factory)(**{k: SCHEDULES.get(v, v) if isinstance(v, str) else v for k, v in kwargs.items()})
     params = {"x": p}
     state = tx.init(params)
     for g in grads:

@@ -216,6 +216,7 @@ def test_python_surface_reproduces_golden(name, donate):
 
 
 VARIANTS = json.load(open(os.path.join(GOLD, "variants.json")))
+SCHEDULES = {"@halving": lambda count: 1e-3 * 0.5 ** int(count)}  # as in tests/golden/make_golden.py
 VARIANT_OPT = {"flash_adam": (C.ADAM, False), "flash_adamw": (C.ADAM, True), "flash_lion": (C.LION, True),
                "flash_sgd": (C.SGD, False), "flash_sgdw": (C.SGD, True)}  # constructor -> (optimizer, decoupled weight decay)
 
@@ -255,7 +256,10 @@ def test_c_oracle_reproduces_variants(name):
     if opt == C.SGD:
         hyper.setdefault("momentum", 0.0)
     leaf = H.fresh_leaf(p0, opt, state, ecc_bits, gs)
+    schedule = SCHEDULES.get(kw["learning_rate"]) if isinstance(kw["learning_rate"], str) else None
     for t, g in enumerate(grads, 1):
+        if schedule is not None:
+            hyper["lr"] = schedule(t - 1)  # the count before the increment (adamw.py:526)
         H.oracle_step(opt, g, leaf, state, gs, H.hyper_tuple(opt, conv, t, **hyper))
     H.assert_leaf_equal(leaf, want, name)
 
@@ -269,7 +273,7 @@ def test_python_surface_reproduces_variants(name):
     import flashoptim_jax_b200 as fo
 
     meta, p0, grads, want = _load_variant(name)
-    tx = getattr(fo, meta["constructor"])(donate=True, **meta["kwargs"])
+    tx = getattr(fo, meta["constructor"])(donate=True, **{k: SCHEDULES.get(v, v) if isinstance(v, str) else v for k, v in meta["kwargs"].items()})
     params = {"x": H.to_torch(p0)}
     state = tx.init(params)
     for g in grads:
