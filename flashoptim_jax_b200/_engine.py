@@ -23,9 +23,7 @@ from ._dev import DTYPE_CODE, ECC_BITS_OF, as_tensor, require_cuda, stream_ptr
 from .quantization import QuantizedArray
 from .utils import (
     _group_config_for_path,
-    _has_state_leaf,
     _is_quantized_leaf,
-    _resolve_learning_rate,
     _tree_leaves_with_paths,
     _use_ecc_leaf,
     _validate_fused_group_size,

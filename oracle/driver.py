@@ -5,7 +5,7 @@ nothing in the product package imports it."""
 
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Optional
 
 import ml_dtypes
 import numpy as np

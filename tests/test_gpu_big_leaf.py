@@ -2,7 +2,6 @@
 use 32-bit element offsets).  The one-call result must equal two calls on hand-made views that
 are each short enough to go in uncut, and the region around the cut must equal the oracle."""
 
-import numpy as np
 import pytest
 
 from oracle import c_oracle as C

@@ -1,7 +1,6 @@
 """Global-norm clipping folded into the step: the sum of squares (fo_sq_norm) against float64, and
 the rescaled step against the oracle (element-wise exact once both sides use the device's sum)."""
 
-import ctypes
 
 import ml_dtypes
 import numpy as np
